@@ -1,0 +1,78 @@
+"""ctypes binding of libeider_b200.so.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libeider_b200.so")
+
+_lib = None
+
+_P = C.c_void_p
+_U32 = C.c_uint32
+_F = C.c_float
+_I = C.c_int
+_SZ = C.c_size_t
+
+# name -> (restype, argtypes).  Mirrors include/eider_b200.h one to one.
+SIGNATURES = {
+    "infer_quantize_nvfp4_col_major_f32": (_I, [_P, _P, _P, _U32, _U32, _F]),
+    "infer_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _P]),
+    "eider_b200_quantize_nvfp4_bf16_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _P]),
+    "eider_b200_quantize_nvfp4_rowscale_on_stream": (_I, [_P, _I, _P, _P, _P, _U32, _U32, _P]),
+    "eider_b200_quantize_nvfp4_weight_on_stream": (_I, [_P, _I, _P, _P, _U32, _U32, _F, _P]),
+    "eider_b200_nvfp4_scales_to_tiled_on_stream": (_I, [_P, _P, _U32, _U32, _P]),
+    "eider_b200_nvfp4_scale_layout_len": (_SZ, [_SZ, _SZ]),
+    "infer_quantize_fp8_e4m3_dynamic_f32_on_stream": (_I, [_P, _P, _P, _U32, _P]),
+    "infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),
+    "eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),
+    "infer_quantize_fp8_e4m3_f32_on_stream": (_I, [_P, _P, _U32, _F, _P]),
+    "eider_b200_quantize_fp8_weight_on_stream": (_I, [_P, _I, _P, _P, _U32, _U32, _P]),
+    "infer_nvfp4_w4a16_matvec_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _F, _U32, _P]),
+    "eider_b200_nvfp4_w4a16_matvec_bf16_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _F, _P]),
+    "eider_b200_fp8_linear_prequantized_simt_on_stream": (_I, [_P, _P, _P, _P, _F, _P, _I, _U32, _U32, _U32, _P]),
+    "eider_b200_nvfp4_gemm_tn_supported": (_I, [_U32, _U32, _U32]),
+    "eider_b200_nvfp4_gemm_tn_create": (_P, [_U32, _U32, _U32]),
+    "eider_b200_nvfp4_gemm_tn_destroy": (None, [_P]),
+    "eider_b200_nvfp4_gemm_tn_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _F, _P, _I, _P]),
+    "eider_b200_fp8_gemm_tn_supported": (_I, [_U32, _U32, _U32]),
+    "eider_b200_fp8_gemm_tn_create": (_P, [_U32, _U32, _U32]),
+    "eider_b200_fp8_gemm_tn_destroy": (None, [_P]),
+    "eider_b200_fp8_gemm_tn_on_stream": (_I, [_P, _P, _P, _P, _P, _F, _F, _P, _P, _I, _P]),
+    "eider_b200_gemm_plan_set_block_n": (_I, [_P, _U32]),
+    "eider_b200_gemm_plan_status": (_I, [_P, _P]),
+}
+
+
+def load() -> C.CDLL:
+    """Load the shared library (building is a separate, explicit step: eider_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m eider_b200.build` "
+            "(there is no CPU or PyTorch fallback for this path)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class CudaError(RuntimeError):
+    """A C-ABI entry point returned a non-zero cudaError_t (crates/eider-cuda/src/error.rs:8-12)."""
+
+    def __init__(self, name: str, code: int):
+        super().__init__(f"{name} failed with cudaError {code}")
+        self.name = name
+        self.code = code
+
+
+def check(name: str, code: int) -> None:
+    if code != 0:
+        raise CudaError(name, int(code))

@@ -1,0 +1,125 @@
+// Shared device/host helpers for the quantized-linear kernels: NVFP4 / FP8 codecs and the
+// 128x4 tiled scale layout.  Numeric semantics follow the reference's host code
+// (crates/eider-cuda/src/format.rs) and are checked bit-for-bit against the CPU oracle.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace eider {
+
+constexpr float kE2M1Max = 6.0f;
+constexpr float kRowScaleDivisor = 2688.0f;  // 6 * 448: e2m1 max times e4m3 max
+
+__host__ __device__ inline uint32_t round_up_u32(uint32_t v, uint32_t m) { return (v + m - 1) / m * m; }
+
+// Bytes of the tiled UE4M3 scale buffer for `outer` rows of `inner` elements
+// (crates/eider-cuda/src/format.rs:194-198).
+__host__ __device__ inline size_t scale_layout_len(size_t outer, size_t inner) {
+    size_t blocks = (inner + 15) / 16;
+    size_t padded = (blocks + 3) / 4 * 4;
+    return (outer + 127) / 128 * 128 * padded;
+}
+
+// Byte offset of (row `outer`, 16-block `kb`) in the 128-row x 4-block tile order
+// (crates/eider-cuda/src/format.rs:208-218).  One 512-byte tile holds 128 rows x 4 blocks as
+// [row % 32][row / 32 % 4][kb % 4], which is also the shape one tcgen05.cp 32x128b copy wants.
+__host__ __device__ inline size_t tiled_scale_offset(uint32_t outer, uint32_t kb, uint32_t inner) {
+    uint32_t blocks = (inner + 15) / 16;
+    uint32_t padded = round_up_u32(blocks, 4);
+    uint32_t in_tile = outer % 128;
+    size_t base = (static_cast<size_t>(kb / 4) * 4 + static_cast<size_t>(outer / 128) * padded) * 128;
+    return base + (in_tile % 32) * 16 + (in_tile / 32) * 4 + (kb % 4);
+}
+
+// E4M3 byte -> f32 (crates/eider-cuda/src/format.rs:121-133).
+__host__ __device__ inline float e4m3_value(uint8_t code) {
+    uint32_t sign = static_cast<uint32_t>(code & 0x80) << 24;
+    uint32_t exp = (code >> 3) & 0x0f;
+    uint32_t mant = code & 0x07;
+    uint32_t bits;
+    if (exp == 0) {
+        float v = static_cast<float>(mant) * 0.001953125f;  // 2^-9
+#ifdef __CUDA_ARCH__
+        bits = __float_as_uint(v) | sign;
+        return __uint_as_float(bits);
+#else
+        return sign ? -v : v;
+#endif
+    }
+    if (exp == 0x0f && mant == 0x07) bits = sign | 0x7fffffffu;
+    else bits = sign | ((exp + 120u) << 23) | (mant << 20);
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(bits);
+#else
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+#endif
+}
+
+#ifdef __CUDACC__
+
+// E2M1 nibble -> f32 (crates/eider-cuda/src/format.rs:78-96).
+__device__ __forceinline__ float e2m1_value(uint32_t nibble) {
+    uint32_t mag = nibble & 7u;
+    uint32_t e = mag >> 1, m = mag & 1u;
+    uint32_t bits = e == 0 ? m * 0x3f000000u : (((e + 126u) << 23) | (m << 22));
+    return __uint_as_float(bits | ((nibble & 8u) << 28));
+}
+
+// Positive finite f32 -> UE4M3 byte, nearest-even, saturating at 448
+// (crates/eider-cuda/src/format.rs:151-167 == __nv_cvt_float_to_fp8(SATFINITE, E4M3)).
+__device__ __forceinline__ uint8_t ue4m3_code(float v) {
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Signed E4M3, saturating, NaN -> 0x7f: the conversion the reference's FP8 quantizers use
+// (crates/eider-cuda/native/non_gemm.cu:9971-9972).
+__device__ __forceinline__ uint8_t e4m3_satfinite(float v) {
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Two f32 -> one byte of E2M1 codes, `lo` in the low nibble (format.rs:44-110).
+__device__ __forceinline__ uint8_t e2m1x2_code(float lo, float hi) {
+    return static_cast<uint8_t>(__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest));
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+
+// f32 -> bf16 bits, nearest-even (crates/eider-cuda/src/format.rs:368-376).
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// Quantize one 16-element block already divided by the input scale.  Returns the scale byte and
+// writes 8 packed bytes.  Order of operations: crates/eider-cuda/native/non_gemm.cu:120-153.
+__device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32_t valid, uint2* packed_out) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        if (static_cast<uint32_t>(i) < valid && isfinite(v[i])) amax = fmaxf(amax, fabsf(v[i]));
+    uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(__fdiv_rn(amax, kE2M1Max));
+    float s = e4m3_value(sc);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        float lo = (s == 0.0f || static_cast<uint32_t>(i) >= valid) ? 0.0f : __fdiv_rn(v[i], s);
+        float hi = (s == 0.0f || static_cast<uint32_t>(i + 1) >= valid) ? 0.0f : __fdiv_rn(v[i + 1], s);
+        uint32_t byte = e2m1x2_code(lo, hi);
+        if (static_cast<uint32_t>(i + 1) >= valid) byte &= 0x0fu;
+        if (static_cast<uint32_t>(i) >= valid) byte = 0;
+        w[i / 8] |= byte << ((i % 8) * 4);
+    }
+    *packed_out = make_uint2(w[0], w[1]);
+    return sc;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace eider

@@ -1,0 +1,385 @@
+// Host side of the tcgen05 GEMMs: TMA descriptor encoding, tile-shape selection at plan creation,
+// launches, and the C ABI.  Replaces the reference's cuBLASLt NVFP4 / FP8 plans
+// (crates/eider-cuda/src/cublaslt/fp4_tn.rs:264-796, fp8_tn.rs:13-292) and its CUTLASS grouped GEMM
+// (crates/eider-cuda/native/cutlass_grouped_gemm.cu) with one hand-written kernel family.
+#include "gemm_umma.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "eider_b200.h"
+
+namespace eider {
+namespace gemm {
+namespace {
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library loads on machines without a driver.
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(ptr);
+    });
+    return fn;
+}
+
+// 2-D byte matrix [rows][row_bytes] with pitch `pitch_bytes`, box = 128 bytes x box_rows, 128-byte swizzle.
+cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch_bytes,
+                     uint32_t box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || pitch_bytes % 16 != 0) return cudaErrorInvalidValue;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {kStageBytesK, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        if (count <= 0) count = 148;
+    }
+    return count;
+}
+
+template <int KIND, int BLOCK_N, bool TRANSPOSED, int TERMS, bool GROUPED>
+cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, const Params& p, uint32_t work_items,
+                   cudaStream_t stream) {
+    constexpr int kStages = default_stages<KIND, BLOCK_N>();
+    constexpr uint32_t kSmem = smem_bytes<KIND, BLOCK_N, kStages>();
+    auto kernel = gemm_kernel<KIND, BLOCK_N, kStages, TRANSPOSED, TERMS, GROUPED>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    uint32_t grid = static_cast<uint32_t>(sm_count());
+    if (work_items < grid) grid = work_items;
+    if (grid == 0) return cudaSuccess;
+    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_rows, map_cols, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------ plans
+struct DensePlan {
+    int kind;
+    uint32_t m, n, k;       // tokens, out features, in features
+    uint32_t block_n;       // weight rows per tile
+    uint32_t* status;       // device status word
+};
+
+struct DecodePlan {
+    int kind;
+    uint32_t max_tokens, n, k, terms;
+    uint32_t splits;
+    float* workspace;
+    uint32_t* counters;
+    uint32_t* status;
+    // activation expansion buffers (NVFP4 W4A16 path)
+    uint8_t* act_packed;
+    uint8_t* act_scales;
+    float* act_col_scale;
+};
+
+struct GroupedPlan {
+    uint32_t m, max_n, k, groups;  // reference naming: m = out features per expert, max_n = max tokens per expert
+    uint32_t* status;
+};
+
+namespace {
+
+cudaError_t alloc_status(uint32_t** status) {
+    cudaError_t st = cudaMalloc(reinterpret_cast<void**>(status), sizeof(uint32_t));
+    if (st != cudaSuccess) return st;
+    return cudaMemset(*status, 0, sizeof(uint32_t));
+}
+
+bool dense_shape_ok(int kind, uint32_t m, uint32_t n, uint32_t k) {
+    if (m == 0 || n == 0 || k == 0) return false;
+    if (kind == kNvf4) return k % 32 == 0;  // TMA pitch (K/2 bytes) must be a multiple of 16
+    return k % 16 == 0;
+}
+
+uint32_t pick_block_n(uint32_t m, uint32_t n) {
+    // Fill the machine: prefer 256-wide weight tiles, fall back to narrower ones when the tile count is small.
+    const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    for (uint32_t bn : {256u, 128u, 64u}) {
+        uint32_t tiles = row_tiles * ((n + bn - 1) / bn);
+        if (tiles >= sms || bn == 64u) return bn;
+    }
+    return 64u;
+}
+
+}  // namespace
+
+cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const uint8_t* w_values,
+                      const uint8_t* w_scales, const void* c, void* d, float alpha, float beta, const float* token_scale,
+                      const float* channel_scale, int out_is_bf16, cudaStream_t stream) {
+    const bool nv = plan.kind == kNvf4;
+    if (!x_values || !w_values || !d || (nv && (!x_scales || !w_scales))) return cudaErrorInvalidValue;
+    if (beta != 0.0f && !c) return cudaErrorInvalidValue;
+    const uint32_t k_bytes = nv ? plan.k / 2 : plan.k;
+    CUtensorMap map_rows, map_cols;
+    cudaError_t st = make_map(&map_rows, x_values, plan.m, k_bytes, k_bytes, kTileRows);
+    if (st != cudaSuccess) return st;
+    st = make_map(&map_cols, w_values, plan.n, k_bytes, k_bytes, plan.block_n);
+    if (st != cudaSuccess) return st;
+    Params p{};
+    p.rows = plan.m;
+    p.cols = plan.n;
+    p.k_bytes = k_bytes;
+    p.row_tiles = (plan.m + kTileRows - 1) / kTileRows;
+    p.col_tiles = (plan.n + plan.block_n - 1) / plan.block_n;
+    p.k_stages = (k_bytes + kStageBytesK - 1) / kStageBytesK;
+    p.sf_rows = x_scales;
+    p.sf_cols = w_scales;
+    p.sf_tile_stride = ((plan.k / 16 + 3) / 4 * 4) * 128;
+    p.out = d;
+    p.c_in = c;
+    p.ld_out = plan.n;
+    p.out_is_bf16 = out_is_bf16;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.row_scale = token_scale;
+    p.col_scale = channel_scale;
+    p.out_cols = plan.n;
+    p.splits = 1;
+    p.status = plan.status;
+    const uint32_t items = p.row_tiles * p.col_tiles;
+#define EIDER_DENSE(KIND, BN) launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream)
+    if (nv) {
+        if (plan.block_n == 256) return EIDER_DENSE(kNvf4, 256);
+        if (plan.block_n == 128) return EIDER_DENSE(kNvf4, 128);
+        return EIDER_DENSE(kNvf4, 64);
+    }
+    if (plan.block_n == 256) return EIDER_DENSE(kFp8, 256);
+    if (plan.block_n == 128) return EIDER_DENSE(kFp8, 128);
+    return EIDER_DENSE(kFp8, 64);
+#undef EIDER_DENSE
+}
+
+// Decode orientation: weights are the row operand (128 output features per tile on the tensor-memory
+// lanes), the few tokens (x terms) are the column operand.
+cudaError_t run_decode(const DecodePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const float* x_col_scale,
+                       uint32_t tokens, const uint8_t* w_values, const uint8_t* w_scales, const float* channel_scale,
+                       const void* c, void* d, float alpha, float beta, int out_is_bf16, cudaStream_t stream) {
+    const bool nv = plan.kind == kNvf4;
+    if (!x_values || !w_values || !d || tokens == 0 || tokens > plan.max_tokens) return cudaErrorInvalidValue;
+    if (nv && (!x_scales || !w_scales)) return cudaErrorInvalidValue;
+    const uint32_t k_bytes = nv ? plan.k / 2 : plan.k;
+    const uint32_t cols = tokens * plan.terms;
+    uint32_t block_n = 16;
+    while (block_n < cols) block_n *= 2;
+    if (block_n > 256) return cudaErrorInvalidValue;
+    CUtensorMap map_rows, map_cols;
+    cudaError_t st = make_map(&map_rows, w_values, plan.n, k_bytes, k_bytes, kTileRows);
+    if (st != cudaSuccess) return st;
+    st = make_map(&map_cols, x_values, cols, k_bytes, k_bytes, block_n);
+    if (st != cudaSuccess) return st;
+    Params p{};
+    p.rows = plan.n;
+    p.cols = cols;
+    p.k_bytes = k_bytes;
+    p.row_tiles = (plan.n + kTileRows - 1) / kTileRows;
+    p.col_tiles = 1;
+    p.k_stages = (k_bytes + kStageBytesK - 1) / kStageBytesK;
+    p.sf_rows = w_scales;
+    p.sf_cols = x_scales;
+    p.sf_tile_stride = ((plan.k / 16 + 3) / 4 * 4) * 128;
+    p.out = d;
+    p.c_in = c;
+    p.ld_out = plan.n;
+    p.out_is_bf16 = out_is_bf16;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.row_scale = channel_scale;
+    p.col_scale = x_col_scale;
+    p.out_cols = tokens;
+    p.splits = plan.splits;
+    p.workspace = plan.workspace;
+    p.counters = plan.counters;
+    p.status = plan.status;
+    const uint32_t items = p.row_tiles * p.splits;
+#define EIDER_DECODE(KIND, BN, TERMS) launch<KIND, BN, true, TERMS, false>(map_rows, map_cols, p, items, stream)
+    if (nv) {
+        if (plan.terms == 8) {
+            switch (block_n) {
+                case 16: return EIDER_DECODE(kNvf4, 16, 8);
+                case 32: return EIDER_DECODE(kNvf4, 32, 8);
+                case 64: return EIDER_DECODE(kNvf4, 64, 8);
+                case 128: return EIDER_DECODE(kNvf4, 128, 8);
+                default: return EIDER_DECODE(kNvf4, 256, 8);
+            }
+        }
+        if (plan.terms == 4) {
+            switch (block_n) {
+                case 16: return EIDER_DECODE(kNvf4, 16, 4);
+                case 32: return EIDER_DECODE(kNvf4, 32, 4);
+                case 64: return EIDER_DECODE(kNvf4, 64, 4);
+                case 128: return EIDER_DECODE(kNvf4, 128, 4);
+                default: return EIDER_DECODE(kNvf4, 256, 4);
+            }
+        }
+        if (plan.terms == 1) {
+            switch (block_n) {
+                case 16: return EIDER_DECODE(kNvf4, 16, 1);
+                case 32: return EIDER_DECODE(kNvf4, 32, 1);
+                case 64: return EIDER_DECODE(kNvf4, 64, 1);
+                case 128: return EIDER_DECODE(kNvf4, 128, 1);
+                default: return EIDER_DECODE(kNvf4, 256, 1);
+            }
+        }
+        return cudaErrorInvalidValue;
+    }
+    switch (block_n) {
+        case 16: return EIDER_DECODE(kFp8, 16, 1);
+        case 32: return EIDER_DECODE(kFp8, 32, 1);
+        case 64: return EIDER_DECODE(kFp8, 64, 1);
+        case 128: return EIDER_DECODE(kFp8, 128, 1);
+        default: return EIDER_DECODE(kFp8, 256, 1);
+    }
+#undef EIDER_DECODE
+}
+
+cudaError_t run_grouped(const GroupedPlan& plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
+                        const uint8_t* w_scales, uint16_t* output, const float* alpha, const uint32_t* expert_offsets,
+                        uint32_t total_routes, cudaStream_t stream) {
+    if (!a_values || !a_scales || !w_values || !w_scales || !output || !alpha || !expert_offsets || total_routes == 0)
+        return cudaErrorInvalidValue;
+    const uint32_t k_bytes = plan.k / 2;
+    constexpr uint32_t kBlockN = 256;
+    CUtensorMap map_rows, map_cols;
+    cudaError_t st = make_map(&map_rows, a_values, total_routes, k_bytes, k_bytes, kTileRows);
+    if (st != cudaSuccess) return st;
+    st = make_map(&map_cols, w_values, static_cast<uint64_t>(plan.groups) * plan.m, k_bytes, k_bytes,
+                  plan.m % 256 == 0 ? 256 : 128);
+    if (st != cudaSuccess) return st;
+    Params p{};
+    p.rows = total_routes;
+    p.cols = plan.groups * plan.m;
+    p.k_bytes = k_bytes;
+    p.row_tiles = 0;
+    p.k_stages = (k_bytes + kStageBytesK - 1) / kStageBytesK;
+    p.sf_rows = a_scales;
+    p.sf_cols = w_scales;
+    p.sf_tile_stride = ((plan.k / 16 + 3) / 4 * 4) * 128;
+    p.out = output;
+    p.ld_out = plan.m;
+    p.out_is_bf16 = 1;
+    p.alpha = 1.0f;
+    p.beta = 0.0f;
+    p.out_cols = plan.m;
+    p.splits = 1;
+    p.group_offsets = expert_offsets;
+    p.groups = plan.groups;
+    p.group_cols = plan.m;
+    p.group_alpha = alpha;
+    p.status = plan.status;
+    // upper bound on work items: every expert may add one partial row tile
+    const uint32_t max_row_tiles = (total_routes + kTileRows - 1) / kTileRows + plan.groups;
+    if (plan.m % 256 == 0) {
+        p.col_tiles = plan.m / 256;
+        return launch<kNvf4, 256, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
+    }
+    p.col_tiles = plan.m / 128;
+    return launch<kNvf4, 128, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
+    (void)kBlockN;
+}
+
+}  // namespace gemm
+}  // namespace eider
+
+using namespace eider;
+using namespace eider::gemm;
+
+extern "C" {
+
+// ---- dense NVFP4 W4A4 GEMM -----------------------------------------------------------------
+int eider_b200_nvfp4_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k) { return dense_shape_ok(kNvf4, m, n, k) ? 1 : 0; }
+
+void* eider_b200_nvfp4_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
+    if (!dense_shape_ok(kNvf4, m, n, k)) return nullptr;
+    auto* plan = new DensePlan{kNvf4, m, n, k, pick_block_n(m, n), nullptr};
+    if (alloc_status(&plan->status) != cudaSuccess) {
+        delete plan;
+        return nullptr;
+    }
+    return plan;
+}
+
+void eider_b200_nvfp4_gemm_tn_destroy(void* raw) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan) return;
+    cudaFree(plan->status);
+    delete plan;
+}
+
+cudaError_t eider_b200_nvfp4_gemm_tn_on_stream(void* raw, const uint8_t* x_values, const uint8_t* x_scales,
+                                               const uint8_t* w_values, const uint8_t* w_scales, const void* c, void* d,
+                                               float alpha, float beta, const float* token_scale, int out_is_bf16,
+                                               cudaStream_t stream) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || plan->kind != kNvf4) return cudaErrorInvalidValue;
+    return run_dense(*plan, x_values, x_scales, w_values, w_scales, c, d, alpha, beta, token_scale, nullptr, out_is_bf16,
+                     stream);
+}
+
+int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || (block_n != 64 && block_n != 128 && block_n != 256)) return 0;
+    plan->block_n = block_n;
+    return 1;
+}
+
+cudaError_t eider_b200_gemm_plan_status(void* raw, uint32_t* host_status) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || !host_status) return cudaErrorInvalidValue;
+    return cudaMemcpy(host_status, plan->status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+}
+
+// ---- dense FP8 E4M3 GEMM ---------------------------------------------------------------------
+int eider_b200_fp8_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k) { return dense_shape_ok(kFp8, m, n, k) ? 1 : 0; }
+
+void* eider_b200_fp8_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
+    if (!dense_shape_ok(kFp8, m, n, k)) return nullptr;
+    auto* plan = new DensePlan{kFp8, m, n, k, pick_block_n(m, n), nullptr};
+    if (alloc_status(&plan->status) != cudaSuccess) {
+        delete plan;
+        return nullptr;
+    }
+    return plan;
+}
+
+void eider_b200_fp8_gemm_tn_destroy(void* raw) { eider_b200_nvfp4_gemm_tn_destroy(raw); }
+
+cudaError_t eider_b200_fp8_gemm_tn_on_stream(void* raw, const uint8_t* x_values, const uint8_t* w_values, const void* c,
+                                             void* d, float alpha, float beta, const float* token_scale,
+                                             const float* channel_scale, int out_is_bf16, cudaStream_t stream) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || plan->kind != kFp8) return cudaErrorInvalidValue;
+    return run_dense(*plan, x_values, nullptr, w_values, nullptr, c, d, alpha, beta, token_scale, channel_scale,
+                     out_is_bf16, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,485 @@
+// tcgen05 GEMM mainloop shared by the dense prefill GEMM, the decode (weights-as-rows) GEMM and the
+// grouped MoE GEMM.
+//
+// One CTA per SM, persistent over output tiles.  Warp roles:
+//   warp 0      TMA producer: operand tiles (cp.async.bulk.tensor, 128-byte swizzle) and, for NVFP4,
+//               the 512-byte scale tiles (cp.async.bulk) into a STAGES-deep shared-memory ring;
+//   warp 1      MMA issuer: one elected lane copies the stage's scale tiles into tensor memory
+//               (tcgen05.cp) and issues four tcgen05.mma per stage, accumulating in tensor memory;
+//   warps 2..5  epilogue: tcgen05.ld the 128 x BLOCK_N fp32 accumulator, apply alpha / row / column
+//               scales (+ beta * C), convert and store.
+// Data layout: both operands are K-major byte matrices ([rows][K/2] packed E2M1 or [rows][K] E4M3); a
+// stage holds 128 bytes of K per row (256 NVFP4 or 128 FP8 elements = four MMAs).  The "row" operand
+// (128 rows per tile) lands on the 128 tensor-memory lanes, the "column" operand (BLOCK_N rows per
+// tile) on tensor-memory columns.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace eider {
+namespace gemm {
+
+enum Kind { kNvf4 = 0, kFp8 = 1 };
+
+constexpr uint32_t kTileRows = 128;       // MMA M
+constexpr uint32_t kStageBytesK = 128;    // bytes of K per row per stage (one swizzle row)
+constexpr uint32_t kNumThreads = 192;     // producer warp, MMA warp, four epilogue warps
+constexpr uint32_t kScaleTileBytes = 512; // 128 rows x 4 blocks
+
+struct Params {
+    // problem
+    uint32_t rows;        // extent of the row operand (tensor-memory lanes)
+    uint32_t cols;        // extent of the column operand
+    uint32_t k_bytes;     // bytes of K per row (K/2 for NVFP4, K for FP8)
+    uint32_t row_tiles;   // ceil(rows / 128)
+    uint32_t col_tiles;   // ceil(cols / BLOCK_N)
+    uint32_t k_stages;    // ceil(k_bytes / 128)
+    // NVFP4 block scales in the 128x4 tile layout (null for FP8)
+    const uint8_t* sf_rows;
+    const uint8_t* sf_cols;
+    uint32_t sf_tile_stride;  // bytes between consecutive 128-row scale tiles = padded(K/16) * 128
+    // epilogue
+    void* out;             // [rows][ld_out] (or [cols][ld_out] when TRANSPOSED)
+    const void* c_in;      // optional C with the same layout and dtype as out (beta != 0)
+    uint32_t ld_out;
+    int out_is_bf16;
+    float alpha, beta;
+    const float* row_scale;  // per row-operand row, may be null
+    const float* col_scale;  // per column-operand row, may be null
+    // decode: combine `TERMS` consecutive columns into one output column; split-K
+    uint32_t out_cols;       // number of logical output columns (cols / TERMS)
+    uint32_t splits;         // K splits (1 = none)
+    float* workspace;        // [splits][row_tiles*128][out_cols] fp32 partials
+    uint32_t* counters;      // [row_tiles] arrival counters, self-resetting
+    // grouped (MoE): per-group row ranges of the row operand
+    const uint32_t* group_offsets;  // [groups + 1] or null
+    uint32_t groups;
+    uint32_t group_cols;            // column-operand rows per group (weights per expert)
+    const float* group_alpha;       // per-group alpha (null: use alpha)
+    uint32_t* status;               // device status word, 0 = ok
+};
+
+template <int BLOCK_N> struct SmemLayout {
+    static constexpr uint32_t kA = kTileRows * kStageBytesK;                 // 16 KB
+    static constexpr uint32_t kB = BLOCK_N * kStageBytesK;
+    static constexpr uint32_t kSfA = 4 * kScaleTileBytes;                    // 2 KB
+    static constexpr uint32_t kSfB = (BLOCK_N > 128 ? 2 : 1) * 4 * kScaleTileBytes;
+    __host__ __device__ static constexpr uint32_t stage_bytes(bool nvf4) { return kA + kB + (nvf4 ? kSfA + kSfB : 0); }
+};
+
+template <int KIND, int BLOCK_N> constexpr int default_stages() {
+    constexpr uint32_t per = SmemLayout<BLOCK_N>::stage_bytes(KIND == kNvf4);
+    constexpr int s = static_cast<int>((220u * 1024u) / per);
+    return s > 8 ? 8 : s;
+}
+
+template <int KIND, int BLOCK_N, int STAGES> constexpr uint32_t smem_bytes() {
+    return SmemLayout<BLOCK_N>::stage_bytes(KIND == kNvf4) * STAGES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+
+// Tensor-memory columns: accumulator stages + (NVFP4) one stage of scale columns.
+template <int KIND, int BLOCK_N> struct TmemPlan {
+    static constexpr uint32_t kSfACols = KIND == kNvf4 ? 16 : 0;                        // 4 MMAs x 4 columns
+    static constexpr uint32_t kSfBCols = KIND == kNvf4 ? (BLOCK_N > 128 ? 32 : 16) : 0;
+    static constexpr uint32_t kAccStages = (2 * BLOCK_N + kSfACols + kSfBCols <= 512) ? 2 : 1;
+    static constexpr uint32_t kUsed = kAccStages * BLOCK_N + kSfACols + kSfBCols;
+    static constexpr uint32_t kAlloc = kUsed <= 32 ? 32 : kUsed <= 64 ? 64 : kUsed <= 128 ? 128 : kUsed <= 256 ? 256 : 512;
+    static constexpr uint32_t kSfAOffset = kAccStages * BLOCK_N;
+    static constexpr uint32_t kSfBOffset = kSfAOffset + kSfACols;
+};
+
+struct TileCoord {
+    uint32_t row0;        // first row-operand row of the tile
+    uint32_t row_end;     // one past the last valid row (group end for grouped GEMM)
+    uint32_t col0;        // first column-operand row (already includes the group's weight offset)
+    uint32_t out_col0;    // first output column
+    uint32_t group;
+    uint32_t sf_row_tile; // index of the 128-row scale tile of the row operand
+    uint32_t k_stage0, k_stage1;  // stage range handled by this work item
+    uint32_t split;
+    uint32_t row_tile;    // index used for split-K bookkeeping
+};
+
+// Grouped schedule: work items are (128-row tile of a group) x column tiles.  Each CTA walks the group
+// table; the walk is cheap (<= a few hundred groups) and identical in all three roles.
+struct GroupWalker {
+    const uint32_t* offsets;
+    uint32_t groups, col_tiles;
+    uint32_t g = 0, base = 0;  // base = number of work items before group g
+    __device__ bool locate(uint32_t item, uint32_t& group, uint32_t& tile_in_group, uint32_t& col_tile) {
+        while (g < groups) {
+            uint32_t n = offsets[g + 1] - offsets[g];
+            uint32_t items = ((n + kTileRows - 1) / kTileRows) * col_tiles;
+            if (item < base + items) {
+                uint32_t local = item - base;
+                group = g;
+                col_tile = local % col_tiles;   // column tiles fastest: CTAs side by side share the rows
+                tile_in_group = local / col_tiles;
+                return true;
+            }
+            base += items;
+            ++g;
+        }
+        return false;
+    }
+};
+
+template <int BLOCK_N, int TERMS, bool GROUPED>
+__device__ __forceinline__ bool get_tile(const Params& p, uint32_t item, GroupWalker& walker, TileCoord& t) {
+    if (GROUPED) {
+        uint32_t group, tile_in_group, col_tile;
+        if (!walker.locate(item, group, tile_in_group, col_tile)) return false;
+        uint32_t g0 = p.group_offsets[group], g1 = p.group_offsets[group + 1];
+        t.row0 = g0 + tile_in_group * kTileRows;
+        t.row_end = g1;
+        t.col0 = group * p.group_cols + col_tile * BLOCK_N;
+        t.out_col0 = col_tile * BLOCK_N;
+        t.group = group;
+        // per-group scale tiles start at ((offset + 127) / 128 + group) tiles
+        t.sf_row_tile = (g0 + kTileRows - 1) / kTileRows + group + tile_in_group;
+        t.k_stage0 = 0;
+        t.k_stage1 = p.k_stages;
+        t.split = 0;
+        t.row_tile = 0;
+        return true;
+    }
+    uint32_t total = p.row_tiles * p.col_tiles * p.splits;
+    if (item >= total) return false;
+    uint32_t row_tile = item % p.row_tiles;  // row tiles fastest: neighbours share the column tile
+    uint32_t rest = item / p.row_tiles;
+    uint32_t col_tile = rest % p.col_tiles;
+    uint32_t split = rest / p.col_tiles;
+    t.row0 = row_tile * kTileRows;
+    t.row_end = p.rows;
+    t.col0 = col_tile * BLOCK_N;
+    t.out_col0 = col_tile * (BLOCK_N / TERMS);
+    t.group = 0;
+    t.sf_row_tile = row_tile;
+    uint32_t per = (p.k_stages + p.splits - 1) / p.splits;
+    t.k_stage0 = split * per;
+    t.k_stage1 = min(p.k_stages, t.k_stage0 + per);
+    t.split = split;
+    t.row_tile = row_tile;
+    return true;
+}
+
+template <bool BF16> __device__ __forceinline__ void store_chunk32(void* out, size_t index, const float (&v)[32]);
+template <> __device__ __forceinline__ void store_chunk32<true>(void* out, size_t index, const float (&v)[32]) {
+    uint16_t* dst = static_cast<uint16_t*>(out) + index;
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+template <> __device__ __forceinline__ void store_chunk32<false>(void* out, size_t index, const float (&v)[32]) {
+    float* dst = static_cast<float*>(out) + index;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
+// KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
+// [col][row] (decode: rows are output features, columns are tokens).  TERMS: consecutive columns that
+// are summed (with their column scales) into one output column.  GROUPED: MoE schedule.
+template <int KIND, int BLOCK_N, int STAGES, bool TRANSPOSED, int TERMS, bool GROUPED>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, const Params p) {
+    using L = SmemLayout<BLOCK_N>;
+    using T = TmemPlan<KIND, BLOCK_N>;
+    constexpr bool kNv = KIND == kNvf4;
+    constexpr uint32_t kStage = L::stage_bytes(kNv);
+    constexpr uint32_t kAcc = T::kAccStages;
+    static_assert(BLOCK_N == 16 || BLOCK_N == 32 || BLOCK_N == 64 || BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+    static_assert(BLOCK_N % TERMS == 0, "TERMS must divide BLOCK_N");
+    static_assert(!(GROUPED && (TRANSPOSED || TERMS != 1)), "grouped GEMM is row-major, one term");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem_a + STAGES * L::kA;
+    uint8_t* smem_sfa = smem_b + STAGES * L::kB;
+    uint8_t* smem_sfb = smem_sfa + (kNv ? STAGES * L::kSfA : 0);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStage);
+    uint64_t* full = bars;                    // [STAGES]
+    uint64_t* empty = bars + STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;   // [kAcc]
+    uint64_t* acc_empty = acc_full + kAcc;    // [kAcc]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAcc);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* last_flag = tmem_slot + 2;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            umma::mbar_init(&full[i], 1);
+            umma::mbar_init(&empty[i], 1);
+        }
+        for (uint32_t i = 0; i < kAcc; ++i) {
+            umma::mbar_init(&acc_full[i], 1);
+            umma::mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        umma::fence_barrier_init();
+        umma::prefetch_tensormap(&map_rows);
+        umma::prefetch_tensormap(&map_cols);
+    }
+    if (warp == 1) {
+        umma::tmem_alloc(tmem_slot, T::kAlloc);
+        umma::tmem_relinquish();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    GroupWalker walker{p.group_offsets, p.groups, p.col_tiles};
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            TileCoord t;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x) {
+                for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
+                    const uint32_t stage = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    if (!umma::mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty)) { ok = false; break; }
+                    const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
+                    uint32_t bytes = L::kA + L::kB;
+                    // scale tiles past the end of the column operand do not exist in memory: their rows are
+                    // zero-filled by the TMA and their outputs are never stored, so the copy is skipped
+                    const uint32_t sf_col_tiles = (p.cols + kTileRows - 1) / kTileRows;
+                    const uint32_t sf_col_tile0 = t.col0 / kTileRows;
+                    const bool second_sf = BLOCK_N > 128 && (sf_col_tile0 + 1 < sf_col_tiles);
+                    if (kNv) bytes += kb * kScaleTileBytes * (2 + (second_sf ? 1 : 0));
+                    umma::mbar_arrive_expect_tx(&full[stage], bytes);
+                    umma::tma_load_2d(smem_a + stage * L::kA, &map_rows, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                      static_cast<int32_t>(t.row0));
+                    umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                      static_cast<int32_t>(t.col0));
+                    if (kNv) {
+                        const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
+                        umma::bulk_load_1d(smem_sfa + stage * L::kSfA,
+                                           p.sf_rows + static_cast<size_t>(t.sf_row_tile) * p.sf_tile_stride + k_off,
+                                           kb * kScaleTileBytes, &full[stage]);
+                        umma::bulk_load_1d(smem_sfb + stage * L::kSfB,
+                                           p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
+                                           kb * kScaleTileBytes, &full[stage]);
+                        if (second_sf)
+                            umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes,
+                                               p.sf_cols + static_cast<size_t>(sf_col_tile0 + 1) * p.sf_tile_stride + k_off,
+                                               kb * kScaleTileBytes, &full[stage]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = kNv ? umma::idesc_nvf4(BLOCK_N) : umma::idesc_f8(BLOCK_N);
+            uint32_t it = 0, tile_count = 0;
+            TileCoord t;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x, ++tile_count) {
+                const uint32_t acc = tile_count % kAcc;
+                const uint32_t acc_phase = (tile_count / kAcc) & 1;
+                if (!umma::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty)) { ok = false; break; }
+                umma::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+                for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
+                    const uint32_t stage = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    if (!umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull)) { ok = false; break; }
+                    umma::tc_fence_after();
+                    const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);
+                    const uint32_t a_addr = umma::smem_u32(smem_a + stage * L::kA);
+                    const uint32_t b_addr = umma::smem_u32(smem_b + stage * L::kB);
+                    if (kNv) {
+                        const uint32_t sfa_addr = umma::smem_u32(smem_sfa + stage * L::kSfA);
+                        const uint32_t sfb_addr = umma::smem_u32(smem_sfb + stage * L::kSfB);
+                        for (uint32_t j = 0; j < kb; ++j) {
+                            umma::tc_copy_scales(tmem_base + T::kSfAOffset + j * 4, umma::smem_desc_scales(sfa_addr + j * kScaleTileBytes));
+                            if (BLOCK_N > 128) {
+                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 8, umma::smem_desc_scales(sfb_addr + j * kScaleTileBytes));
+                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 8 + 4,
+                                                     umma::smem_desc_scales(sfb_addr + (4 + j) * kScaleTileBytes));
+                            } else {
+                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 4, umma::smem_desc_scales(sfb_addr + j * kScaleTileBytes));
+                            }
+                        }
+                    }
+                    for (uint32_t j = 0; j < kb; ++j) {
+                        const uint64_t a_desc = umma::smem_desc_sw128(a_addr + j * 32);
+                        const uint64_t b_desc = umma::smem_desc_sw128(b_addr + j * 32);
+                        const uint32_t accumulate = (s > t.k_stage0 || j > 0) ? 1u : 0u;
+                        // a column tile narrower than 128 starts (col0 % 128) / 32 columns into its scale tile
+                        const uint32_t sfb_sub = BLOCK_N < 128 ? (t.col0 % kTileRows) / 32 : 0;
+                        if (kNv)
+                            umma::mma_nvf4(d_tmem, a_desc, b_desc, idesc, tmem_base + T::kSfAOffset + j * 4,
+                                           tmem_base + T::kSfBOffset + j * (BLOCK_N > 128 ? 8 : 4) + sfb_sub, accumulate);
+                        else
+                            umma::mma_f8(d_tmem, a_desc, b_desc, idesc, accumulate);
+                    }
+                    umma::tc_commit(&empty[stage]);  // frees the stage once these MMAs (and scale copies) retire
+                }
+                if (ok) umma::tc_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        uint32_t tile_count = 0;
+        TileCoord t;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x, ++tile_count) {
+            const uint32_t acc = tile_count % kAcc;
+            const uint32_t acc_phase = (tile_count / kAcc) & 1;
+            const bool empty_tile = t.k_stage0 >= t.k_stage1;  // a K split with no stages contributes zeros
+            if (!umma::mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
+            umma::tc_fence_after();
+            const uint32_t row = t.row0 + quad * 32 + lane;
+            const bool row_ok = row < t.row_end;
+            float rs = GROUPED ? (p.group_alpha ? p.group_alpha[t.group] : p.alpha) : p.alpha;
+            if (p.row_scale && row_ok) rs *= p.row_scale[row];
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BLOCK_N; c += 32) {
+                constexpr uint32_t kChunk = BLOCK_N < 32 ? BLOCK_N : 32;
+                uint32_t raw[32];
+                if (empty_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) raw[i] = 0;
+                } else if (kChunk == 32) {
+                    umma::tmem_load_32x32(taddr + c, raw);
+                } else {
+                    uint32_t r16[16];
+                    umma::tmem_load_32x16(taddr + c, r16);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { raw[i] = r16[i]; raw[i + 16] = 0; }
+                }
+                umma::tmem_load_wait();
+                if (!TRANSPOSED) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t col = t.out_col0 + c + i;
+                        float x = __uint_as_float(raw[i]) * rs;
+                        if (p.col_scale) x *= (col < (GROUPED ? p.group_cols : p.cols)) ? p.col_scale[(GROUPED ? t.group * p.group_cols : 0) + col] : 0.0f;
+                        v[i] = x;
+                    }
+                    const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
+                    const uint32_t col0 = t.out_col0 + c;
+                    if (row_ok && col0 < ncols) {
+                        const size_t index = static_cast<size_t>(row) * p.ld_out + col0;
+                        const bool full_chunk = (col0 + 32 <= ncols) && (kChunk == 32);
+                        const bool aligned = p.out_is_bf16 ? ((index % 8) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
+                                                           : ((index % 4) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+                        if (p.beta != 0.0f && p.c_in) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (col0 + i < ncols && static_cast<uint32_t>(i) < kChunk) {
+                                    float cv = p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index + i])
+                                                             : static_cast<const float*>(p.c_in)[index + i];
+                                    v[i] = fmaf(p.beta, cv, v[i]);
+                                }
+                            }
+                        }
+                        if (full_chunk && aligned) {
+                            if (p.out_is_bf16) store_chunk32<true>(p.out, index, v);
+                            else store_chunk32<false>(p.out, index, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (col0 + i < ncols && static_cast<uint32_t>(i) < kChunk) {
+                                    if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index + i] = float_to_bf16_bits(v[i]);
+                                    else static_cast<float*>(p.out)[index + i] = v[i];
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    // rows are output features, groups of TERMS columns are one token
+#pragma unroll
+                    for (int g = 0; g < 32 / TERMS; ++g) {
+                        if (static_cast<uint32_t>(g * TERMS) >= kChunk) break;
+                        const uint32_t ocol = t.out_col0 + (c / TERMS) + g;
+                        if (ocol >= p.out_cols) break;
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < TERMS; ++j) {
+                            const uint32_t col = t.col0 + c + g * TERMS + j;
+                            const float cs = p.col_scale ? p.col_scale[col] : 1.0f;
+                            sum = fmaf(__uint_as_float(raw[g * TERMS + j]), cs, sum);
+                        }
+                        if (p.splits > 1) {
+                            p.workspace[(static_cast<size_t>(t.split) * p.row_tiles * kTileRows + row) * p.out_cols + ocol] = sum;
+                        } else if (row_ok) {
+                            const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
+                            float x = sum * rs;
+                            if (p.beta != 0.0f && p.c_in)
+                                x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
+                                                               : static_cast<const float*>(p.c_in)[index], x);
+                            if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
+                            else static_cast<float*>(p.out)[index] = x;
+                        }
+                    }
+                }
+            }
+            // accumulator drained: hand the tensor-memory stage back to the MMA warp
+            umma::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+
+            if (TRANSPOSED && p.splits > 1) {
+                // split-K: the last CTA to finish a row tile sums the partials in split order.
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    uint32_t prev = atomicAdd(&p.counters[t.row_tile], 1u);
+                    *last_flag = (prev == p.splits - 1) ? 1u : 0u;
+                    if (prev == p.splits - 1) p.counters[t.row_tile] = 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    if (row_ok) {
+                        for (uint32_t ocol = 0; ocol < p.out_cols; ++ocol) {
+                            float sum = 0.0f;
+                            for (uint32_t s = 0; s < p.splits; ++s)
+                                sum += __ldcg(&p.workspace[(static_cast<size_t>(s) * p.row_tiles * kTileRows + row) * p.out_cols + ocol]);
+                            const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
+                            float x = sum * rs;
+                            if (p.beta != 0.0f && p.c_in)
+                                x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
+                                                               : static_cast<const float*>(p.c_in)[index], x);
+                            if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
+                            else static_cast<float*>(p.out)[index] = x;
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    umma::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        umma::tc_fence_after();
+        umma::tmem_dealloc(tmem_base, T::kAlloc);
+    }
+}
+
+}  // namespace gemm
+}  // namespace eider

@@ -1,0 +1,305 @@
+// Activation / weight quantizers: NVFP4 (E2M1 codes + UE4M3 block scales) and FP8 E4M3.
+//
+// HBM-bound element-wise work: one CTA per row, each thread owns whole 16-element blocks so the
+// block maximum, the scale byte and the eight packed bytes are produced without shuffles, loads
+// are 128-bit and the packed store is one 64-bit word per block.
+//
+// Numerics restate crates/eider-cuda/native/non_gemm.cu:106-155 with IEEE divisions
+// (the reference's host twin, crates/eider-cuda/src/format.rs:242-292, is the arbiter).
+#include "common.cuh"
+#include "eider_b200.h"
+
+namespace eider {
+
+namespace {
+
+template <typename T> struct Loader;
+template <> struct Loader<float> {
+    static __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
+        const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float4 f = __ldg(q + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    }
+    static __device__ __forceinline__ float load1(const float* p) { return __ldg(p); }
+};
+template <> struct Loader<uint16_t> {
+    static __device__ __forceinline__ void load16(const uint16_t* p, float (&v)[16]) {
+        const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint4 u = __ldg(q + i);
+            uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        }
+    }
+    static __device__ __forceinline__ float load1(const uint16_t* p) { return bf16_bits_to_float(__ldg(p)); }
+};
+
+template <typename T>
+__device__ __forceinline__ void load_block(const T* row, uint32_t k, uint32_t b, bool vec_ok, float (&v)[16],
+                                           uint32_t& valid) {
+    uint32_t start = b * 16;
+    valid = min(16u, k - start);
+    if (valid == 16 && vec_ok) {
+        Loader<T>::load16(row + start, v);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = static_cast<uint32_t>(i) < valid ? Loader<T>::load1(row + start + i) : 0.0f;
+    }
+}
+
+__device__ __forceinline__ float block_max(float v, float* smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = smem[0];
+    for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) r = fmaxf(r, smem[w]);
+    __syncthreads();
+    return r;
+}
+
+enum ScaleMode { kStatic = 0, kPerRow = 1 };
+
+// One CTA per row.  TILED: scales go to the 128x4 tile layout with outer = row (activations);
+// otherwise row-major [rows][K/16] (checkpoint weight layout).
+template <typename T, int MODE, bool TILED>
+__global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
+                                                             uint8_t* __restrict__ scales, float* __restrict__ row_scales,
+                                                             uint32_t rows, uint32_t k, float input_scale) {
+    __shared__ float red[8];
+    const uint32_t row = blockIdx.x;
+    const T* src = input + static_cast<size_t>(row) * k;
+    const uint32_t blocks = (k + 15) / 16;
+    const bool vec_ok = (k % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0);
+    float g = input_scale;
+    if (MODE == kPerRow) {
+        float amax = 0.0f;
+        for (uint32_t b = threadIdx.x; b < blocks; b += blockDim.x) {
+            float v[16];
+            uint32_t valid;
+            load_block(src, k, b, vec_ok, v, valid);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (isfinite(v[i])) amax = fmaxf(amax, fabsf(v[i]));
+        }
+        amax = block_max(amax, red);
+        g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+        if (threadIdx.x == 0) row_scales[row] = g;
+    }
+    uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
+    for (uint32_t b = threadIdx.x; b < blocks; b += blockDim.x) {
+        float v[16];
+        uint32_t valid;
+        load_block(src, k, b, vec_ok, v, valid);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __fdiv_rn(v[i], g);
+        uint2 bytes;
+        uint8_t sc = quantize_block16(v, valid, &bytes);
+        if (valid == 16 && (k % 16 == 0)) {
+            *reinterpret_cast<uint2*>(prow + b * 8) = bytes;
+        } else {
+            // ragged tail: element (row*k + i) lives in nibble (row*k + i) & 1 of byte (row*k + i) / 2
+            uint32_t w[2] = {bytes.x, bytes.y};
+            for (uint32_t i = 0; i < valid; ++i) {
+                size_t flat = static_cast<size_t>(row) * k + b * 16 + i;
+                uint32_t code = (w[i / 8] >> ((i % 8) * 4)) & 0xfu;
+                uint8_t* dst = packed + flat / 2;
+                if (flat & 1) *dst = static_cast<uint8_t>((*dst & 0x0f) | (code << 4));
+                else *dst = static_cast<uint8_t>((*dst & 0xf0) | code);
+            }
+        }
+        if (TILED) scales[tiled_scale_offset(row, b, k)] = sc;
+        else scales[static_cast<size_t>(row) * blocks + b] = sc;
+    }
+}
+
+// Per-token dynamic FP8: s = amax / 448 (1 when 0), q = e4m3(x / s)
+// (crates/eider-cuda/native/non_gemm.cu:9952-9974, 10028-10066).
+template <typename T, bool DYNAMIC>
+__global__ void __launch_bounds__(256) quantize_fp8_kernel(const T* __restrict__ input, uint8_t* __restrict__ q,
+                                                           float* __restrict__ row_scale, uint32_t rows, uint32_t cols,
+                                                           float static_scale) {
+    __shared__ float red[8];
+    const uint32_t row = blockIdx.x;
+    const T* src = input + static_cast<size_t>(row) * cols;
+    float s = static_scale;
+    if (DYNAMIC) {
+        float amax = 0.0f;
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+            float v = Loader<T>::load1(src + i);
+            if (isfinite(v)) amax = fmaxf(amax, fabsf(v));
+        }
+        amax = block_max(amax, red);
+        s = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+        if (threadIdx.x == 0) row_scale[row] = s;
+    }
+    uint8_t* dst = q + static_cast<size_t>(row) * cols;
+    const bool vec_ok = (cols % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
+    if (vec_ok) {
+        for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+            float v[16];
+            Loader<T>::load16(src + b * 16, v);
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[j] |= static_cast<uint32_t>(e4m3_satfinite(__fdiv_rn(v[4 * j + i], s))) << (8 * i);
+            }
+            *reinterpret_cast<uint4*>(dst + b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) dst[i] = e4m3_satfinite(__fdiv_rn(Loader<T>::load1(src + i), s));
+    }
+}
+
+// Row-major [N][K/16] scale bytes -> 128x4 tiled layout (crates/eider-format/src/modelopt.rs:1148-1161).
+__global__ void scales_to_tiled_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint32_t rows,
+                                       uint32_t k) {
+    const uint32_t blocks = k / 16;
+    size_t total = static_cast<size_t>(rows) * blocks;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        uint32_t r = static_cast<uint32_t>(i / blocks), b = static_cast<uint32_t>(i % blocks);
+        dst[tiled_scale_offset(r, b, k)] = src[i];
+    }
+}
+
+bool bad_scale(float s) { return !(s > 0.0f) || !isfinite(s); }
+
+}  // namespace
+
+}  // namespace eider
+
+using namespace eider;
+
+extern "C" {
+
+cudaError_t infer_quantize_nvfp4_col_major_f32_on_stream(const float* input, uint8_t* packed, uint8_t* scales,
+                                                         uint32_t rows, uint32_t cols, float input_scale,
+                                                         cudaStream_t stream) {
+    if (!input || !packed || !scales || rows == 0 || cols == 0 || bad_scale(input_scale)) return cudaErrorInvalidValue;
+    quantize_nvfp4_kernel<float, kStatic, true><<<cols, 256, 0, stream>>>(input, packed, scales, nullptr, cols, rows,
+                                                                          input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_quantize_nvfp4_col_major_f32(const float* input, uint8_t* packed, uint8_t* scales, uint32_t rows,
+                                               uint32_t cols, float input_scale) {
+    return infer_quantize_nvfp4_col_major_f32_on_stream(input, packed, scales, rows, cols, input_scale, nullptr);
+}
+
+cudaError_t eider_b200_quantize_nvfp4_bf16_on_stream(const uint16_t* input, uint8_t* packed, uint8_t* scales,
+                                                     uint32_t rows, uint32_t cols, float input_scale,
+                                                     cudaStream_t stream) {
+    if (!input || !packed || !scales || rows == 0 || cols == 0 || bad_scale(input_scale)) return cudaErrorInvalidValue;
+    quantize_nvfp4_kernel<uint16_t, kStatic, true><<<cols, 256, 0, stream>>>(input, packed, scales, nullptr, cols, rows,
+                                                                             input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t eider_b200_quantize_nvfp4_rowscale_on_stream(const void* input, int input_is_bf16, uint8_t* packed,
+                                                         uint8_t* scales, float* row_scales, uint32_t rows,
+                                                         uint32_t cols, cudaStream_t stream) {
+    if (!input || !packed || !scales || !row_scales || rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    if (input_is_bf16)
+        quantize_nvfp4_kernel<uint16_t, kPerRow, true><<<cols, 256, 0, stream>>>(
+            static_cast<const uint16_t*>(input), packed, scales, row_scales, cols, rows, 1.0f);
+    else
+        quantize_nvfp4_kernel<float, kPerRow, true><<<cols, 256, 0, stream>>>(static_cast<const float*>(input), packed,
+                                                                            scales, row_scales, cols, rows, 1.0f);
+    return cudaGetLastError();
+}
+
+cudaError_t eider_b200_quantize_nvfp4_weight_on_stream(const void* weight, int input_is_bf16, uint8_t* packed,
+                                                       uint8_t* scales_row_major, uint32_t out_features,
+                                                       uint32_t in_features, float global_scale, cudaStream_t stream) {
+    if (!weight || !packed || !scales_row_major || out_features == 0 || in_features == 0 || in_features % 16 != 0 ||
+        bad_scale(global_scale))
+        return cudaErrorInvalidValue;
+    if (input_is_bf16)
+        quantize_nvfp4_kernel<uint16_t, kStatic, false><<<out_features, 256, 0, stream>>>(
+            static_cast<const uint16_t*>(weight), packed, scales_row_major, nullptr, out_features, in_features,
+            global_scale);
+    else
+        quantize_nvfp4_kernel<float, kStatic, false><<<out_features, 256, 0, stream>>>(
+            static_cast<const float*>(weight), packed, scales_row_major, nullptr, out_features, in_features,
+            global_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row_major, uint8_t* scales_tiled,
+                                                       uint32_t out_features, uint32_t in_features,
+                                                       cudaStream_t stream) {
+    if (!scales_row_major || !scales_tiled || out_features == 0 || in_features == 0 || in_features % 16 != 0)
+        return cudaErrorInvalidValue;
+    cudaError_t st = cudaMemsetAsync(scales_tiled, 0, scale_layout_len(out_features, in_features), stream);
+    if (st != cudaSuccess) return st;
+    size_t total = static_cast<size_t>(out_features) * (in_features / 16);
+    uint32_t grid = static_cast<uint32_t>((total + 255) / 256);
+    if (grid > 148 * 16) grid = 148 * 16;
+    scales_to_tiled_kernel<<<grid, 256, 0, stream>>>(scales_row_major, scales_tiled, out_features, in_features);
+    return cudaGetLastError();
+}
+
+size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner) { return scale_layout_len(outer, inner); }
+
+cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(const float* input, uint8_t* quantized_input,
+                                                                float* input_scale, uint32_t rows, uint32_t cols,
+                                                                cudaStream_t stream) {
+    if (!input || !quantized_input || !input_scale || rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    quantize_fp8_kernel<float, true><<<rows, 256, 0, stream>>>(input, quantized_input, input_scale, rows, cols, 1.0f);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_on_stream(const float* input, uint8_t* quantized_input,
+                                                          float* input_scale, uint32_t cols, cudaStream_t stream) {
+    return infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(input, quantized_input, input_scale, 1, cols, stream);
+}
+
+cudaError_t eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(const uint16_t* input, uint8_t* quantized_input,
+                                                                      float* input_scale, uint32_t rows, uint32_t cols,
+                                                                      cudaStream_t stream) {
+    if (!input || !quantized_input || !input_scale || rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    quantize_fp8_kernel<uint16_t, true><<<rows, 256, 0, stream>>>(input, quantized_input, input_scale, rows, cols, 1.0f);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_quantize_fp8_e4m3_f32_on_stream(const float* input, uint8_t* output, uint32_t len, float input_scale,
+                                                  cudaStream_t stream) {
+    if (!input || !output || len == 0 || bad_scale(input_scale)) return cudaErrorInvalidValue;
+    // one logical row split over CTAs of 4096 elements keeps 128-bit accesses aligned
+    const uint32_t chunk = 4096;
+    uint32_t full = len / chunk;
+    if (full)
+        quantize_fp8_kernel<float, false><<<full, 256, 0, stream>>>(input, output, nullptr, full, chunk, input_scale);
+    if (len % chunk)
+        quantize_fp8_kernel<float, false><<<1, 256, 0, stream>>>(input + static_cast<size_t>(full) * chunk,
+                                                                 output + static_cast<size_t>(full) * chunk, nullptr, 1,
+                                                                 len % chunk, input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t eider_b200_quantize_fp8_weight_on_stream(const void* weight, int input_is_bf16, uint8_t* q,
+                                                     float* channel_scale, uint32_t out_features, uint32_t in_features,
+                                                     cudaStream_t stream) {
+    if (!weight || !q || !channel_scale || out_features == 0 || in_features == 0) return cudaErrorInvalidValue;
+    if (input_is_bf16)
+        quantize_fp8_kernel<uint16_t, true><<<out_features, 256, 0, stream>>>(static_cast<const uint16_t*>(weight), q,
+                                                                            channel_scale, out_features, in_features, 1.0f);
+    else
+        quantize_fp8_kernel<float, true><<<out_features, 256, 0, stream>>>(static_cast<const float*>(weight), q,
+                                                                         channel_scale, out_features, in_features, 1.0f);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

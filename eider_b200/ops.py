@@ -1,0 +1,343 @@
+"""Host-side mirror of the reference's safe operator API for the quantized-linear path.
+
+Names follow crates/eider-cuda (Nvfp4Matrix, ModelOptCublasLtWeight -> ModelOptWeight,
+Fp4TnMatmulPlan, Fp8TnMatmulPlan, MoeSortedRoutes ...) so tests read like the reference's.  PyTorch
+only owns device memory and streams here; every computation goes through the C ABI in
+include/eider_b200.h.  Shape / format errors are raised on the host before any launch, as the
+reference's wrappers do (crates/eider-cuda/src/kernels/non_gemm.rs:5672-5703).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+
+class ShapeError(ValueError):
+    """crates/eider-cuda/src/error.rs Error::Shape."""
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype, label: str) -> None:
+    if not t.is_cuda or not t.is_contiguous() or t.dtype != dtype:
+        raise ShapeError(f"{label}: expected contiguous CUDA tensor of {dtype}, got {t.dtype} cuda={t.is_cuda}")
+
+
+def scale_layout_len(outer: int, inner: int) -> int:
+    """ue4m3_scale_layout_len (crates/eider-cuda/src/format.rs:194-198)."""
+    return int(_lib.load().eider_b200_nvfp4_scale_layout_len(outer, inner))
+
+
+@dataclass
+class Nvfp4Matrix:
+    """Device NVFP4 matrix: packed E2M1 [rows, K/2] + tiled UE4M3 scales (crates/eider-cuda/src/matrix.rs:43-331)."""
+    packed: torch.Tensor
+    scales: torch.Tensor
+    rows: int
+    k: int
+    row_scales: torch.Tensor | None = None  # per-row global scale when quantized on the fly
+
+    @staticmethod
+    def zeros(rows: int, k: int, device="cuda", row_scales: bool = False) -> "Nvfp4Matrix":
+        if k % 16 != 0:
+            raise ShapeError(f"NVFP4 needs K % 16 == 0, got {k}")
+        return Nvfp4Matrix(
+            torch.zeros(rows, k // 2, dtype=torch.uint8, device=device),
+            torch.zeros(scale_layout_len(rows, k), dtype=torch.uint8, device=device),
+            rows, k,
+            torch.zeros(rows, dtype=torch.float32, device=device) if row_scales else None)
+
+
+# ---- NVFP4 activation quantize ------------------------------------------------------------------
+def quantize_nvfp4(x: torch.Tensor, input_scale: float = 1.0, out: Nvfp4Matrix | None = None) -> Nvfp4Matrix:
+    """infer_quantize_nvfp4_col_major_f32_on_stream for x [tokens, K] (f32 or bf16), static scale."""
+    lib = _lib.load()
+    tokens, k = x.shape
+    if not (input_scale > 0.0) or input_scale != input_scale or input_scale == float("inf"):
+        raise ShapeError(f"input_scale must be positive and finite, got {input_scale}")
+    out = out or Nvfp4Matrix.zeros(tokens, k, x.device)
+    if x.dtype == torch.float32:
+        _need(x, torch.float32, "activation")
+        check("infer_quantize_nvfp4_col_major_f32_on_stream",
+              lib.infer_quantize_nvfp4_col_major_f32_on_stream(x.data_ptr(), out.packed.data_ptr(), out.scales.data_ptr(),
+                                                               k, tokens, input_scale, _stream()))
+    else:
+        _need(x, torch.bfloat16, "activation")
+        check("eider_b200_quantize_nvfp4_bf16_on_stream",
+              lib.eider_b200_quantize_nvfp4_bf16_on_stream(x.data_ptr(), out.packed.data_ptr(), out.scales.data_ptr(), k,
+                                                           tokens, input_scale, _stream()))
+    return out
+
+
+def quantize_nvfp4_rowscale(x: torch.Tensor, out: Nvfp4Matrix | None = None) -> Nvfp4Matrix:
+    """Per-token global scale g = amax/2688, then the reference quantizer with input_scale = g."""
+    lib = _lib.load()
+    tokens, k = x.shape
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ShapeError("activation must be f32 or bf16")
+    _need(x, x.dtype, "activation")
+    out = out or Nvfp4Matrix.zeros(tokens, k, x.device, row_scales=True)
+    check("eider_b200_quantize_nvfp4_rowscale_on_stream",
+          lib.eider_b200_quantize_nvfp4_rowscale_on_stream(x.data_ptr(), int(x.dtype == torch.bfloat16),
+                                                           out.packed.data_ptr(), out.scales.data_ptr(),
+                                                           out.row_scales.data_ptr(), k, tokens, _stream()))
+    return out
+
+
+# ---- weights ------------------------------------------------------------------------------------
+@dataclass
+class ModelOptWeight:
+    """Device NVFP4 weight (crates/eider-cuda/src/modelopt_device.rs:18-22,109-200): the checkpoint's packed
+    bytes as they are, row-major scales for the CUDA-core GEMV and tile-repacked scales for the tensor-core
+    kernels; matmul_alpha = weight_scale_2 * input_scale."""
+    packed: torch.Tensor            # [N, K/2] u8
+    scales_row_major: torch.Tensor  # [N, K/16] u8 (checkpoint layout)
+    scales_tiled: torch.Tensor      # tiled layout, outer = N
+    weight_scale_2: float
+    input_scale: float
+    out_features: int
+    in_features: int
+
+    @property
+    def matmul_alpha(self) -> float:
+        return self.weight_scale_2 * self.input_scale
+
+    @staticmethod
+    def from_checkpoint(packed: torch.Tensor, scales_row_major: torch.Tensor, weight_scale_2: float,
+                        input_scale: float = 1.0) -> "ModelOptWeight":
+        """Upload-time preparation from ModelOptNvfp4Linear bytes (crates/eider-format/src/modelopt.rs:11-26)."""
+        lib = _lib.load()
+        n, kh = packed.shape
+        k = kh * 2
+        if scales_row_major.shape != (n, k // 16):
+            raise ShapeError(f"weight_scale must be [{n}, {k // 16}], got {tuple(scales_row_major.shape)}")
+        _need(packed, torch.uint8, "weight")
+        _need(scales_row_major, torch.uint8, "weight_scale")
+        tiled = torch.empty(scale_layout_len(n, k), dtype=torch.uint8, device=packed.device)
+        check("eider_b200_nvfp4_scales_to_tiled_on_stream",
+              lib.eider_b200_nvfp4_scales_to_tiled_on_stream(scales_row_major.data_ptr(), tiled.data_ptr(), n, k, _stream()))
+        return ModelOptWeight(packed, scales_row_major, tiled, float(weight_scale_2), float(input_scale), n, k)
+
+    @staticmethod
+    def quantize(weight: torch.Tensor, global_scale: float | None = None, input_scale: float = 1.0) -> "ModelOptWeight":
+        """Quantize a dense [N, K] f32/bf16 weight the ModelOpt way: g = amax/(6*448) unless given."""
+        lib = _lib.load()
+        n, k = weight.shape
+        if k % 16 != 0:
+            raise ShapeError(f"NVFP4 needs K % 16 == 0, got {k}")
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise ShapeError("weight must be f32 or bf16")
+        _need(weight, weight.dtype, "weight")
+        if global_scale is None:
+            amax = weight.abs().max().float()
+            # one IEEE f32 divide by 6 * 448, 1 for an all-zero weight
+            global_scale = float((amax / 2688.0).item()) if float(amax.item()) > 0 else 1.0
+        packed = torch.empty(n, k // 2, dtype=torch.uint8, device=weight.device)
+        scales = torch.empty(n, k // 16, dtype=torch.uint8, device=weight.device)
+        check("eider_b200_quantize_nvfp4_weight_on_stream",
+              lib.eider_b200_quantize_nvfp4_weight_on_stream(weight.data_ptr(), int(weight.dtype == torch.bfloat16),
+                                                             packed.data_ptr(), scales.data_ptr(), n, k, global_scale,
+                                                             _stream()))
+        return ModelOptWeight.from_checkpoint(packed, scales, global_scale, input_scale)
+
+
+# ---- dense GEMM plans -------------------------------------------------------------------------------
+class Fp4TnMatmulPlan:
+    """Dense W4A4 GEMM plan (crates/eider-cuda/src/cublaslt/fp4_tn.rs:264-796): D = alpha * X . W^T + beta * C with
+    fp32 accumulation, BF16 or F32 output [tokens, out_features]."""
+
+    def __init__(self, tokens: int, out_features: int, in_features: int):
+        lib = _lib.load()
+        if not lib.eider_b200_nvfp4_gemm_tn_supported(tokens, out_features, in_features):
+            raise ShapeError(f"unsupported NVFP4 GEMM shape m={tokens} n={out_features} k={in_features}")
+        self._lib = lib
+        self.m, self.n, self.k = tokens, out_features, in_features
+        self._plan = lib.eider_b200_nvfp4_gemm_tn_create(tokens, out_features, in_features)
+        if not self._plan:
+            raise RuntimeError("eider_b200_nvfp4_gemm_tn_create failed")
+
+    def set_block_n(self, block_n: int) -> None:
+        if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
+            raise ShapeError(f"block_n must be 64, 128 or 256, got {block_n}")
+
+    def run(self, x: Nvfp4Matrix, w: ModelOptWeight, out: torch.Tensor | None = None, alpha: float | None = None,
+            beta: float = 0.0, c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        if x.rows != self.m or x.k != self.k or w.out_features != self.n or w.in_features != self.k:
+            raise ShapeError("operand shapes do not match the plan")
+        if out is None:
+            out = torch.empty(self.m, self.n, dtype=out_dtype, device=x.packed.device)
+        if out.dtype not in (torch.bfloat16, torch.float32) or out.shape != (self.m, self.n) or not out.is_contiguous():
+            raise ShapeError("output must be contiguous [tokens, out_features] bf16 or f32")
+        if beta != 0.0 and c is None:
+            c = out
+        a = w.matmul_alpha if alpha is None else alpha
+        check("eider_b200_nvfp4_gemm_tn_on_stream",
+              self._lib.eider_b200_nvfp4_gemm_tn_on_stream(self._plan, x.packed.data_ptr(), x.scales.data_ptr(),
+                                                           w.packed.data_ptr(), w.scales_tiled.data_ptr(), _ptr(c),
+                                                           out.data_ptr(), a, beta, _ptr(x.row_scales),
+                                                           int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def status(self) -> int:
+        v = C.c_uint32(0)
+        check("eider_b200_gemm_plan_status", self._lib.eider_b200_gemm_plan_status(self._plan, C.byref(v)))
+        return v.value
+
+    def close(self) -> None:
+        if self._plan:
+            self._lib.eider_b200_nvfp4_gemm_tn_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Fp8TnMatmulPlan:
+    """Dense FP8 E4M3 GEMM plan (crates/eider-cuda/src/cublaslt/fp8_tn.rs:13-292) with the per-token and
+    per-channel scaling fused into the epilogue."""
+
+    def __init__(self, tokens: int, out_features: int, in_features: int):
+        lib = _lib.load()
+        if not lib.eider_b200_fp8_gemm_tn_supported(tokens, out_features, in_features):
+            raise ShapeError(f"unsupported FP8 GEMM shape m={tokens} n={out_features} k={in_features}")
+        self._lib = lib
+        self.m, self.n, self.k = tokens, out_features, in_features
+        self._plan = lib.eider_b200_fp8_gemm_tn_create(tokens, out_features, in_features)
+        if not self._plan:
+            raise RuntimeError("eider_b200_fp8_gemm_tn_create failed")
+
+    def set_block_n(self, block_n: int) -> None:
+        if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
+            raise ShapeError(f"block_n must be 64, 128 or 256, got {block_n}")
+
+    def run(self, xq: torch.Tensor, wq: torch.Tensor, token_scale: torch.Tensor | None,
+            channel_scale: torch.Tensor | None, out: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0,
+            c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        if xq.shape != (self.m, self.k) or wq.shape != (self.n, self.k):
+            raise ShapeError("operand shapes do not match the plan")
+        _need(xq, torch.uint8, "xq")
+        _need(wq, torch.uint8, "wq")
+        if out is None:
+            out = torch.empty(self.m, self.n, dtype=out_dtype, device=xq.device)
+        if beta != 0.0 and c is None:
+            c = out
+        check("eider_b200_fp8_gemm_tn_on_stream",
+              self._lib.eider_b200_fp8_gemm_tn_on_stream(self._plan, xq.data_ptr(), wq.data_ptr(), _ptr(c), out.data_ptr(),
+                                                         alpha, beta, _ptr(token_scale), _ptr(channel_scale),
+                                                         int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def status(self) -> int:
+        v = C.c_uint32(0)
+        check("eider_b200_gemm_plan_status", self._lib.eider_b200_gemm_plan_status(self._plan, C.byref(v)))
+        return v.value
+
+    def close(self) -> None:
+        if self._plan:
+            self._lib.eider_b200_fp8_gemm_tn_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- FP8 quantizers ---------------------------------------------------------------------------------
+def quantize_fp8_dynamic(x: torch.Tensor):
+    """Per-token dynamic E4M3: returns (codes [rows, cols] u8, scales [rows] f32)."""
+    lib = _lib.load()
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    if x.dtype == torch.float32:
+        _need(x, torch.float32, "activation")
+        check("infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream",
+              lib.infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, cols,
+                                                                      _stream()))
+    else:
+        _need(x, torch.bfloat16, "activation")
+        check("eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream",
+              lib.eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows,
+                                                                            cols, _stream()))
+    return q, s
+
+
+def quantize_fp8_static(x: torch.Tensor, input_scale: float) -> torch.Tensor:
+    lib = _lib.load()
+    _need(x, torch.float32, "activation")
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    check("infer_quantize_fp8_e4m3_f32_on_stream",
+          lib.infer_quantize_fp8_e4m3_f32_on_stream(x.data_ptr(), q.data_ptr(), x.numel(), input_scale, _stream()))
+    return q
+
+
+def quantize_fp8_weight(w: torch.Tensor):
+    """Per-output-channel E4M3 weight: returns (codes [N, K] u8, channel scales [N] f32)."""
+    lib = _lib.load()
+    n, k = w.shape
+    if w.dtype not in (torch.float32, torch.bfloat16):
+        raise ShapeError("weight must be f32 or bf16")
+    _need(w, w.dtype, "weight")
+    q = torch.empty(n, k, dtype=torch.uint8, device=w.device)
+    s = torch.empty(n, dtype=torch.float32, device=w.device)
+    check("eider_b200_quantize_fp8_weight_on_stream",
+          lib.eider_b200_quantize_fp8_weight_on_stream(w.data_ptr(), int(w.dtype == torch.bfloat16), q.data_ptr(),
+                                                       s.data_ptr(), n, k, _stream()))
+    return q, s
+
+
+# ---- CUDA-core decode kernels -----------------------------------------------------------------------
+def nvfp4_w4a16_matvec(x: torch.Tensor, w: ModelOptWeight, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[b] = weight_scale_2 * W . x[b] with exact f32 products (infer_nvfp4_w4a16_matvec_f32_*).
+    x [batch, K] f32 -> f32 out, or bf16 -> bf16 out."""
+    lib = _lib.load()
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    b, k = x.shape
+    if k != w.in_features:
+        raise ShapeError(f"in_features mismatch: {k} vs {w.in_features}")
+    if out is None:
+        out = torch.empty(b, w.out_features, dtype=x.dtype, device=x.device)
+    if x.dtype == torch.float32:
+        _need(x, torch.float32, "input")
+        check("infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream",
+              lib.infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream(
+                  x.data_ptr(), w.packed.data_ptr(), w.scales_row_major.data_ptr(), out.data_ptr(), b, w.out_features,
+                  k, w.weight_scale_2, 8, _stream()))
+    else:
+        _need(x, torch.bfloat16, "input")
+        check("eider_b200_nvfp4_w4a16_matvec_bf16_on_stream",
+              lib.eider_b200_nvfp4_w4a16_matvec_bf16_on_stream(
+                  x.data_ptr(), w.packed.data_ptr(), w.scales_row_major.data_ptr(), out.data_ptr(), b, w.out_features,
+                  k, w.weight_scale_2, _stream()))
+    return out
+
+
+def fp8_linear_prequantized_simt(xq: torch.Tensor, s_x: torch.Tensor, wq: torch.Tensor,
+                                 channel_scale: torch.Tensor | None, weight_scale: float = 1.0,
+                                 out_dtype=torch.float32) -> torch.Tensor:
+    lib = _lib.load()
+    m, k = xq.shape
+    n = wq.shape[0]
+    out = torch.empty(m, n, dtype=out_dtype, device=xq.device)
+    check("eider_b200_fp8_linear_prequantized_simt_on_stream",
+          lib.eider_b200_fp8_linear_prequantized_simt_on_stream(xq.data_ptr(), s_x.data_ptr(), wq.data_ptr(),
+                                                                _ptr(channel_scale), weight_scale, out.data_ptr(),
+                                                                int(out_dtype == torch.bfloat16), m, n, k, _stream()))
+    return out

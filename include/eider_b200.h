@@ -1,0 +1,145 @@
+/*
+ * eider_b200 — C ABI of the B200 (sm_100a) quantized-linear path.
+ *
+ * This is the boundary the reference binds in crates/eider-cuda/src/ffi.rs: plain C scalars, raw
+ * device pointers, a trailing cudaStream_t, cudaError_t results (0 = success).  Conventions kept from
+ * the reference (crates/eider-cuda/native/README.md:45-50):
+ *   - the caller owns every buffer; pointers are borrowed for the duration of the enqueued work;
+ *   - nothing synchronises the device or uses the default stream implicitly;
+ *   - null pointers, zero extents and unsupported divisibility return cudaErrorInvalidValue before
+ *     any launch; `*_supported` return 1/0; `*_create` return NULL on failure.
+ * Symbols named infer_* keep the reference's name and argument list; symbols named eider_b200_* are
+ * new or supersede a closed-library call (cuBLASLt / CUTLASS) of the reference, cited per entry.
+ *
+ * Shapes: tokens = rows of X, in_features = K (reduction), out_features = rows of W.
+ * NVFP4 images: values are E2M1 codes packed two per byte (even element in the low nibble),
+ * row-major [rows][K/2]; scales are UE4M3 bytes, one per 16 elements, either row-major
+ * [rows][K/16] (checkpoint layout) or "tiled" = the 128-row x 4-block layout of
+ * crates/eider-cuda/src/format.rs:194-218.
+ */
+#ifndef EIDER_B200_H
+#define EIDER_B200_H
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EIDER_B200_API __attribute__((visibility("default")))
+
+/* ---- NVFP4 activation / weight quantizers --------------------------------------------------- */
+
+/* crates/eider-cuda/src/ffi.rs:2363 and :2372 (kernel crates/eider-cuda/native/non_gemm.cu:106-191).
+ * input: f32 [cols tokens][rows = K]; packed: [cols][rows/2]; scales: tiled, outer = token. */
+EIDER_B200_API cudaError_t infer_quantize_nvfp4_col_major_f32(const float* input, uint8_t* packed, uint8_t* scales,
+                                                              uint32_t rows, uint32_t cols, float input_scale);
+EIDER_B200_API cudaError_t infer_quantize_nvfp4_col_major_f32_on_stream(const float* input, uint8_t* packed,
+                                                                        uint8_t* scales, uint32_t rows, uint32_t cols,
+                                                                        float input_scale, cudaStream_t stream);
+/* Same operator for bf16 activations (the reference widens bf16 to f32 first, non_gemm.cu:2577). */
+EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_bf16_on_stream(const uint16_t* input, uint8_t* packed,
+                                                                    uint8_t* scales, uint32_t rows, uint32_t cols,
+                                                                    float input_scale, cudaStream_t stream);
+/* On-the-fly quantizer of the prefill GEMM: per token g = amax / 2688 (1 for an all-zero row), then the
+ * operator above with input_scale = g; g is written to row_scales[cols].  Supersedes the static-scale
+ * call of crates/eider-cuda/src/modelopt_device.rs:178-194 for inputs without a calibrated scale. */
+EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_rowscale_on_stream(const void* input, int input_is_bf16,
+                                                                        uint8_t* packed, uint8_t* scales,
+                                                                        float* row_scales, uint32_t rows, uint32_t cols,
+                                                                        cudaStream_t stream);
+/* Device twin of ModelOptNvfp4Linear::quantize_values (crates/eider-format/src/modelopt.rs:649-716) with a
+ * per-tensor global scale: weight [out][in] f32 or bf16 -> packed [out][in/2] + row-major scales [out][in/16]. */
+EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_weight_on_stream(const void* weight, int input_is_bf16,
+                                                                      uint8_t* packed, uint8_t* scales_row_major,
+                                                                      uint32_t out_features, uint32_t in_features,
+                                                                      float global_scale, cudaStream_t stream);
+/* Device twin of modelopt_scales_to_cublaslt (crates/eider-format/src/modelopt.rs:1148-1161). */
+EIDER_B200_API cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row_major,
+                                                                      uint8_t* scales_tiled, uint32_t out_features,
+                                                                      uint32_t in_features, cudaStream_t stream);
+/* ue4m3_scale_layout_len, crates/eider-cuda/src/format.rs:194-198. */
+EIDER_B200_API size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner);
+
+/* ---- FP8 E4M3 quantizers -------------------------------------------------------------------- */
+
+/* crates/eider-cuda/src/ffi.rs:3198 and :3206 (kernels non_gemm.cu:9952-9974, 10028-10066). */
+EIDER_B200_API cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_on_stream(const float* input, uint8_t* quantized_input,
+                                                                         float* input_scale, uint32_t cols,
+                                                                         cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(const float* input,
+                                                                               uint8_t* quantized_input,
+                                                                               float* input_scale, uint32_t rows,
+                                                                               uint32_t cols, cudaStream_t stream);
+EIDER_B200_API cudaError_t eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(const uint16_t* input,
+                                                                                     uint8_t* quantized_input,
+                                                                                     float* input_scale, uint32_t rows,
+                                                                                     uint32_t cols, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3278. */
+EIDER_B200_API cudaError_t infer_quantize_fp8_e4m3_f32_on_stream(const float* input, uint8_t* output, uint32_t len,
+                                                                 float input_scale, cudaStream_t stream);
+/* Per-output-channel weight quantizer, s_w[n] = amax_n / 448 (precedent crates/infer/src/qwen3/qwen36.rs:2047-2057). */
+EIDER_B200_API cudaError_t eider_b200_quantize_fp8_weight_on_stream(const void* weight, int input_is_bf16, uint8_t* q,
+                                                                    float* channel_scale, uint32_t out_features,
+                                                                    uint32_t in_features, cudaStream_t stream);
+
+/* ---- decode GEMV on CUDA cores (exact f32 semantics of the reference) ------------------------ */
+
+/* crates/eider-cuda/src/ffi.rs:3285 (kernels non_gemm.cu:13147-13256): row-major checkpoint scales. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_matvec_f32_on_stream(const float* input, const uint8_t* packed_weight,
+                                                                  const uint8_t* weight_scale, float* output,
+                                                                  uint32_t out_features, uint32_t in_features,
+                                                                  float weight_scale_2, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3308. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream(
+    const float* input, const uint8_t* packed_weight, const uint8_t* weight_scale, float* output, uint32_t batch_size,
+    uint32_t out_features, uint32_t in_features, float weight_scale_2, uint32_t warps_per_block, cudaStream_t stream);
+/* bf16 in / bf16 out form of the same operator. */
+EIDER_B200_API cudaError_t eider_b200_nvfp4_w4a16_matvec_bf16_on_stream(const uint16_t* input,
+                                                                        const uint8_t* packed_weight,
+                                                                        const uint8_t* weight_scale, uint16_t* output,
+                                                                        uint32_t batch_size, uint32_t out_features,
+                                                                        uint32_t in_features, float weight_scale_2,
+                                                                        cudaStream_t stream);
+/* FP8 W8A8 for a few pre-quantized tokens, y = (sum xq*w) * s_x[t] * s_w[n]
+ * (crates/eider-cuda/src/ffi.rs:3151, kernel non_gemm.cu:9976-10011).  channel_scale may be NULL
+ * (then weight_scale is the per-tensor scale). */
+EIDER_B200_API cudaError_t eider_b200_fp8_linear_prequantized_simt_on_stream(
+    const uint8_t* xq, const float* input_scales, const uint8_t* weight, const float* channel_scale, float weight_scale,
+    void* output, int output_is_bf16, uint32_t tokens, uint32_t out_features, uint32_t in_features, cudaStream_t stream);
+
+/* ---- dense GEMM on tcgen05 -------------------------------------------------------------------- */
+
+/* Supersedes cublasLtMatmul behind Fp4TnMatmulPlan (crates/eider-cuda/src/cublaslt/fp4_tn.rs:264-796,
+ * crates/eider-cuda/src/ffi.rs:4196).  D[tokens][out] = alpha * token_scale[t] * (X . W^T) + beta * C.
+ * m = tokens, n = out features, k = in features (k % 32 == 0).  x_scales / w_scales are tiled. */
+EIDER_B200_API int eider_b200_nvfp4_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k);
+EIDER_B200_API void* eider_b200_nvfp4_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k);
+EIDER_B200_API void eider_b200_nvfp4_gemm_tn_destroy(void* plan);
+EIDER_B200_API cudaError_t eider_b200_nvfp4_gemm_tn_on_stream(void* plan, const uint8_t* x_values,
+                                                              const uint8_t* x_scales, const uint8_t* w_values,
+                                                              const uint8_t* w_scales, const void* c, void* d,
+                                                              float alpha, float beta, const float* token_scale,
+                                                              int out_is_bf16, cudaStream_t stream);
+/* Supersedes cublasLtMatmul behind Fp8TnMatmulPlan (crates/eider-cuda/src/cublaslt/fp8_tn.rs:13-292) and the
+ * separate scaling pass infer_scale_channel_f32_device_row_scalar (crates/eider-cuda/src/ffi.rs:3231):
+ * D = alpha * token_scale[t] * channel_scale[n] * (Xq . Wq^T) + beta * C. */
+EIDER_B200_API int eider_b200_fp8_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k);
+EIDER_B200_API void* eider_b200_fp8_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k);
+EIDER_B200_API void eider_b200_fp8_gemm_tn_destroy(void* plan);
+EIDER_B200_API cudaError_t eider_b200_fp8_gemm_tn_on_stream(void* plan, const uint8_t* x_values, const uint8_t* w_values,
+                                                            const void* c, void* d, float alpha, float beta,
+                                                            const float* token_scale, const float* channel_scale,
+                                                            int out_is_bf16, cudaStream_t stream);
+/* Tile-shape override (64, 128 or 256 weight rows per tile) and the kernel status word of a plan
+ * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
+EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
+EIDER_B200_API cudaError_t eider_b200_gemm_plan_status(void* plan, uint32_t* host_status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* EIDER_B200_H */

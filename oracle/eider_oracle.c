@@ -366,23 +366,36 @@ ORACLE_API void oracle_nvfp4_linear_host(const float* x, size_t m, const uint8_t
 
 /* ------------------------------------------------------------------------ FP8 */
 
+/* __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3) as the reference's device quantizers call
+ * it (crates/eider-cuda/native/non_gemm.cu:9971-9972): NaN -> 0x7f, |v| > 448 (and +-inf)
+ * saturate to +-448, -0 keeps its sign, finite values round to nearest even. */
+ORACLE_API uint8_t oracle_e4m3_satfinite(float v) {
+    if (isnan(v)) return 0x7f;
+    uint8_t sign = signbit(v) ? 0x80 : 0;
+    float a = fabsf(v);
+    if (isinf(a)) return sign | 0x7e;
+    return sign | oracle_ue4m3_code(a);
+}
+
 /* Per-token dynamic E4M3 quantize: crates/eider-cuda/native/non_gemm.cu:9952-9974,
- * 10028-10066.  s = amax/448 (1 when amax == 0); q = e4m3_satfinite(x / s). */
+ * 10028-10066.  s = amax/448 over the finite entries (1 when amax == 0);
+ * q = cvt_satfinite(x / s). */
 ORACLE_API void oracle_quantize_fp8_dynamic(const float* x, size_t rows, size_t cols, uint8_t* q,
                                             float* row_scale) {
     for (size_t r = 0; r < rows; ++r) {
         float amax = 0.0f;
-        for (size_t i = 0; i < cols; ++i) amax = fmaxf(amax, fabsf(x[r * cols + i]));
-        float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+        for (size_t i = 0; i < cols; ++i)
+            if (isfinite(x[r * cols + i])) amax = fmaxf(amax, fabsf(x[r * cols + i]));
+        float s = amax == 0.0f ? 1.0f : amax / 448.0f;
         row_scale[r] = s;
-        for (size_t i = 0; i < cols; ++i) q[r * cols + i] = oracle_e4m3_code(x[r * cols + i] / s);
+        for (size_t i = 0; i < cols; ++i) q[r * cols + i] = oracle_e4m3_satfinite(x[r * cols + i] / s);
     }
 }
 
-/* Static-scale form: crates/eider-cuda/native/non_gemm.cu:10487+ (q = e4m3(x / input_scale)). */
+/* Static-scale form: crates/eider-cuda/native/non_gemm.cu:10487+ (q = cvt_satfinite(x / input_scale)). */
 ORACLE_API void oracle_quantize_fp8_static(const float* x, size_t len, float input_scale,
                                            uint8_t* q) {
-    for (size_t i = 0; i < len; ++i) q[i] = oracle_e4m3_code(x[i] / input_scale);
+    for (size_t i = 0; i < len; ++i) q[i] = oracle_e4m3_satfinite(x[i] / input_scale);
 }
 
 typedef struct { const float* w; size_t k; uint8_t* q; float* cs; } f8w_ctx;
@@ -391,10 +404,11 @@ static void f8w_body(size_t b, size_t e, void* p) {
     size_t k = c->k;
     for (size_t r = b; r < e; ++r) {
         float amax = 0.0f;
-        for (size_t i = 0; i < k; ++i) amax = fmaxf(amax, fabsf(c->w[r * k + i]));
-        float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+        for (size_t i = 0; i < k; ++i)
+            if (isfinite(c->w[r * k + i])) amax = fmaxf(amax, fabsf(c->w[r * k + i]));
+        float s = amax == 0.0f ? 1.0f : amax / 448.0f;
         c->cs[r] = s;
-        for (size_t i = 0; i < k; ++i) c->q[r * k + i] = oracle_e4m3_code(c->w[r * k + i] / s);
+        for (size_t i = 0; i < k; ++i) c->q[r * k + i] = oracle_e4m3_satfinite(c->w[r * k + i] / s);
     }
 }
 

@@ -1,0 +1,152 @@
+"""Bit-exact parity of the CUDA quantizers against the CPU oracle (through the C ABI)."""
+import math
+
+import numpy as np
+import pytest
+
+from tests.test_oracle_golden import E2M1_VALUES
+from tests.util import require_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    require_cuda()
+    from eider_b200 import ops
+    return ops
+
+
+def _dev(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def test_reference_fixture_static_scale(ops, oracle):
+    # crates/eider-cuda/src/kernels/non_gemm.rs:19655-19683: K=96, 3 tokens, input_scale=.25
+    k, t = 96, 3
+    x = (((np.arange(k * t) % 29) - 14) / 32.0).astype(np.float32).reshape(t, k)
+    q = ops.quantize_nvfp4(_dev(x), 0.25)
+    packed, scales = oracle.quantize_nvfp4(x, 0.25)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+    assert np.array_equal(q.scales.cpu().numpy(), scales)
+
+
+@pytest.mark.parametrize("tokens,k", [(1, 16), (1, 5120), (7, 544), (130, 2048), (512, 5120)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_static_scale_random(ops, oracle, tokens, k, dtype):
+    import torch
+    rng = np.random.default_rng(tokens * 1000 + k)
+    x = rng.standard_normal((tokens, k)).astype(np.float32) * np.exp(rng.uniform(-3, 3, (tokens, 1))).astype(np.float32)
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    xd = _dev(x, torch.bfloat16 if dtype == "bf16" else None)
+    for scale in (1.0, 0.37):
+        q = ops.quantize_nvfp4(xd, scale)
+        packed, scales = oracle.quantize_nvfp4(x, scale)
+        assert np.array_equal(q.packed.cpu().numpy(), packed)
+        assert np.array_equal(q.scales.cpu().numpy(), scales)
+
+
+def test_edge_values(ops, oracle):
+    # every tie point / saturation / NaN / signed zero of the reference's E2M1 list, one per block position
+    vals = np.array(E2M1_VALUES, np.float32)
+    pad = (-len(vals)) % 16
+    x = np.concatenate([vals, np.zeros(pad, np.float32)]).reshape(1, -1)
+    # block scale 1.0: put a 6.0 in every block so the codes are the raw E2M1 roundings
+    x = x.reshape(-1, 16).copy()
+    x = np.concatenate([x[:, :15], np.full((x.shape[0], 1), 6.0, np.float32)], axis=1).reshape(1, -1)
+    q = ops.quantize_nvfp4(_dev(x), 1.0)
+    packed, scales = oracle.quantize_nvfp4(x, 1.0)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+    assert np.array_equal(q.scales.cpu().numpy(), scales)
+
+
+def test_all_zero_and_nonfinite_rows(ops, oracle):
+    x = np.zeros((3, 64), np.float32)
+    x[1, 5] = np.inf
+    x[1, 6] = 2.0
+    x[2, 17] = np.nan
+    x[2, 18] = -3.0
+    q = ops.quantize_nvfp4(_dev(x), 1.0)
+    packed, scales = oracle.quantize_nvfp4(x, 1.0)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+    assert np.array_equal(q.scales.cpu().numpy(), scales)
+    qr = ops.quantize_nvfp4_rowscale(_dev(x))
+    p2, s2, r2 = oracle.quantize_nvfp4_rowscale(x)
+    assert np.array_equal(qr.packed.cpu().numpy(), p2)
+    assert np.array_equal(qr.scales.cpu().numpy(), s2)
+    assert np.array_equal(qr.row_scales.cpu().numpy(), r2)
+
+
+@pytest.mark.parametrize("tokens,k", [(1, 5120), (33, 2048), (512, 5120)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_rowscale(ops, oracle, tokens, k, dtype):
+    import torch
+    rng = np.random.default_rng(7 + tokens)
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    q = ops.quantize_nvfp4_rowscale(_dev(x, torch.bfloat16 if dtype == "bf16" else None))
+    packed, scales, row = oracle.quantize_nvfp4_rowscale(x)
+    assert np.array_equal(q.row_scales.cpu().numpy(), row)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+    assert np.array_equal(q.scales.cpu().numpy(), scales)
+
+
+def test_weight_quantize_and_repack(ops, oracle):
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((384, 1024)) * 0.02).astype(np.float32)
+    wd = ops.ModelOptWeight.quantize(_dev(w))
+    packed, scales, g = oracle.quantize_weight(w)
+    assert wd.weight_scale_2 == float(g)
+    assert np.array_equal(wd.packed.cpu().numpy(), packed)
+    assert np.array_equal(wd.scales_row_major.cpu().numpy(), scales)
+    assert np.array_equal(wd.scales_tiled.cpu().numpy(), oracle.scales_to_tiled(scales, 384, 1024))
+
+
+def test_modelopt_k16_known_answer(ops):
+    # crates/eider-format/src/modelopt.rs:1281-1294
+    row = np.array([[0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]], np.float32)
+    wd = ops.ModelOptWeight.quantize(_dev(row), global_scale=1.0)
+    assert wd.scales_row_major.cpu().numpy().tolist() == [[0x38]]
+    assert wd.packed.cpu().numpy().tolist() == [[0x10, 0x32, 0x54, 0x76, 0x98, 0xBA, 0xDC, 0xFE]]
+
+
+def test_invalid_arguments(ops):
+    import torch
+    x = torch.zeros(2, 32, device="cuda")
+    with pytest.raises(ops.ShapeError):
+        ops.quantize_nvfp4(x, 0.0)
+    from eider_b200 import _lib
+    lib = _lib.load()
+    assert lib.infer_quantize_nvfp4_col_major_f32_on_stream(None, None, None, 16, 1, 1.0, None) == 1  # cudaErrorInvalidValue
+    assert lib.infer_quantize_nvfp4_col_major_f32_on_stream(x.data_ptr(), x.data_ptr(), x.data_ptr(), 0, 1, 1.0, None) == 1
+    assert lib.infer_quantize_nvfp4_col_major_f32_on_stream(x.data_ptr(), x.data_ptr(), x.data_ptr(), 16, 1, math.inf, None) == 1
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 5120), (8, 5120), (64, 1000)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_fp8_dynamic(ops, oracle, rows, cols, dtype):
+    import torch
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    q, s = ops.quantize_fp8_dynamic(_dev(x, torch.bfloat16 if dtype == "bf16" else None))
+    qo, so = oracle.quantize_fp8_dynamic(x)
+    assert np.array_equal(s.cpu().numpy(), so)
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+def test_fp8_static_and_weight(ops, oracle):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((5, 4100)).astype(np.float32)
+    q = ops.quantize_fp8_static(_dev(x), 0.125)
+    assert np.array_equal(q.cpu().numpy(), oracle.quantize_fp8_static(x, 0.125))
+    w = (rng.standard_normal((96, 512)) * 0.02).astype(np.float32)
+    wq, ws = ops.quantize_fp8_weight(_dev(w))
+    wqo, wso = oracle.quantize_fp8_weight(w)
+    assert np.array_equal(ws.cpu().numpy(), wso)
+    assert np.array_equal(wq.cpu().numpy(), wqo)
