@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config NAME]
+
+Default workload (N = 1): the NVFP4 W4A4 prefill GEMM of one 512-token chunk, M = 512, K = 5120,
+N = 27648 (fused gate+up).  A step = quantize the bf16 activations to NVFP4 on the fly (per-row global
+scale, per-16 E4M3 scales) + the block-scaled tcgen05 GEMM with bf16 output.  Inputs are synthetic
+(X ~ N(0,1) bf16, W ~ N(0, 0.02^2) quantized the ModelOpt way), seeded.
+
+Prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`), the same through the public
+API with host buffers (`e2e`), the roofline of the dominant kernel, and the reference's CPU path timed on
+the host cores (`cpu_baseline`).  With --gpus N > 1 (launched by torchrun) the weight is sharded over N
+column-wise and the bf16 outputs are all-gathered over NCCL (strong scaling of the same workload).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M, K, N = 512, 5120, 27648
+WORKLOAD = "nvfp4_w4a4_prefill_gemm_M512_K5120_N27648"
+METRIC = "nvfp4_gemm_tflops"
+UNIT = "TFLOP/s"
+FLOPS_PER_STEP = 2.0 * M * N * K
+NOMINAL_NVFP4_TFLOPS = 9000.0
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(sample_cols: int | None = None, threads: int = 0, target_seconds: float = 12.0):
+    """The reference's host path (NVFP4 unpack + f32 triple loop) on a bounded sample: all 512 tokens, all of K,
+    the first `sample_cols` output features.  Returns (TFLOP/s, cores, sample description, seconds)."""
+    import numpy as np
+
+    from oracle import oracle as o
+    rng = np.random.default_rng(0)
+    cores = o.max_threads() if threads <= 0 else threads
+    x = o.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+
+    def run(cols):
+        w = (rng.standard_normal((cols, K)) * 0.02).astype(np.float32)
+        wp, ws, g = o.quantize_weight(w)
+        scratch = np.empty(cols * K, np.float32)
+        t0 = time.perf_counter()
+        o.nvfp4_linear_host(x, wp, ws, float(g), threads=threads, scratch=scratch)
+        return time.perf_counter() - t0
+
+    if sample_cols is None:
+        probe_cols = 64
+        t_probe = run(probe_cols)
+        sample_cols = int(max(64, min(N, probe_cols * target_seconds / max(t_probe, 1e-6))))
+        sample_cols = max(64, sample_cols // 64 * 64)
+    seconds = run(sample_cols)
+    tflops = 2.0 * M * sample_cols * K / seconds / 1e12
+    sample = f"all {M} tokens x all K={K} x first {sample_cols} of {N} output features (unpack + f32 triple loop)"
+    return tflops, cores, sample, seconds
+
+
+def reference_arm(args):
+    """--impl reference: the reference's own CPU implementation of the path (oracle port; the Rust original cannot be
+    built here: no cargo/rustc) with all host threads, each step a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+
+    from oracle import oracle as o
+    rng = np.random.default_rng(0)
+    cores = o.max_threads()
+    x = o.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    # size the per-step sample so the whole run stays within a couple of minutes
+    cols = 64
+    w = (rng.standard_normal((cols, K)) * 0.02).astype(np.float32)
+    wp, ws, g = o.quantize_weight(w)
+    t0 = time.perf_counter()
+    o.nvfp4_linear_host(x, wp, ws, float(g))
+    t_probe = time.perf_counter() - t0
+    budget = 90.0 / max(1, args.steps + args.warmup)
+    cols = int(max(64, min(N, cols * budget / max(t_probe, 1e-6)))) // 64 * 64
+    cols = max(cols, 64)
+    w = (rng.standard_normal((cols, K)) * 0.02).astype(np.float32)
+    wp, ws, g = o.quantize_weight(w)
+    scratch = np.empty(cols * K, np.float32)
+    for _ in range(args.warmup):
+        o.nvfp4_linear_host(x, wp, ws, float(g), scratch=scratch)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.nvfp4_linear_host(x, wp, ws, float(g), scratch=scratch)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 2.0 * M * cols * K / dt / 1e12
+    sample = f"all {M} tokens x all K={K} x first {cols} of {N} output features per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3 * (N / cols), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4(e2m1+ue4m3) x nvfp4, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="eider_b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--block-n", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+
+    from eider_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.gpus != world:
+        if rank == 0:
+            print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
+    peaks = load_peaks()
+
+    # ---- synthetic inputs (seed 0): weights quantized the ModelOpt way on the device --------------------
+    n_local = N // world
+    assert N % (world * 128) == 0, "N shards must be multiples of 128 rows"
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rotate = 4 if world == 1 else 2  # distinct weight copies so the 126 MB L2 cannot hold the working set
+    weights = []
+    for r in range(rotate):
+        wgen = torch.Generator(device="cuda").manual_seed(1000 + r)
+        w_full_rows = torch.randn(n_local, K, device="cuda", generator=wgen) * 0.02
+        weights.append(ops.ModelOptWeight.quantize(w_full_rows))
+        del w_full_rows
+    x_host = torch.randn(M, K, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.cuda()
+    xq = ops.Nvfp4Matrix.zeros(M, K, "cuda", row_scales=True)
+    y_local = torch.empty(M, n_local, dtype=torch.bfloat16, device="cuda")
+    y_full = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    y_host = torch.empty(M, N if world == 1 else n_local * world, dtype=torch.bfloat16).pin_memory()
+    plan = ops.Fp4TnMatmulPlan(M, n_local, K)
+    if args.block_n:
+        plan.set_block_n(args.block_n)
+
+    def step(i, x):
+        w = weights[i % rotate]
+        ops.quantize_nvfp4_rowscale(x, out=xq)
+        plan.run(xq, w, out=y_local)
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y_local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """Device time of `steps` calls of fn(i) in ms, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for i in range(args.warmup):
+        step(i, x_dev)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    total_ms = timed(lambda i: step(i, x_dev), args.steps)
+    ms_per_step = total_ms / args.steps
+    value = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+
+    # ---- dominant kernel alone (roofline): CUDA events around the GEMM launches only ----------------------
+    gemm_ms = timed(lambda i: plan.run(xq, weights[i % rotate], out=y_local), args.steps) / args.steps
+    quant_ms = timed(lambda i: ops.quantize_nvfp4_rowscale(x_dev, out=xq), args.steps) / args.steps
+    if rank == 0:
+        clocks = sampler.stop()
+    status = plan.status()
+    assert status == 0, f"GEMM kernel reported status {status:#x}"
+
+    # ---- end to end through the public API with host buffers ------------------------------------------------
+    x_stage = torch.empty_like(x_dev)
+
+    def e2e_step(i):
+        x_stage.copy_(x_host, non_blocking=True)
+        step(i, x_stage)
+        if world == 1:
+            y_host.copy_(y_local, non_blocking=True)
+        else:
+            y_host.view(world, M, n_local).copy_(y_full, non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_value = FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    gemm_flops_local = 2.0 * M * n_local * K
+    achieved = gemm_flops_local / (gemm_ms * 1e-3) / 1e12
+    nvfp4_peak = 4.0 * peaks["bf16_tflops"]
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_kernel<nvfp4> (tcgen05.mma kind::mxf4nvf4.block_scale)",
+        "achieved": achieved, "peak": nvfp4_peak, "unit": "TFLOP/s", "frac": achieved / nvfp4_peak,
+        "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TF/s); NVFP4 is not measured by the driver",
+        "frac_of_nominal_9pf": achieved / NOMINAL_NVFP4_TFLOPS,
+        "kernel_ms": gemm_ms, "quantize_kernel_ms": quant_ms,
+        "hbm_gbs_at_min_bytes": (n_local * K * 9 / 16 + M * K * 9 / 16 + 2.0 * M * n_local) / (gemm_ms * 1e-3) / 1e9,
+        "traffic": None,
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "nvfp4(e2m1+ue4m3) x nvfp4, f32 accumulate, bf16 out", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "partition": f"N column-sharded x{world}" +
+                   (" + NCCL all-gather of bf16 outputs" if world > 1 else ""),
+                   "l2": f"inputs larger than L2: {rotate} rotating weight copies of {n_local * K * 9 // 16 // 2**20} MiB each"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "note": "weights stay resident in HBM (model state); X from and Y to pinned host memory"},
+        "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        tflops, cores, sample, seconds = cpu_baseline()
+        line["cpu_baseline"] = {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                "seconds": seconds}
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

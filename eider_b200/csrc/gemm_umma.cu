@@ -170,10 +170,12 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
 #define EIDER_DENSE(KIND, BN) launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream)
     if (nv) {
         if (plan.block_n == 256) return EIDER_DENSE(kNvf4, 256);
+        if (plan.block_n == 192) return EIDER_DENSE(kNvf4, 192);
         if (plan.block_n == 128) return EIDER_DENSE(kNvf4, 128);
         return EIDER_DENSE(kNvf4, 64);
     }
     if (plan.block_n == 256) return EIDER_DENSE(kFp8, 256);
+    if (plan.block_n == 192) return EIDER_DENSE(kFp8, 192);
     if (plan.block_n == 128) return EIDER_DENSE(kFp8, 128);
     return EIDER_DENSE(kFp8, 64);
 #undef EIDER_DENSE
@@ -313,6 +315,18 @@ cudaError_t run_grouped(const GroupedPlan& plan, const uint8_t* a_values, const 
 using namespace eider;
 using namespace eider::gemm;
 
+#ifdef EIDER_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
+    cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
+    if (st != cudaSuccess) return st;
+    if (reset) {
+        static long long zeros[256 * 8] = {0};
+        st = cudaMemcpyToSymbol(eider::gemm::g_trace, zeros, sizeof(zeros));
+    }
+    return st;
+}
+#endif
+
 extern "C" {
 
 // ---- dense NVFP4 W4A4 GEMM -----------------------------------------------------------------
@@ -347,7 +361,7 @@ cudaError_t eider_b200_nvfp4_gemm_tn_on_stream(void* raw, const uint8_t* x_value
 
 int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     auto* plan = static_cast<DensePlan*>(raw);
-    if (!plan || (block_n != 64 && block_n != 128 && block_n != 256)) return 0;
+    if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256)) return 0;
     plan->block_n = block_n;
     return 1;
 }

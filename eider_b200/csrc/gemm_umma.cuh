@@ -85,11 +85,31 @@ template <int KIND, int BLOCK_N> struct TmemPlan {
     static constexpr uint32_t kSfACols = KIND == kNvf4 ? 16 : 0;                        // 4 MMAs x 4 columns
     static constexpr uint32_t kSfBCols = KIND == kNvf4 ? (BLOCK_N > 128 ? 32 : 16) : 0;
     static constexpr uint32_t kAccStages = (2 * BLOCK_N + kSfACols + kSfBCols <= 512) ? 2 : 1;
-    static constexpr uint32_t kUsed = kAccStages * BLOCK_N + kSfACols + kSfBCols;
+    // When two full accumulators do not fit beside the scale columns, two buffers that share their last /
+    // first kOverlapCols columns are used: buffer 0 = [0, N), buffer 1 = [N - 64, 2N - 64).  The epilogue
+    // drains the shared columns first and hands the tensor memory back early, so the next tile's MMAs (into
+    // the other buffer) run while the rest of the tile is still being stored.
+    static constexpr uint32_t kOverlapCols = 64;
+    static constexpr bool kOverlap = kAccStages == 1 && (2 * BLOCK_N - kOverlapCols + kSfACols + kSfBCols <= 512);
+    static constexpr uint32_t kAccStride = kOverlap ? BLOCK_N - kOverlapCols : BLOCK_N;
+    static constexpr uint32_t kAccCols = kOverlap ? 2 * BLOCK_N - kOverlapCols : kAccStages * BLOCK_N;
+    static constexpr uint32_t kUsed = kAccCols + kSfACols + kSfBCols;
     static constexpr uint32_t kAlloc = kUsed <= 32 ? 32 : kUsed <= 64 ? 64 : kUsed <= 128 ? 128 : kUsed <= 256 ? 256 : 512;
-    static constexpr uint32_t kSfAOffset = kAccStages * BLOCK_N;
+    static constexpr uint32_t kSfAOffset = kAccCols;
     static constexpr uint32_t kSfBOffset = kSfAOffset + kSfACols;
 };
+
+#ifdef EIDER_GEMM_TRACE
+// Bring-up instrumentation (never compiled into the shipped library): per-CTA cycle counters.
+// [cta][0] mma total, [1] mma wait full, [2] mma wait acc_empty, [3] epilogue total, [4] epilogue wait acc_full,
+// [5] producer wait empty, [6] producer total, [7] tiles
+__device__ long long g_trace[256][8];
+#define TRACE_ADD(slot, v) g_trace[blockIdx.x][slot] += (v)
+#define TRACE_NOW() clock64()
+#else
+#define TRACE_ADD(slot, v) ((void)0)
+#define TRACE_NOW() 0ll
+#endif
 
 struct TileCoord {
     uint32_t row0;        // first row-operand row of the tile
@@ -195,7 +215,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     constexpr bool kNv = KIND == kNvf4;
     constexpr uint32_t kStage = L::stage_bytes(kNv);
     constexpr uint32_t kAcc = T::kAccStages;
-    static_assert(BLOCK_N == 16 || BLOCK_N == 32 || BLOCK_N == 64 || BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+    static_assert(BLOCK_N == 16 || BLOCK_N == 32 || BLOCK_N == 64 || BLOCK_N == 128 || BLOCK_N == 192 || BLOCK_N == 256, "BLOCK_N");
     static_assert(BLOCK_N % TERMS == 0, "TERMS must divide BLOCK_N");
     static_assert(!(GROUPED && (TRANSPOSED || TERMS != 1)), "grouped GEMM is row-major, one term");
 
@@ -242,18 +262,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     GroupWalker walker{p.group_offsets, p.groups, p.col_tiles};
+    const long long tr_e0_outer = TRACE_NOW();
+    (void)tr_e0_outer;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // (whole warp walks the schedule, one elected lane issues the copies)
+        {
+            const bool leader = umma::elect_one();
             uint32_t it = 0;
             TileCoord t;
             bool ok = true;
+            const long long tr_p0 = TRACE_NOW();
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x) {
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
                     const uint32_t stage = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
-                    if (!umma::mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty)) { ok = false; break; }
+                    const long long tr_w = TRACE_NOW();
+                    if (!__all_sync(0xffffffffu, umma::mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
+                    if (leader) TRACE_ADD(5, TRACE_NOW() - tr_w);
+                    if (!leader) continue;
                     const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
                     uint32_t bytes = L::kA + L::kB;
                     // scale tiles past the end of the column operand do not exist in memory: their rows are
@@ -282,58 +310,102 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     }
                 }
             }
+            if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp walks the schedule (so loop state stays warp-uniform and lives in uniform registers);
+        // one elected lane issues the tcgen05 instructions.
+        {
+            const bool leader = umma::elect_one();
             constexpr uint32_t idesc = kNv ? umma::idesc_nvf4(BLOCK_N) : umma::idesc_f8(BLOCK_N);
+            constexpr uint32_t kSfbStep = BLOCK_N > 128 ? 8 : 4;  // tensor-memory columns of column-operand scales per MMA
+            const uint32_t a_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_a));
+            const uint32_t b_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_b));
+            const uint32_t sfa_lo0 = umma::desc_lo_scales(umma::smem_u32(smem_sfa));
+            const uint32_t sfb_lo0 = umma::desc_lo_scales(umma::smem_u32(smem_sfb));
+            const uint32_t sfa_tmem = tmem_base + T::kSfAOffset;
+            const uint32_t tail_kb = ((p.k_bytes - (p.k_stages - 1) * kStageBytesK) + 31) / 32;  // MMAs in the last stage
             uint32_t it = 0, tile_count = 0;
             TileCoord t;
             bool ok = true;
+            const long long tr_m0 = TRACE_NOW();
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x, ++tile_count) {
                 const uint32_t acc = tile_count % kAcc;
                 const uint32_t acc_phase = (tile_count / kAcc) & 1;
-                if (!umma::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty)) { ok = false; break; }
+                const long long tr_a = TRACE_NOW();
+                if (!__all_sync(0xffffffffu, umma::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
+                if (leader) { TRACE_ADD(2, TRACE_NOW() - tr_a); TRACE_ADD(7, 1); }
                 umma::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+                const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
+                // a column tile that does not start on a 128-row scale tile starts (col0 % 128) / 32 columns into it
+                const uint32_t sfb_sub = (BLOCK_N % 128 != 0) ? (t.col0 % kTileRows) / 32 : 0;
+                const uint32_t sfb_tmem = tmem_base + T::kSfBOffset;
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
                     const uint32_t stage = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
-                    if (!umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull)) { ok = false; break; }
+                    const long long tr_f = TRACE_NOW();
+                    if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
+                    if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
                     umma::tc_fence_after();
-                    const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);
-                    const uint32_t a_addr = umma::smem_u32(smem_a + stage * L::kA);
-                    const uint32_t b_addr = umma::smem_u32(smem_b + stage * L::kB);
-                    if (kNv) {
-                        const uint32_t sfa_addr = umma::smem_u32(smem_sfa + stage * L::kSfA);
-                        const uint32_t sfb_addr = umma::smem_u32(smem_sfb + stage * L::kSfB);
-                        for (uint32_t j = 0; j < kb; ++j) {
-                            umma::tc_copy_scales(tmem_base + T::kSfAOffset + j * 4, umma::smem_desc_scales(sfa_addr + j * kScaleTileBytes));
-                            if (BLOCK_N > 128) {
-                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 8, umma::smem_desc_scales(sfb_addr + j * kScaleTileBytes));
-                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 8 + 4,
-                                                     umma::smem_desc_scales(sfb_addr + (4 + j) * kScaleTileBytes));
-                            } else {
-                                umma::tc_copy_scales(tmem_base + T::kSfBOffset + j * 4, umma::smem_desc_scales(sfb_addr + j * kScaleTileBytes));
+                    // descriptors differ from the per-CTA base only in the start-address field (16-byte units)
+                    const uint32_t a_lo = a_lo0 + stage * (L::kA >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (L::kB >> 4);
+                    const uint32_t sfa_lo = sfa_lo0 + stage * (L::kSfA >> 4);
+                    const uint32_t sfb_lo = sfb_lo0 + stage * (L::kSfB >> 4);
+                    const uint32_t first = (s > t.k_stage0) ? 1u : 0u;
+                    if (!leader) {
+                        // nothing to issue
+                    } else if (s + 1 < p.k_stages || tail_kb == 4) {
+#ifndef EIDER_EXP_SKIP_SFCP
+                        if (kNv) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                umma::tc_copy_scales(sfa_tmem + j * 4, umma::make_desc(sfa_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales(sfb_tmem + j * kSfbStep, umma::make_desc(sfb_lo + j * 32, umma::kDescHiScales));
+                                if (BLOCK_N > 128)
+                                    umma::tc_copy_scales(sfb_tmem + j * kSfbStep + 4,
+                                                         umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
                             }
                         }
+#endif
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
+                            const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
+                            if (kNv)
+                                umma::mma_nvf4(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * kSfbStep + sfb_sub,
+                                               j == 0 ? first : 1u);
+                            else
+                                umma::mma_f8(d_tmem, a_desc, b_desc, idesc, j == 0 ? first : 1u);
+                        }
+                    } else {  // last stage of a K that is not a multiple of the stage depth
+                        for (uint32_t j = 0; j < tail_kb; ++j) {
+                            if (kNv) {
+                                umma::tc_copy_scales(sfa_tmem + j * 4, umma::make_desc(sfa_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales(sfb_tmem + j * kSfbStep, umma::make_desc(sfb_lo + j * 32, umma::kDescHiScales));
+                                if (BLOCK_N > 128)
+                                    umma::tc_copy_scales(sfb_tmem + j * kSfbStep + 4,
+                                                         umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
+                            }
+                        }
+                        for (uint32_t j = 0; j < tail_kb; ++j) {
+                            const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
+                            const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
+                            if (kNv)
+                                umma::mma_nvf4(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * kSfbStep + sfb_sub,
+                                               j == 0 ? first : 1u);
+                            else
+                                umma::mma_f8(d_tmem, a_desc, b_desc, idesc, j == 0 ? first : 1u);
+                        }
                     }
-                    for (uint32_t j = 0; j < kb; ++j) {
-                        const uint64_t a_desc = umma::smem_desc_sw128(a_addr + j * 32);
-                        const uint64_t b_desc = umma::smem_desc_sw128(b_addr + j * 32);
-                        const uint32_t accumulate = (s > t.k_stage0 || j > 0) ? 1u : 0u;
-                        // a column tile narrower than 128 starts (col0 % 128) / 32 columns into its scale tile
-                        const uint32_t sfb_sub = BLOCK_N < 128 ? (t.col0 % kTileRows) / 32 : 0;
-                        if (kNv)
-                            umma::mma_nvf4(d_tmem, a_desc, b_desc, idesc, tmem_base + T::kSfAOffset + j * 4,
-                                           tmem_base + T::kSfBOffset + j * (BLOCK_N > 128 ? 8 : 4) + sfb_sub, accumulate);
-                        else
-                            umma::mma_f8(d_tmem, a_desc, b_desc, idesc, accumulate);
-                    }
-                    umma::tc_commit(&empty[stage]);  // frees the stage once these MMAs (and scale copies) retire
+                    if (leader) umma::tc_commit(&empty[stage]);  // frees the stage once these MMAs (and scale copies) retire
+                    __syncwarp();
                 }
-                if (ok) umma::tc_commit(&acc_full[acc]);
+                if (ok && leader) umma::tc_commit(&acc_full[acc]);
+                __syncwarp();
             }
+            if (leader) TRACE_ADD(0, TRACE_NOW() - tr_m0);
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
@@ -345,16 +417,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
             const bool empty_tile = t.k_stage0 >= t.k_stage1;  // a K split with no stages contributes zeros
+            const long long tr_w = TRACE_NOW();
             if (!umma::mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
+            if (threadIdx.x == 64) TRACE_ADD(4, TRACE_NOW() - tr_w);
             umma::tc_fence_after();
             const uint32_t row = t.row0 + quad * 32 + lane;
             const bool row_ok = row < t.row_end;
             float rs = GROUPED ? (p.group_alpha ? p.group_alpha[t.group] : p.alpha) : p.alpha;
             if (p.row_scale && row_ok) rs *= p.row_scale[row];
-            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + acc * BLOCK_N;
+            const uint32_t buf = T::kOverlap ? (tile_count & 1) : acc;
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * T::kAccStride;
 #pragma unroll 1
-            for (uint32_t c = 0; c < BLOCK_N; c += 32) {
+            for (uint32_t ci = 0; ci < BLOCK_N; ci += 32) {
                 constexpr uint32_t kChunk = BLOCK_N < 32 ? BLOCK_N : 32;
+                // overlapping buffers: buffer 0 shares its last columns, buffer 1 its first ones; drain those first
+                const uint32_t c = (T::kOverlap && buf == 0) ? (BLOCK_N - 32 - ci) : ci;
                 uint32_t raw[32];
                 if (empty_tile) {
 #pragma unroll
@@ -368,6 +445,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     for (int i = 0; i < 16; ++i) { raw[i] = r16[i]; raw[i + 16] = 0; }
                 }
                 umma::tmem_load_wait();
+                if (T::kOverlap && ci + 32 == T::kOverlapCols) {
+                    // the shared columns are in registers: the MMA warp may start the next tile in the other buffer
+                    umma::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+                }
                 if (!TRANSPOSED) {
                     float v[32];
 #pragma unroll
@@ -436,9 +519,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 }
             }
             // accumulator drained: hand the tensor-memory stage back to the MMA warp
-            umma::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+            if (!T::kOverlap) {
+                umma::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+            }
 
             if (TRANSPOSED && p.splits > 1) {
                 // split-K: the last CTA to finish a row tile sums the partials in split order.
@@ -472,6 +557,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
         }
     }
 
+    if (threadIdx.x == 64) TRACE_ADD(3, TRACE_NOW() - tr_e0_outer);
     // ---------------------------------------------------------------------- teardown
     umma::tc_fence_before();
     __syncthreads();

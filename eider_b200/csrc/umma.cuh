@@ -186,6 +186,18 @@ __device__ __forceinline__ uint64_t smem_desc_scales(uint32_t smem_addr) {
     return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (8ull << 32) | (1ull << 46);
 }
 
+// The same descriptors split into the per-stage low word (start address, 16-byte units) and the constant high
+// word, so that the MMA-issuing thread spends one integer add per descriptor.
+constexpr uint32_t kDescHiSw128 = 64u | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiScales = 8u | (1u << 14);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr) { return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_scales(uint32_t smem_addr) { return (smem_addr & 0x3ffffu) >> 4; }
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor, kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M = 128.
 __host__ __device__ constexpr uint32_t idesc_f8(uint32_t n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);

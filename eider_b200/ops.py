@@ -169,7 +169,7 @@ class Fp4TnMatmulPlan:
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128 or 256, got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192 or 256, got {block_n}")
 
     def run(self, x: Nvfp4Matrix, w: ModelOptWeight, out: torch.Tensor | None = None, alpha: float | None = None,
             beta: float = 0.0, c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
@@ -222,7 +222,7 @@ class Fp8TnMatmulPlan:
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128 or 256, got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192 or 256, got {block_n}")
 
     def run(self, xq: torch.Tensor, wq: torch.Tensor, token_scale: torch.Tensor | None,
             channel_scale: torch.Tensor | None, out: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0,
