@@ -41,6 +41,13 @@ SIGNATURES = {
     "eider_b200_fp8_gemm_tn_create": (_P, [_U32, _U32, _U32]),
     "eider_b200_fp8_gemm_tn_destroy": (None, [_P]),
     "eider_b200_fp8_gemm_tn_on_stream": (_I, [_P, _P, _P, _P, _P, _F, _F, _P, _P, _I, _P]),
+    "eider_b200_expand_nvfp4_terms_on_stream": (_I, [_P, _I, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "eider_b200_nvfp4_decode_create": (_P, [_U32, _U32, _U32]),
+    "eider_b200_fp8_decode_create": (_P, [_U32, _U32, _U32]),
+    "eider_b200_decode_destroy": (None, [_P]),
+    "eider_b200_decode_plan_status": (_I, [_P, _P]),
+    "eider_b200_nvfp4_w4a16_gemv_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _P, _F, _I, _P]),
+    "eider_b200_fp8_linear_decode_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _I, _P]),
     "eider_b200_gemm_plan_set_block_n": (_I, [_P, _U32]),
     "eider_b200_gemm_plan_status": (_I, [_P, _P]),
 }

@@ -97,20 +97,60 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Correctly rounded division by a divisor that is reused many times.  With r = RN(1/d) correctly rounded,
+// q0 = RN(x r), e = x - q0 d (exact in one FMA) and q = RN(q0 + e r) is the correctly rounded x / d (Markstein)
+// whenever nothing under- or overflows on the way.  The quantizers only depend on quotients of ordinary
+// magnitude: a quotient that underflows is far below every E2M1 / E4M3 rounding boundary and encodes to the same
+// code either way, zeros keep their sign through q0, and an overflowing q0 is passed through as the infinity the
+// IEEE division would give.  Divisors outside 2^-20 .. 2^20 (where e itself could underflow) use __fdiv_rn.
+struct Divisor {
+    float d, r;
+    bool fast;
+};
+__device__ __forceinline__ Divisor make_divisor(float d) {
+    Divisor D;
+    D.d = d;
+    D.r = __frcp_rn(d);
+    D.fast = d > 9.5367431640625e-07f && d < 1048576.0f;
+    return D;
+}
+__device__ __forceinline__ float div_rn(float x, const Divisor& D) {
+    if (!D.fast) return __fdiv_rn(x, D.d);
+    const float q0 = x * D.r;
+    const float e = fmaf(-q0, D.d, x);
+    const float q = fmaf(e, D.r, q0);
+    const float aq = fabsf(q0);
+    return (aq == 0.0f || aq == __int_as_float(0x7f800000)) ? q0 : q;
+}
+// |v| for finite v, 0 otherwise (NaN compares false): the quantizers ignore non-finite values in maxima.
+__device__ __forceinline__ float finite_abs(float v) {
+    const float a = fabsf(v);
+    return a < __int_as_float(0x7f800000) ? a : 0.0f;
+}
+// amax / 6 correctly rounded (6 is far from every hazard of the scheme above).
+__device__ __forceinline__ float div6_rn(float a) {
+    const float r = 0.16666667163372039794921875f;  // RN(1/6)
+    const float q0 = a * r;
+    const float e = fmaf(-q0, 6.0f, a);
+    const float q = fmaf(e, r, q0);
+    return (q0 > 1e-30f && q0 < 1e30f) ? q : __fdiv_rn(a, 6.0f);
+}
+
 // Quantize one 16-element block already divided by the input scale.  Returns the scale byte and
 // writes 8 packed bytes.  Order of operations: crates/eider-cuda/native/non_gemm.cu:120-153.
 __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32_t valid, uint2* packed_out) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i)
-        if (static_cast<uint32_t>(i) < valid && isfinite(v[i])) amax = fmaxf(amax, fabsf(v[i]));
-    uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(__fdiv_rn(amax, kE2M1Max));
+        if (static_cast<uint32_t>(i) < valid) amax = fmaxf(amax, finite_abs(v[i]));
+    uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(div6_rn(amax));
     float s = e4m3_value(sc);
+    const Divisor ds = make_divisor(s == 0.0f ? 1.0f : s);
     uint32_t w[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-        float lo = (s == 0.0f || static_cast<uint32_t>(i) >= valid) ? 0.0f : __fdiv_rn(v[i], s);
-        float hi = (s == 0.0f || static_cast<uint32_t>(i + 1) >= valid) ? 0.0f : __fdiv_rn(v[i + 1], s);
+        float lo = (s == 0.0f || static_cast<uint32_t>(i) >= valid) ? 0.0f : div_rn(v[i], ds);
+        float hi = (s == 0.0f || static_cast<uint32_t>(i + 1) >= valid) ? 0.0f : div_rn(v[i + 1], ds);
         uint32_t byte = e2m1x2_code(lo, hi);
         if (static_cast<uint32_t>(i + 1) >= valid) byte &= 0x0fu;
         if (static_cast<uint32_t>(i) >= valid) byte = 0;

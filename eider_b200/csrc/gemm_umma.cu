@@ -396,4 +396,114 @@ cudaError_t eider_b200_fp8_gemm_tn_on_stream(void* raw, const uint8_t* x_values,
                      out_is_bf16, stream);
 }
 
+// ---- decode (tokens <= 64): weights stream once, tokens ride on the MMA N dimension -----------------
+namespace {
+
+uint32_t pick_splits(uint32_t k_stages) {
+    // about five 128-byte K stages per work item keeps every persistent CTA within one item of the average load
+    uint32_t splits = (k_stages + 4) / 5;
+    if (splits < 1) splits = 1;
+    if (splits > 32) splits = 32;
+    while (splits > 1 && ((k_stages + splits - 1) / splits) * (splits - 1) >= k_stages) --splits;  // no empty split
+    return splits;
+}
+
+DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t k) {
+    if (max_tokens == 0 || max_tokens > 64 || n == 0 || k == 0) return nullptr;
+    if (kind == kNvf4 && (k % 32 != 0 || k / 8 > 4096)) return nullptr;
+    if (kind == kFp8 && k % 16 != 0) return nullptr;
+    auto* plan = new DecodePlan{};
+    plan->kind = kind;
+    plan->max_tokens = max_tokens;
+    plan->n = n;
+    plan->k = k;
+    plan->terms = kind == kNvf4 ? (max_tokens * 8 <= 256 ? 8u : 4u) : 1u;
+    const uint32_t k_bytes = kind == kNvf4 ? k / 2 : k;
+    plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK);
+    const uint32_t row_tiles = (n + kTileRows - 1) / kTileRows;
+    const size_t ws = static_cast<size_t>(plan->splits) * row_tiles * kTileRows * max_tokens * sizeof(float);
+    const uint32_t rows = max_tokens * plan->terms;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&plan->workspace), ws) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&plan->counters), row_tiles * sizeof(uint32_t)) == cudaSuccess &&
+              cudaMemset(plan->counters, 0, row_tiles * sizeof(uint32_t)) == cudaSuccess &&
+              alloc_status(&plan->status) == cudaSuccess;
+    if (ok && kind == kNvf4) {
+        const size_t sf = scale_layout_len(rows, k);
+        ok = cudaMalloc(reinterpret_cast<void**>(&plan->act_packed), static_cast<size_t>(rows) * (k / 2)) == cudaSuccess &&
+             cudaMalloc(reinterpret_cast<void**>(&plan->act_scales), sf) == cudaSuccess &&
+             cudaMemset(plan->act_scales, 0, sf) == cudaSuccess &&
+             cudaMalloc(reinterpret_cast<void**>(&plan->act_col_scale), rows * sizeof(float)) == cudaSuccess;
+    } else if (ok) {
+        ok = cudaMalloc(reinterpret_cast<void**>(&plan->act_packed), static_cast<size_t>(max_tokens) * k) == cudaSuccess &&
+             cudaMalloc(reinterpret_cast<void**>(&plan->act_col_scale), max_tokens * sizeof(float)) == cudaSuccess;
+    }
+    if (!ok) {
+        cudaFree(plan->workspace); cudaFree(plan->counters); cudaFree(plan->status);
+        cudaFree(plan->act_packed); cudaFree(plan->act_scales); cudaFree(plan->act_col_scale);
+        delete plan;
+        return nullptr;
+    }
+    return plan;
+}
+
+}  // namespace
+
+/* NVFP4 W4A16 decode: y[t][n] = weight_scale_2 * sum_k x[t][k] * e2m1(W[n][k]) * ue4m3(S[n][k/16]) */
+void* eider_b200_nvfp4_decode_create(uint32_t max_tokens, uint32_t out_features, uint32_t in_features) {
+    return make_decode_plan(kNvf4, max_tokens, out_features, in_features);
+}
+
+void* eider_b200_fp8_decode_create(uint32_t max_tokens, uint32_t out_features, uint32_t in_features) {
+    return make_decode_plan(kFp8, max_tokens, out_features, in_features);
+}
+
+void eider_b200_decode_destroy(void* raw) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan) return;
+    cudaFree(plan->workspace); cudaFree(plan->counters); cudaFree(plan->status);
+    cudaFree(plan->act_packed); cudaFree(plan->act_scales); cudaFree(plan->act_col_scale);
+    delete plan;
+}
+
+cudaError_t eider_b200_decode_plan_status(void* raw, uint32_t* host_status) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan || !host_status) return cudaErrorInvalidValue;
+    return cudaMemcpy(host_status, plan->status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+}
+
+cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, int input_is_bf16, uint32_t tokens,
+                                                  const uint8_t* w_values, const uint8_t* w_scales_tiled,
+                                                  float weight_scale_2, const void* c, void* d, float beta,
+                                                  int out_is_bf16, cudaStream_t stream) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan || plan->kind != kNvf4 || !input || !w_values || !w_scales_tiled || !d || tokens == 0 ||
+        tokens > plan->max_tokens)
+        return cudaErrorInvalidValue;
+    cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
+                                                             plan->act_col_scale, tokens, plan->k, plan->terms, stream);
+    if (st != cudaSuccess) return st;
+    return run_decode(*plan, plan->act_packed, plan->act_scales, plan->act_col_scale, tokens, w_values, w_scales_tiled,
+                      nullptr, c, d, weight_scale_2, beta, out_is_bf16, stream);
+}
+
+/* FP8 W8A8 decode with per-token dynamic activation scales:
+ * y[t][n] = (sum_k e4m3(xq[t][k]) * e4m3(w[n][k])) * s_x[t] * s_w[n] */
+cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input, int input_is_bf16, uint32_t tokens,
+                                                   const uint8_t* weight, const float* channel_scale, float weight_scale,
+                                                   void* d, int out_is_bf16, cudaStream_t stream) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan || plan->kind != kFp8 || !input || !weight || !d || tokens == 0 || tokens > plan->max_tokens)
+        return cudaErrorInvalidValue;
+    cudaError_t st;
+    if (input_is_bf16)
+        st = eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(static_cast<const uint16_t*>(input), plan->act_packed,
+                                                                       plan->act_col_scale, tokens, plan->k, stream);
+    else
+        st = infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(static_cast<const float*>(input), plan->act_packed,
+                                                                 plan->act_col_scale, tokens, plan->k, stream);
+    if (st != cudaSuccess) return st;
+    return run_decode(*plan, plan->act_packed, nullptr, plan->act_col_scale, tokens, weight, nullptr, channel_scale, nullptr,
+                      d, weight_scale, 0.0f, out_is_bf16, stream);
+}
+
 }  // extern "C"

@@ -52,7 +52,7 @@ struct Params {
     // decode: combine `TERMS` consecutive columns into one output column; split-K
     uint32_t out_cols;       // number of logical output columns (cols / TERMS)
     uint32_t splits;         // K splits (1 = none)
-    float* workspace;        // [splits][row_tiles*128][out_cols] fp32 partials
+    float* workspace;        // [splits][out_cols][row_tiles*128] fp32 partials
     uint32_t* counters;      // [row_tiles] arrival counters, self-resetting
     // grouped (MoE): per-group row ranges of the row operand
     const uint32_t* group_offsets;  // [groups + 1] or null
@@ -505,7 +505,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                             sum = fmaf(__uint_as_float(raw[g * TERMS + j]), cs, sum);
                         }
                         if (p.splits > 1) {
-                            p.workspace[(static_cast<size_t>(t.split) * p.row_tiles * kTileRows + row) * p.out_cols + ocol] = sum;
+                            p.workspace[(static_cast<size_t>(t.split) * p.out_cols + ocol) * (p.row_tiles * kTileRows) + row] = sum;
                         } else if (row_ok) {
                             const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
                             float x = sum * rs;
@@ -541,7 +541,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                         for (uint32_t ocol = 0; ocol < p.out_cols; ++ocol) {
                             float sum = 0.0f;
                             for (uint32_t s = 0; s < p.splits; ++s)
-                                sum += __ldcg(&p.workspace[(static_cast<size_t>(s) * p.row_tiles * kTileRows + row) * p.out_cols + ocol]);
+                                sum += __ldcg(&p.workspace[(static_cast<size_t>(s) * p.out_cols + ocol) * (p.row_tiles * kTileRows) + row]);
                             const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
                             float x = sum * rs;
                             if (p.beta != 0.0f && p.c_in)

@@ -68,8 +68,102 @@ __device__ __forceinline__ float block_max(float v, float* smem) {
 
 enum ScaleMode { kStatic = 0, kPerRow = 1 };
 
-// One CTA per row.  TILED: scales go to the 128x4 tile layout with outer = row (activations);
-// otherwise row-major [rows][K/16] (checkpoint weight layout).
+// Eight consecutive elements of a row (half a 16-element block) per thread: 128-bit loads, the block maximum
+// is completed with one shuffle between the two lanes of a block, one 32-bit packed store per thread.
+template <typename T> struct Half8;
+template <> struct Half8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct Half8<uint16_t> {
+    static __device__ __forceinline__ void load(const uint16_t* p, float (&v)[8]) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+};
+
+// One CTA per row, one thread per 8 elements (rows longer than 8 * blockDim are walked in passes).  Requires
+// K % 16 == 0 and 16-byte aligned rows; the generic kernel below takes everything else.
+// TILED: scales go to the 128x4 tile layout with outer = row (activations); otherwise row-major [rows][K/16].
+template <typename T, int MODE, bool TILED, int PASSES>
+__global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
+                                                                   uint8_t* __restrict__ scales,
+                                                                   float* __restrict__ row_scales, uint32_t rows, uint32_t k,
+                                                                   float input_scale) {
+    __shared__ float red[32];
+    const uint32_t row = blockIdx.x;
+    const T* src = input + static_cast<size_t>(row) * k;
+    const uint32_t halves = k / 8;
+    float held[PASSES][8];
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+        const uint32_t h = threadIdx.x + j * blockDim.x;
+        if (h < halves) {
+            Half8<T>::load(src + h * 8, held[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) held[j][i] = 0.0f;
+        }
+    }
+    float g = input_scale;
+    if (MODE == kPerRow) {
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(held[j][i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        amax = red[0];
+        for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+        g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+        if (threadIdx.x == 0) row_scales[row] = g;
+    }
+    const Divisor dg = make_divisor(g);
+    uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
+    const uint32_t blocks = k / 16;
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+        const uint32_t h = threadIdx.x + j * blockDim.x;
+        float v[8];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = div_rn(held[j][i], dg);
+            amax = fmaxf(amax, finite_abs(v[i]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the other half of the block (all lanes take part)
+        if (h >= halves) continue;
+        const uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(div6_rn(amax));
+        const float sv = e4m3_value(sc);
+        const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
+            const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
+            w |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << (i * 4);
+        }
+        *reinterpret_cast<uint32_t*>(prow + h * 4) = w;
+        if ((h & 1) == 0) {
+            const uint32_t b = h >> 1;
+            if (TILED) scales[tiled_scale_offset(row, b, k)] = sc;
+            else scales[static_cast<size_t>(row) * blocks + b] = sc;
+        }
+    }
+}
+
+// Generic kernel: any K (ragged last block, odd K) and any alignment.  One CTA per row, one thread per block.
 template <typename T, int MODE, bool TILED>
 __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
                                                              uint8_t* __restrict__ scales, float* __restrict__ row_scales,
@@ -94,13 +188,14 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict
         g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
         if (threadIdx.x == 0) row_scales[row] = g;
     }
+    const Divisor dg = make_divisor(g);
     uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
     for (uint32_t b = threadIdx.x; b < blocks; b += blockDim.x) {
         float v[16];
         uint32_t valid;
         load_block(src, k, b, vec_ok, v, valid);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __fdiv_rn(v[i], g);
+        for (int i = 0; i < 16; ++i) v[i] = div_rn(v[i], dg);
         uint2 bytes;
         uint8_t sc = quantize_block16(v, valid, &bytes);
         if (valid == 16 && (k % 16 == 0)) {
@@ -118,6 +213,107 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict
         }
         if (TILED) scales[tiled_scale_offset(row, b, k)] = sc;
         else scales[static_cast<size_t>(row) * blocks + b] = sc;
+    }
+}
+
+template <typename T, int MODE, bool TILED>
+cudaError_t launch_quantize_nvfp4(const T* input, uint8_t* packed, uint8_t* scales, float* row_scales, uint32_t rows,
+                                  uint32_t k, float input_scale, cudaStream_t stream) {
+    const bool aligned = (k % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(packed) & 3) == 0);
+    const uint32_t halves = k / 8;
+    if (aligned && halves <= 4096) {
+        // an even number of threads, a multiple of 32, so both halves of a block sit in one warp
+        const uint32_t passes = (halves + 1023) / 1024;
+        uint32_t threads = ((halves + passes - 1) / passes + 31) / 32 * 32;
+        switch (passes) {
+            case 1: quantize_nvfp4_fast_kernel<T, MODE, TILED, 1><<<rows, threads, 0, stream>>>(input, packed, scales, row_scales, rows, k, input_scale); break;
+            case 2: quantize_nvfp4_fast_kernel<T, MODE, TILED, 2><<<rows, threads, 0, stream>>>(input, packed, scales, row_scales, rows, k, input_scale); break;
+            case 3: quantize_nvfp4_fast_kernel<T, MODE, TILED, 3><<<rows, threads, 0, stream>>>(input, packed, scales, row_scales, rows, k, input_scale); break;
+            default: quantize_nvfp4_fast_kernel<T, MODE, TILED, 4><<<rows, threads, 0, stream>>>(input, packed, scales, row_scales, rows, k, input_scale); break;
+        }
+        return cudaGetLastError();
+    }
+    quantize_nvfp4_kernel<T, MODE, TILED><<<rows, 256, 0, stream>>>(input, packed, scales, row_scales, rows, k, input_scale);
+    return cudaGetLastError();
+}
+
+// Residual NVFP4 expansion of a few activation rows for the tensor-core decode GEMV.
+//
+// x ~= sum_j g_j * deq(q_j): term 0 is the ordinary NVFP4 quantization of x with the per-row scale
+// g_0 = amax / 2688; every further term quantizes what the previous ones left over, with g_j = g_0 / 4^j
+// (the leftover of a block is at most about 1/6 of its maximum, so the block scales stay inside E4M3).
+// Eight terms carry an fp32 activation to better than 2^-17 of the row maximum, so a W4A4 block-scaled MMA
+// over the expanded rows reproduces the W4A16 product (the reference keeps up to two such residual terms for
+// its own W4A4 decode, crates/eider-cuda/native/sm12x_mma.cu:717-880).
+// Output rows are token-major: row = token * TERMS + j; scales are tiled with outer = that row.
+template <typename T, int PASSES>
+__global__ void __launch_bounds__(1024) expand_nvfp4_terms_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
+                                                                  uint8_t* __restrict__ scales, float* __restrict__ col_scale,
+                                                                  uint32_t k, uint32_t terms) {
+    __shared__ float red[32];
+    const uint32_t token = blockIdx.x;
+    const T* src = input + static_cast<size_t>(token) * k;
+    const uint32_t halves = k / 8;
+    float r[PASSES][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PASSES; ++j) {
+        const uint32_t h = threadIdx.x + j * blockDim.x;
+        if (h < halves) {
+            Half8<T>::load(src + h * 8, r[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[j][i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (!isfinite(r[j][i])) r[j][i] = 0.0f;  // non-finite activations carry no information for a GEMV
+            amax = fmaxf(amax, fabsf(r[j][i]));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+    for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+    float g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+    for (uint32_t term = 0; term < terms; ++term) {
+        const uint32_t row = token * terms + term;
+        if (threadIdx.x == 0) col_scale[row] = g;
+        const Divisor dg = make_divisor(g);
+        uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const uint32_t h = threadIdx.x + j * blockDim.x;
+            float v[8];
+            float bmax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = div_rn(r[j][i], dg);
+                bmax = fmaxf(bmax, fabsf(v[i]));
+            }
+            bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+            if (h >= halves) continue;
+            const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(div6_rn(bmax));
+            const float sv = e4m3_value(sc);
+            const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
+                const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
+                const uint32_t byte = e2m1x2_code(lo, hi);
+                w |= byte << (i * 4);
+                // leftover for the next term
+                r[j][i] = fmaf(-e2m1_value(byte & 0xfu) * sv, g, r[j][i]);
+                r[j][i + 1] = fmaf(-e2m1_value(byte >> 4) * sv, g, r[j][i + 1]);
+            }
+            *reinterpret_cast<uint32_t*>(prow + h * 4) = w;
+            if ((h & 1) == 0) scales[tiled_scale_offset(row, h >> 1, k)] = sc;
+        }
+        g *= 0.25f;
     }
 }
 
@@ -188,9 +384,7 @@ cudaError_t infer_quantize_nvfp4_col_major_f32_on_stream(const float* input, uin
                                                          uint32_t rows, uint32_t cols, float input_scale,
                                                          cudaStream_t stream) {
     if (!input || !packed || !scales || rows == 0 || cols == 0 || bad_scale(input_scale)) return cudaErrorInvalidValue;
-    quantize_nvfp4_kernel<float, kStatic, true><<<cols, 256, 0, stream>>>(input, packed, scales, nullptr, cols, rows,
-                                                                          input_scale);
-    return cudaGetLastError();
+    return launch_quantize_nvfp4<float, kStatic, true>(input, packed, scales, nullptr, cols, rows, input_scale, stream);
 }
 
 cudaError_t infer_quantize_nvfp4_col_major_f32(const float* input, uint8_t* packed, uint8_t* scales, uint32_t rows,
@@ -202,9 +396,7 @@ cudaError_t eider_b200_quantize_nvfp4_bf16_on_stream(const uint16_t* input, uint
                                                      uint32_t rows, uint32_t cols, float input_scale,
                                                      cudaStream_t stream) {
     if (!input || !packed || !scales || rows == 0 || cols == 0 || bad_scale(input_scale)) return cudaErrorInvalidValue;
-    quantize_nvfp4_kernel<uint16_t, kStatic, true><<<cols, 256, 0, stream>>>(input, packed, scales, nullptr, cols, rows,
-                                                                             input_scale);
-    return cudaGetLastError();
+    return launch_quantize_nvfp4<uint16_t, kStatic, true>(input, packed, scales, nullptr, cols, rows, input_scale, stream);
 }
 
 cudaError_t eider_b200_quantize_nvfp4_rowscale_on_stream(const void* input, int input_is_bf16, uint8_t* packed,
@@ -212,12 +404,10 @@ cudaError_t eider_b200_quantize_nvfp4_rowscale_on_stream(const void* input, int 
                                                          uint32_t cols, cudaStream_t stream) {
     if (!input || !packed || !scales || !row_scales || rows == 0 || cols == 0) return cudaErrorInvalidValue;
     if (input_is_bf16)
-        quantize_nvfp4_kernel<uint16_t, kPerRow, true><<<cols, 256, 0, stream>>>(
-            static_cast<const uint16_t*>(input), packed, scales, row_scales, cols, rows, 1.0f);
-    else
-        quantize_nvfp4_kernel<float, kPerRow, true><<<cols, 256, 0, stream>>>(static_cast<const float*>(input), packed,
-                                                                            scales, row_scales, cols, rows, 1.0f);
-    return cudaGetLastError();
+        return launch_quantize_nvfp4<uint16_t, kPerRow, true>(static_cast<const uint16_t*>(input), packed, scales, row_scales,
+                                                              cols, rows, 1.0f, stream);
+    return launch_quantize_nvfp4<float, kPerRow, true>(static_cast<const float*>(input), packed, scales, row_scales, cols,
+                                                       rows, 1.0f, stream);
 }
 
 cudaError_t eider_b200_quantize_nvfp4_weight_on_stream(const void* weight, int input_is_bf16, uint8_t* packed,
@@ -227,14 +417,10 @@ cudaError_t eider_b200_quantize_nvfp4_weight_on_stream(const void* weight, int i
         bad_scale(global_scale))
         return cudaErrorInvalidValue;
     if (input_is_bf16)
-        quantize_nvfp4_kernel<uint16_t, kStatic, false><<<out_features, 256, 0, stream>>>(
-            static_cast<const uint16_t*>(weight), packed, scales_row_major, nullptr, out_features, in_features,
-            global_scale);
-    else
-        quantize_nvfp4_kernel<float, kStatic, false><<<out_features, 256, 0, stream>>>(
-            static_cast<const float*>(weight), packed, scales_row_major, nullptr, out_features, in_features,
-            global_scale);
-    return cudaGetLastError();
+        return launch_quantize_nvfp4<uint16_t, kStatic, false>(static_cast<const uint16_t*>(weight), packed, scales_row_major,
+                                                               nullptr, out_features, in_features, global_scale, stream);
+    return launch_quantize_nvfp4<float, kStatic, false>(static_cast<const float*>(weight), packed, scales_row_major, nullptr,
+                                                        out_features, in_features, global_scale, stream);
 }
 
 cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row_major, uint8_t* scales_tiled,
@@ -252,6 +438,37 @@ cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row
 }
 
 size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner) { return scale_layout_len(outer, inner); }
+
+cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input_is_bf16, uint8_t* packed,
+                                                    uint8_t* scales, float* col_scale, uint32_t tokens,
+                                                    uint32_t in_features, uint32_t terms, cudaStream_t stream) {
+    if (!input || !packed || !scales || !col_scale || tokens == 0 || in_features == 0 || in_features % 16 != 0 ||
+        terms == 0 || terms > 16 || in_features / 8 > 4096 || (reinterpret_cast<uintptr_t>(input) & 15) != 0)
+        return cudaErrorInvalidValue;
+    const uint32_t halves = in_features / 8;
+    const uint32_t passes = (halves + 1023) / 1024;
+    const uint32_t threads = ((halves + passes - 1) / passes + 31) / 32 * 32;
+#define EIDER_EXPAND(TT, PP)                                                                                          \
+    expand_nvfp4_terms_kernel<TT, PP><<<tokens, threads, 0, stream>>>(static_cast<const TT*>(input), packed, scales, \
+                                                                      col_scale, in_features, terms)
+    if (input_is_bf16) {
+        switch (passes) {
+            case 1: EIDER_EXPAND(uint16_t, 1); break;
+            case 2: EIDER_EXPAND(uint16_t, 2); break;
+            case 3: EIDER_EXPAND(uint16_t, 3); break;
+            default: EIDER_EXPAND(uint16_t, 4); break;
+        }
+    } else {
+        switch (passes) {
+            case 1: EIDER_EXPAND(float, 1); break;
+            case 2: EIDER_EXPAND(float, 2); break;
+            case 3: EIDER_EXPAND(float, 3); break;
+            default: EIDER_EXPAND(float, 4); break;
+        }
+    }
+#undef EIDER_EXPAND
+    return cudaGetLastError();
+}
 
 cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(const float* input, uint8_t* quantized_input,
                                                                 float* input_scale, uint32_t rows, uint32_t cols,

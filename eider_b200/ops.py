@@ -341,3 +341,117 @@ def fp8_linear_prequantized_simt(xq: torch.Tensor, s_x: torch.Tensor, wq: torch.
                                                                 _ptr(channel_scale), weight_scale, out.data_ptr(),
                                                                 int(out_dtype == torch.bfloat16), m, n, k, _stream()))
     return out
+
+
+# ---- tensor-core decode (1..64 tokens) ----------------------------------------------------------------
+class Nvfp4DecodePlan:
+    """W4A16 decode linear on tcgen05: y[t] = weight_scale_2 * W . x[t] for up to 64 tokens.  Plays the role of the
+    reference's decode operators (LinearDecodeOp, crates/infer/src/qwen3/infer.rs:3385-3584; Nvfp4DeviceLinear::run_f32_into,
+    crates/infer/src/qwen3/qwen36.rs:6399-6460) with the weight matrix streamed once through the tensor cores."""
+
+    def __init__(self, max_tokens: int, out_features: int, in_features: int):
+        lib = _lib.load()
+        self._lib = lib
+        self.max_tokens, self.n, self.k = max_tokens, out_features, in_features
+        self._plan = lib.eider_b200_nvfp4_decode_create(max_tokens, out_features, in_features)
+        if not self._plan:
+            raise ShapeError(f"unsupported decode shape tokens<={max_tokens} n={out_features} k={in_features}")
+
+    def run(self, x: torch.Tensor, w: ModelOptWeight, out: torch.Tensor | None = None, beta: float = 0.0,
+            c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        tokens, k = x.shape
+        if k != self.k or w.in_features != self.k or w.out_features != self.n or tokens > self.max_tokens:
+            raise ShapeError("operand shapes do not match the plan")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise ShapeError("activation must be f32 or bf16")
+        _need(x, x.dtype, "activation")
+        if out is None:
+            out = torch.empty(tokens, self.n, dtype=out_dtype, device=x.device)
+        if beta != 0.0 and c is None:
+            c = out
+        check("eider_b200_nvfp4_w4a16_gemv_on_stream",
+              self._lib.eider_b200_nvfp4_w4a16_gemv_on_stream(self._plan, x.data_ptr(), int(x.dtype == torch.bfloat16), tokens,
+                                                              w.packed.data_ptr(), w.scales_tiled.data_ptr(),
+                                                              w.weight_scale_2, _ptr(c), out.data_ptr(), beta,
+                                                              int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def status(self) -> int:
+        v = C.c_uint32(0)
+        check("eider_b200_decode_plan_status", self._lib.eider_b200_decode_plan_status(self._plan, C.byref(v)))
+        return v.value
+
+    def close(self) -> None:
+        if self._plan:
+            self._lib.eider_b200_decode_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Fp8DecodePlan:
+    """FP8 W8A8 decode linear with per-token dynamic activation scales (Fp8Linear decode path,
+    crates/infer/src/qwen3/qwen36.rs:2079-2160) on tcgen05 for up to 64 tokens."""
+
+    def __init__(self, max_tokens: int, out_features: int, in_features: int):
+        lib = _lib.load()
+        self._lib = lib
+        self.max_tokens, self.n, self.k = max_tokens, out_features, in_features
+        self._plan = lib.eider_b200_fp8_decode_create(max_tokens, out_features, in_features)
+        if not self._plan:
+            raise ShapeError(f"unsupported decode shape tokens<={max_tokens} n={out_features} k={in_features}")
+
+    def run(self, x: torch.Tensor, wq: torch.Tensor, channel_scale: torch.Tensor | None, weight_scale: float = 1.0,
+            out: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        tokens, k = x.shape
+        if k != self.k or wq.shape != (self.n, self.k) or tokens > self.max_tokens:
+            raise ShapeError("operand shapes do not match the plan")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise ShapeError("activation must be f32 or bf16")
+        _need(x, x.dtype, "activation")
+        _need(wq, torch.uint8, "weight")
+        if out is None:
+            out = torch.empty(tokens, self.n, dtype=out_dtype, device=x.device)
+        check("eider_b200_fp8_linear_decode_on_stream",
+              self._lib.eider_b200_fp8_linear_decode_on_stream(self._plan, x.data_ptr(), int(x.dtype == torch.bfloat16), tokens,
+                                                               wq.data_ptr(), _ptr(channel_scale), weight_scale,
+                                                               out.data_ptr(), int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def status(self) -> int:
+        v = C.c_uint32(0)
+        check("eider_b200_decode_plan_status", self._lib.eider_b200_decode_plan_status(self._plan, C.byref(v)))
+        return v.value
+
+    def close(self) -> None:
+        if self._plan:
+            self._lib.eider_b200_decode_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def expand_nvfp4_terms(x: torch.Tensor, terms: int):
+    """Residual NVFP4 expansion (packed [tokens*terms, K/2], tiled scales, per-row f32 scales)."""
+    lib = _lib.load()
+    tokens, k = x.shape
+    rows = tokens * terms
+    packed = torch.zeros(rows, k // 2, dtype=torch.uint8, device=x.device)
+    scales = torch.zeros(scale_layout_len(rows, k), dtype=torch.uint8, device=x.device)
+    col = torch.zeros(rows, dtype=torch.float32, device=x.device)
+    check("eider_b200_expand_nvfp4_terms_on_stream",
+          lib.eider_b200_expand_nvfp4_terms_on_stream(x.data_ptr(), int(x.dtype == torch.bfloat16), packed.data_ptr(),
+                                                      scales.data_ptr(), col.data_ptr(), tokens, k, terms, _stream()))
+    return packed, scales, col

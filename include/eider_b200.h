@@ -60,6 +60,13 @@ EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_weight_on_stream(const void
 EIDER_B200_API cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row_major,
                                                                       uint8_t* scales_tiled, uint32_t out_features,
                                                                       uint32_t in_features, cudaStream_t stream);
+/* Residual NVFP4 expansion of up to 64 activation rows for the tensor-core decode GEMV: x ~= sum_j g_j deq(q_j),
+ * rows of the result are token * terms + j.  Generalises the reference's residual-term activation quantizer
+ * (crates/eider-cuda/native/sm12x_mma.cu:717-880, two residual terms) to `terms` <= 16. */
+EIDER_B200_API cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input_is_bf16, uint8_t* packed,
+                                                                   uint8_t* scales, float* col_scale, uint32_t tokens,
+                                                                   uint32_t in_features, uint32_t terms,
+                                                                   cudaStream_t stream);
 /* ue4m3_scale_layout_len, crates/eider-cuda/src/format.rs:194-198. */
 EIDER_B200_API size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner);
 
@@ -133,7 +140,32 @@ EIDER_B200_API cudaError_t eider_b200_fp8_gemm_tn_on_stream(void* plan, const ui
                                                             const void* c, void* d, float alpha, float beta,
                                                             const float* token_scale, const float* channel_scale,
                                                             int out_is_bf16, cudaStream_t stream);
-/* Tile-shape override (64, 128 or 256 weight rows per tile) and the kernel status word of a plan
+/* ---- decode (1..64 tokens) on tcgen05 ---------------------------------------------------------- */
+
+/* Supersedes the decode GEMV family: infer_nvfp4_w4a16_matvec_f32* (crates/eider-cuda/src/ffi.rs:3285-3308, CUDA-core
+ * W4A16), infer_cutlass_fp4_gemv_f32_on_stream (crates/eider-cuda/src/ffi.rs:576-588, W4A4) and the sm_121 mma.sync GEMV
+ * (crates/eider-cuda/native/sm12x_mma.cu:521-601).  The weight matrix streams through shared memory once (TMA) and the
+ * tokens ride on the MMA N dimension; the activation keeps 16-bit accuracy through a residual NVFP4 expansion.
+ * y[t][n] = weight_scale_2 * sum_k x[t][k] * w[n][k] (+ beta * c).  The plan owns its scratch (split-K partials,
+ * expanded activations); w_scales are tiled. */
+EIDER_B200_API void* eider_b200_nvfp4_decode_create(uint32_t max_tokens, uint32_t out_features, uint32_t in_features);
+EIDER_B200_API cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* plan, const void* input, int input_is_bf16,
+                                                                 uint32_t tokens, const uint8_t* w_values,
+                                                                 const uint8_t* w_scales_tiled, float weight_scale_2,
+                                                                 const void* c, void* d, float beta, int out_is_bf16,
+                                                                 cudaStream_t stream);
+/* Supersedes infer_fp8_linear_channel_scaled_dynamic_f32_on_stream and its batch forms
+ * (crates/eider-cuda/src/ffi.rs:3110-3162; kernels non_gemm.cu:9826-10011): per-token dynamic E4M3 activations,
+ * per-channel (channel_scale != NULL) or per-tensor (weight_scale) weight scales. */
+EIDER_B200_API void* eider_b200_fp8_decode_create(uint32_t max_tokens, uint32_t out_features, uint32_t in_features);
+EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_on_stream(void* plan, const void* input, int input_is_bf16,
+                                                                  uint32_t tokens, const uint8_t* weight,
+                                                                  const float* channel_scale, float weight_scale, void* d,
+                                                                  int out_is_bf16, cudaStream_t stream);
+EIDER_B200_API void eider_b200_decode_destroy(void* plan);
+EIDER_B200_API cudaError_t eider_b200_decode_plan_status(void* plan, uint32_t* host_status);
+
+/* Tile-shape override (64, 128, 192 or 256 weight rows per tile) and the kernel status word of a plan
  * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
 EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
 EIDER_B200_API cudaError_t eider_b200_gemm_plan_status(void* plan, uint32_t* host_status);

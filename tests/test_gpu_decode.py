@@ -1,0 +1,127 @@
+"""Tensor-core decode path (1..64 tokens): NVFP4 W4A16 through the residual activation expansion and FP8 W8A8,
+against the oracle's host path (unpack + f32 dot, the reference's own CPU form)."""
+import numpy as np
+import pytest
+
+from tests.util import gemm_close, require_cuda, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    require_cuda()
+    from eider_b200 import ops
+    return ops
+
+
+def _dev(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+@pytest.mark.parametrize("terms", [1, 4, 8])
+def test_expansion_reconstructs_activation(ops, oracle, terms):
+    rng = np.random.default_rng(terms)
+    x = rng.standard_normal((3, 2048)).astype(np.float32) * np.exp(rng.uniform(-4, 4, (3, 2048))).astype(np.float32)
+    packed, scales, col = ops.expand_nvfp4_terms(_dev(x), terms)
+    deq = oracle.dequantize_tiled(packed.cpu().numpy(), scales.cpu().numpy()) * col.cpu().numpy()[:, None]
+    rec = deq.reshape(3, terms, -1).sum(axis=1)
+    amax = np.abs(x).max(axis=1, keepdims=True)
+    bound = {1: 0.2, 4: 2e-3, 8: 2e-5}[terms]
+    assert np.all(np.abs(rec - x) <= bound * amax)
+    if terms == 1:  # term 0 is exactly the row-scale quantizer
+        p0, s0, r0 = oracle.quantize_nvfp4_rowscale(x)
+        assert np.array_equal(packed.cpu().numpy(), p0)
+        assert np.array_equal(col.cpu().numpy(), r0)
+
+
+@pytest.mark.parametrize("tokens,n,k", [(1, 128, 256), (1, 13824, 5120), (1, 5120, 13824), (3, 1000, 2048), (8, 7168, 5120),
+                                        (32, 520, 1024), (33, 512, 1024), (64, 2048, 5120)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
+    import torch
+    rng = np.random.default_rng(tokens + n + k)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales, g = oracle.quantize_weight(w)
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    wd = ops.ModelOptWeight.from_checkpoint(_dev(packed), _dev(scales), float(g))
+    plan = ops.Nvfp4DecodePlan(64 if tokens > 32 else 32 if tokens > 1 else 1, n, k)
+    y = plan.run(_dev(x, torch.bfloat16 if dtype == "bf16" else None), wd, out_dtype=torch.float32)
+    y2 = plan.run(_dev(x, torch.bfloat16 if dtype == "bf16" else None), wd, out_dtype=torch.float32)  # counters self-reset
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    ref = oracle.nvfp4_linear_host(x, packed, scales, float(g))
+    # eight residual terms carry the activation essentially exactly; four terms keep ~1e-3 of the block maximum
+    tol = 1e-4 if tokens <= 32 else 1e-2
+    ok, stats = gemm_close(to_np(y), ref, rel=tol, abs_frac=tol)
+    assert ok, stats
+    assert torch.equal(y, y2)
+
+
+def test_nvfp4_decode_bf16_out_and_beta(ops, oracle):
+    import torch
+    rng = np.random.default_rng(9)
+    n, k = 640, 1024
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales, g = oracle.quantize_weight(w)
+    x = oracle.bf16_round(rng.standard_normal((2, k)).astype(np.float32))
+    wd = ops.ModelOptWeight.from_checkpoint(_dev(packed), _dev(scales), float(g))
+    plan = ops.Nvfp4DecodePlan(2, n, k)
+    ref = oracle.nvfp4_linear_host(x, packed, scales, float(g))
+    y = plan.run(_dev(x, torch.bfloat16), wd)
+    ok, stats = gemm_close(to_np(y), ref)
+    assert ok, stats
+    res = rng.standard_normal((2, n)).astype(np.float32)
+    out = _dev(res)
+    plan.run(_dev(x, torch.bfloat16), wd, out=out, beta=1.0)  # residual add fused, as LinearDecodeOp does with beta = 1
+    ok, stats = gemm_close(to_np(out), ref + res, rel=1e-4, abs_frac=1e-4)
+    assert ok, stats
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 32, 64])
+def test_fp8_decode_qkv(ops, oracle, tokens):
+    # FP8 attention projection: K = 5120, N = 7168 (fused QKV), per-channel weight scales, per-token activations
+    import torch
+    n, k = 7168, 5120
+    rng = np.random.default_rng(tokens)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = oracle.bf16_round(rng.standard_normal((tokens, k)).astype(np.float32))
+    wq, ws = oracle.quantize_fp8_weight(w)
+    xq, xs = oracle.quantize_fp8_dynamic(x)
+    plan = ops.Fp8DecodePlan(64, n, k)
+    y = plan.run(_dev(x, torch.bfloat16), _dev(wq), _dev(ws))
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    ref = oracle.fp8_linear(xq, xs, wq, ws)
+    ok, stats = gemm_close(to_np(y), ref)
+    assert ok, stats
+
+
+def test_fp8_decode_small_and_scalar_scale(ops, oracle):
+    import torch
+    n, k = 200, 528
+    rng = np.random.default_rng(4)
+    wq = rng.integers(0, 0x7E, (n, k)).astype(np.uint8) | (rng.integers(0, 2, (n, k)).astype(np.uint8) << 7)
+    x = rng.standard_normal((5, k)).astype(np.float32)
+    xq, xs = oracle.quantize_fp8_dynamic(x)
+    plan = ops.Fp8DecodePlan(8, n, k)
+    y = plan.run(_dev(x), _dev(wq), None, weight_scale=0.03125, out_dtype=torch.float32)
+    ref = oracle.fp8_linear(xq, xs, wq, np.full(n, 0.03125, np.float32))
+    ok, stats = gemm_close(to_np(y), ref, rel=1e-4, abs_frac=1e-4)
+    assert ok, stats
+
+
+def test_decode_rejects_bad_arguments(ops):
+    from eider_b200 import _lib
+    lib = _lib.load()
+    assert not lib.eider_b200_nvfp4_decode_create(65, 128, 128)
+    assert not lib.eider_b200_nvfp4_decode_create(1, 128, 48)
+    with pytest.raises(ops.ShapeError):
+        ops.Nvfp4DecodePlan(0, 128, 128)
+    plan = lib.eider_b200_nvfp4_decode_create(4, 128, 128)
+    assert lib.eider_b200_nvfp4_w4a16_gemv_on_stream(plan, None, 1, 1, None, None, 1.0, None, None, 0.0, 1, None) == 1
+    lib.eider_b200_decode_destroy(plan)
