@@ -48,6 +48,20 @@ SIGNATURES = {
     "eider_b200_decode_plan_status": (_I, [_P, _P]),
     "eider_b200_nvfp4_w4a16_gemv_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _P, _F, _I, _P]),
     "eider_b200_fp8_linear_decode_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _I, _P]),
+    "infer_moe_topk_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _I, _P]),
+    "infer_moe_topk_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _I, _P]),
+    "eider_b200_moe_sort_scratch_bytes": (_SZ, [_U32, _U32]),
+    "eider_b200_moe_sort_routes_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P, _SZ, _P]),
+    "infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _P]),
+    "eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _P]),
+    "infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_moe_grouped_pointer_tables_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
+    "eider_b200_nvfp4_grouped_gemm_supported": (_I, [_U32, _U32, _U32, _U32]),
+    "eider_b200_nvfp4_grouped_gemm_create": (_P, [_U32, _U32, _U32, _U32]),
+    "eider_b200_nvfp4_grouped_gemm_destroy": (None, [_P]),
+    "eider_b200_nvfp4_grouped_gemm_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _P]),
+    "eider_b200_grouped_plan_status": (_I, [_P, _P]),
+    "infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "eider_b200_gemm_plan_set_block_n": (_I, [_P, _U32]),
     "eider_b200_gemm_plan_status": (_I, [_P, _P]),
 }

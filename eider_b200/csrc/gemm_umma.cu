@@ -506,4 +506,46 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
                       d, weight_scale, 0.0f, out_is_bf16, stream);
 }
 
+// ---- routed-MoE grouped GEMM --------------------------------------------------------------------------
+/* Supersedes infer_cutlass_fp4_grouped_gemm_{supported,create,destroy,on_stream} (crates/eider-cuda/src/ffi.rs:643-667,
+ * crates/eider-cuda/native/cutlass_grouped_gemm.cu).  m = out features per expert, max_n = most rows one expert may get,
+ * k = in features.  Instead of device pointer tables the kernel takes the base pointers and the expert offsets the
+ * tables were derived from (infer_moe_grouped_pointer_tables_on_stream computes exactly base + offset), so the TMA
+ * descriptors can be built on the host and nothing is read back. */
+int eider_b200_nvfp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
+    return (m > 0 && max_n > 0 && k > 0 && groups > 0 && m % 128 == 0 && k % 64 == 0) ? 1 : 0;
+}
+
+void* eider_b200_nvfp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
+    if (!eider_b200_nvfp4_grouped_gemm_supported(m, max_n, k, groups)) return nullptr;
+    auto* plan = new GroupedPlan{m, max_n, k, groups, nullptr};
+    if (alloc_status(&plan->status) != cudaSuccess) {
+        delete plan;
+        return nullptr;
+    }
+    return plan;
+}
+
+void eider_b200_nvfp4_grouped_gemm_destroy(void* raw) {
+    auto* plan = static_cast<GroupedPlan*>(raw);
+    if (!plan) return;
+    cudaFree(plan->status);
+    delete plan;
+}
+
+cudaError_t eider_b200_nvfp4_grouped_gemm_on_stream(void* raw, const uint8_t* a_values, const uint8_t* a_scales,
+                                                    const uint8_t* w_values, const uint8_t* w_scales_tiled, uint16_t* output,
+                                                    const float* alpha, const uint32_t* expert_offsets, uint32_t total_routes,
+                                                    cudaStream_t stream) {
+    auto* plan = static_cast<GroupedPlan*>(raw);
+    if (!plan) return cudaErrorInvalidValue;
+    return run_grouped(*plan, a_values, a_scales, w_values, w_scales_tiled, output, alpha, expert_offsets, total_routes, stream);
+}
+
+cudaError_t eider_b200_grouped_plan_status(void* raw, uint32_t* host_status) {
+    auto* plan = static_cast<GroupedPlan*>(raw);
+    if (!plan || !host_status) return cudaErrorInvalidValue;
+    return cudaMemcpy(host_status, plan->status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+}
+
 }  // extern "C"

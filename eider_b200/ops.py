@@ -455,3 +455,210 @@ def expand_nvfp4_terms(x: torch.Tensor, terms: int):
           lib.eider_b200_expand_nvfp4_terms_on_stream(x.data_ptr(), int(x.dtype == torch.bfloat16), packed.data_ptr(),
                                                       scales.data_ptr(), col.data_ptr(), tokens, k, terms, _stream()))
     return packed, scales, col
+
+
+# ---- routed MoE ----------------------------------------------------------------------------------------
+def moe_topk(logits: torch.Tensor, k: int, norm_topk_prob: bool):
+    """moe_topk_f32_batch (crates/eider-cuda/src/kernels/non_gemm.rs:2131-2196): indices [T, k] u32 (as int32 storage)
+    and weights [T, k] f32."""
+    lib = _lib.load()
+    _need(logits, torch.float32, "logits")
+    t, e = logits.shape
+    idx = torch.empty(t, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
+    check("infer_moe_topk_f32_batch_on_stream",
+          lib.infer_moe_topk_f32_batch_on_stream(logits.data_ptr(), idx.data_ptr(), w.data_ptr(), t, e, k,
+                                                 int(bool(norm_topk_prob)), _stream()))
+    return idx, w
+
+
+def moe_scale_tile_bytes(k: int) -> int:
+    return 128 * ((k // 16 + 3) // 4 * 4)
+
+
+class MoeSortedRoutes:
+    """Permutation metadata of one MoE layer call (crates/eider-cuda/src/kernels/non_gemm.rs:2199-2323): expert counts,
+    offsets [E+1], sorted route ids, sorted expert ids and the inverse map, all device-resident (no host readback)."""
+
+    def __init__(self, routes: int, experts: int, device="cuda"):
+        lib = _lib.load()
+        self._lib = lib
+        self.routes, self.experts = routes, experts
+        i32 = dict(dtype=torch.int32, device=device)
+        self.expert_counts = torch.zeros(experts, **i32)
+        self.expert_offsets = torch.zeros(experts + 1, **i32)
+        self.expert_cursors = torch.zeros(experts, **i32)
+        self.sorted_routes = torch.zeros(routes, **i32)
+        self.sorted_experts = torch.zeros(routes, **i32)
+        self.route_to_sorted = torch.zeros(routes, **i32)
+        self._scratch = torch.zeros(max(1, lib.eider_b200_moe_sort_scratch_bytes(routes, experts)), dtype=torch.uint8, device=device)
+
+    def sort(self, indices: torch.Tensor) -> "MoeSortedRoutes":
+        if indices.numel() != self.routes or indices.dtype != torch.int32:
+            raise ShapeError("indices must be int32 with one entry per route")
+        check("eider_b200_moe_sort_routes_on_stream",
+              self._lib.eider_b200_moe_sort_routes_on_stream(indices.data_ptr(), self.expert_counts.data_ptr(),
+                                                             self.expert_offsets.data_ptr(), self.expert_cursors.data_ptr(),
+                                                             self.sorted_routes.data_ptr(), self.sorted_experts.data_ptr(),
+                                                             self.route_to_sorted.data_ptr(), self.routes, self.experts,
+                                                             self._scratch.data_ptr(), self._scratch.numel(), _stream()))
+        return self
+
+
+class MoeSortedNvfp4Rows:
+    """Expert-major NVFP4 rows with per-expert 128-row scale tiles (crates/eider-cuda/src/kernels/non_gemm.rs:2326-2821)."""
+
+    def __init__(self, routes: int, experts: int, k: int, tokens: int, device="cuda"):
+        self._lib = _lib.load()
+        self.routes, self.experts, self.k, self.tokens = routes, experts, k, tokens
+        self.tile_bytes = moe_scale_tile_bytes(k)
+        self.packed = torch.zeros(routes, k // 2, dtype=torch.uint8, device=device)
+        self.scales = torch.zeros(((routes + 127) // 128 + experts) * self.tile_bytes, dtype=torch.uint8, device=device)
+        self.source_packed = torch.zeros(tokens, k // 2, dtype=torch.uint8, device=device)
+        self.source_scales = torch.zeros(scale_layout_len(tokens, k), dtype=torch.uint8, device=device)
+
+    def gather_quantize(self, x: torch.Tensor, routes: MoeSortedRoutes, routes_per_row: int) -> "MoeSortedNvfp4Rows":
+        t, k = x.shape
+        if k != self.k or t != self.tokens:
+            raise ShapeError("input does not match the buffer")
+        name = ("infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream" if x.dtype == torch.float32
+                else "eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream")
+        _need(x, x.dtype, "input")
+        fn = getattr(self._lib, name)
+        check(name, fn(x.data_ptr(), routes.sorted_routes.data_ptr(), routes.sorted_experts.data_ptr(),
+                       routes.expert_offsets.data_ptr(), self.source_packed.data_ptr(), self.source_scales.data_ptr(),
+                       self.packed.data_ptr(), self.scales.data_ptr(), t, self.routes, routes_per_row, k, self.tile_bytes,
+                       _stream()))
+        return self
+
+    def silu_mul_halves_quantize(self, gate_up: torch.Tensor, routes: MoeSortedRoutes) -> "MoeSortedNvfp4Rows":
+        _need(gate_up, torch.bfloat16, "gate_up")
+        if gate_up.shape != (self.routes, 2 * self.k):
+            raise ShapeError("gate_up must be [routes, 2 * in_features]")
+        check("infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream",
+              self._lib.infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(
+                  gate_up.data_ptr(), routes.sorted_experts.data_ptr(), routes.expert_offsets.data_ptr(),
+                  self.packed.data_ptr(), self.scales.data_ptr(), self.routes, self.k, self.tile_bytes, _stream()))
+        return self
+
+
+@dataclass
+class GroupedNvfp4Weights:
+    """Stacked per-expert NVFP4 weights [E, N, K/2] with tiled scales over the stacked [E*N, K] matrix and one
+    weight_scale_2 per expert (Qwen36GroupedMoeWeights, crates/infer/src/qwen3/qwen36.rs:3261-3330)."""
+    packed: torch.Tensor
+    scales_row_major: torch.Tensor
+    scales_tiled: torch.Tensor
+    alpha: torch.Tensor  # [E] f32
+    experts: int
+    out_features: int
+    in_features: int
+
+    @staticmethod
+    def from_checkpoint(packed: torch.Tensor, scales_row_major: torch.Tensor, weight_scale_2: torch.Tensor) -> "GroupedNvfp4Weights":
+        e, n, kh = packed.shape
+        flat = ModelOptWeight.from_checkpoint(packed.reshape(e * n, kh), scales_row_major.reshape(e * n, kh * 2 // 16), 1.0)
+        return GroupedNvfp4Weights(packed, scales_row_major, flat.scales_tiled, weight_scale_2.to(torch.float32).contiguous(),
+                                   e, n, kh * 2)
+
+    @staticmethod
+    def quantize(weights: torch.Tensor) -> "GroupedNvfp4Weights":
+        """[E, N, K] f32/bf16 -> per-expert ModelOpt quantization (own global scale per expert)."""
+        e, n, k = weights.shape
+        packs, scs, alphas = [], [], []
+        for i in range(e):
+            w = ModelOptWeight.quantize(weights[i].contiguous())
+            packs.append(w.packed)
+            scs.append(w.scales_row_major)
+            alphas.append(w.weight_scale_2)
+        return GroupedNvfp4Weights.from_checkpoint(torch.stack(packs), torch.stack(scs),
+                                                   torch.tensor(alphas, dtype=torch.float32, device=weights.device))
+
+
+class Fp4GroupedGemmPlan:
+    """CutlassFp4GroupedGemmPlan (crates/eider-cuda/src/cublaslt/fp4_tn.rs:1160-1278): per expert
+    D_e = alpha_e * X_e . W_e^T, bf16 [route, m], token counts stay on the device."""
+
+    def __init__(self, m: int, max_n: int, k: int, groups: int):
+        lib = _lib.load()
+        if not lib.eider_b200_nvfp4_grouped_gemm_supported(m, max_n, k, groups):
+            raise ShapeError(f"unsupported grouped GEMM m={m} k={k} groups={groups}")
+        self._lib = lib
+        self.m, self.max_n, self.k, self.groups = m, max_n, k, groups
+        self._plan = lib.eider_b200_nvfp4_grouped_gemm_create(m, max_n, k, groups)
+        if not self._plan:
+            raise RuntimeError("eider_b200_nvfp4_grouped_gemm_create failed")
+
+    def run(self, rows: MoeSortedNvfp4Rows, w: GroupedNvfp4Weights, routes: MoeSortedRoutes,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+        if rows.k != self.k or w.in_features != self.k or w.out_features != self.m or w.experts != self.groups:
+            raise ShapeError("operand shapes do not match the plan")
+        if out is None:
+            out = torch.empty(rows.routes, self.m, dtype=torch.bfloat16, device=rows.packed.device)
+        check("eider_b200_nvfp4_grouped_gemm_on_stream",
+              self._lib.eider_b200_nvfp4_grouped_gemm_on_stream(self._plan, rows.packed.data_ptr(), rows.scales.data_ptr(),
+                                                                w.packed.data_ptr(), w.scales_tiled.data_ptr(), out.data_ptr(),
+                                                                w.alpha.data_ptr(), routes.expert_offsets.data_ptr(),
+                                                                rows.routes, _stream()))
+        return out
+
+    def status(self) -> int:
+        v = C.c_uint32(0)
+        check("eider_b200_grouped_plan_status", self._lib.eider_b200_grouped_plan_status(self._plan, C.byref(v)))
+        return v.value
+
+    def close(self) -> None:
+        if self._plan:
+            self._lib.eider_b200_nvfp4_grouped_gemm_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def moe_weighted_accumulate(routes: MoeSortedRoutes, route_weights: torch.Tensor, sorted_rows: torch.Tensor,
+                            tokens: int, routes_per_row: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """moe_weighted_accumulate_sorted_bf16_batch (crates/eider-cuda/src/kernels/non_gemm.rs:3336+): f32 [tokens, len]."""
+    lib = _lib.load()
+    _need(sorted_rows, torch.bfloat16, "sorted rows")
+    _need(route_weights, torch.float32, "route weights")
+    ln = sorted_rows.shape[1]
+    if out is None:
+        out = torch.empty(tokens, ln, dtype=torch.float32, device=sorted_rows.device)
+    check("infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream",
+          lib.infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream(routes.route_to_sorted.data_ptr(),
+                                                                        route_weights.data_ptr(), sorted_rows.data_ptr(),
+                                                                        out.data_ptr(), tokens, ln, routes_per_row, _stream()))
+    return out
+
+
+class GroupedMoe:
+    """The routed-MoE prefill pipeline of Qwen36MoeWeights::run_batch (crates/infer/src/qwen3/qwen36/batch.rs:6785-6860):
+    top-k -> sort -> gather + quantize -> grouped gate/up GEMM -> SiLU * up + quantize -> grouped down GEMM -> combine."""
+
+    def __init__(self, tokens: int, experts: int, top_k: int, hidden: int, intermediate: int, device="cuda"):
+        self.tokens, self.experts, self.top_k, self.hidden, self.inter = tokens, experts, top_k, hidden, intermediate
+        r = tokens * top_k
+        self.routes = MoeSortedRoutes(r, experts, device)
+        self.gate_up_in = MoeSortedNvfp4Rows(r, experts, hidden, tokens, device)
+        self.down_in = MoeSortedNvfp4Rows(r, experts, intermediate, tokens, device)
+        self.gate_up_plan = Fp4GroupedGemmPlan(2 * intermediate, tokens, hidden, experts)
+        self.down_plan = Fp4GroupedGemmPlan(hidden, tokens, intermediate, experts)
+        self.gate_up_out = torch.empty(r, 2 * intermediate, dtype=torch.bfloat16, device=device)
+        self.down_out = torch.empty(r, hidden, dtype=torch.bfloat16, device=device)
+        self.out = torch.empty(tokens, hidden, dtype=torch.float32, device=device)
+
+    def run(self, x: torch.Tensor, router_logits: torch.Tensor, w_gate_up: GroupedNvfp4Weights, w_down: GroupedNvfp4Weights,
+            norm_topk_prob: bool = True) -> torch.Tensor:
+        idx, weights = moe_topk(router_logits, self.top_k, norm_topk_prob)
+        self.routes.sort(idx.reshape(-1))
+        self.gate_up_in.gather_quantize(x, self.routes, self.top_k)
+        self.gate_up_plan.run(self.gate_up_in, w_gate_up, self.routes, out=self.gate_up_out)
+        self.down_in.silu_mul_halves_quantize(self.gate_up_out, self.routes)
+        self.down_plan.run(self.down_in, w_down, self.routes, out=self.down_out)
+        self.route_weights = weights
+        self.route_indices = idx
+        return moe_weighted_accumulate(self.routes, weights.reshape(-1), self.down_out, self.tokens, self.top_k, out=self.out)

@@ -165,6 +165,63 @@ EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_on_stream(void* plan, co
 EIDER_B200_API void eider_b200_decode_destroy(void* plan);
 EIDER_B200_API cudaError_t eider_b200_decode_plan_status(void* plan, uint32_t* host_status);
 
+/* ---- routed MoE ----------------------------------------------------------------------------------- */
+
+/* crates/eider-cuda/src/ffi.rs:1638 and :1691 (kernel non_gemm.cu:1854-2020): softmax / top-k router. */
+EIDER_B200_API cudaError_t infer_moe_topk_f32_on_stream(const float* logits, uint32_t* out_indices, float* out_weights,
+                                                        uint32_t experts, uint32_t k, int norm_topk_prob,
+                                                        cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_moe_topk_f32_batch_on_stream(const float* logits, uint32_t* out_indices,
+                                                              float* out_weights, uint32_t batch_size, uint32_t experts,
+                                                              uint32_t k, int norm_topk_prob, cudaStream_t stream);
+/* Supersedes infer_moe_sort_routes_on_stream (crates/eider-cuda/src/ffi.rs:1701, kernels non_gemm.cu:2473-2550): same
+ * outputs, but routes of one expert keep ascending route order (the reference's atomic scatter leaves that order
+ * unspecified), which needs `scratch` of eider_b200_moe_sort_scratch_bytes(routes, experts) bytes. */
+EIDER_B200_API size_t eider_b200_moe_sort_scratch_bytes(uint32_t routes, uint32_t experts);
+EIDER_B200_API cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* indices, uint32_t* expert_counts,
+                                                                uint32_t* expert_offsets, uint32_t* expert_cursors,
+                                                                uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                                                uint32_t* route_to_sorted, uint32_t routes, uint32_t experts,
+                                                                void* scratch, size_t scratch_bytes, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1783 (kernels non_gemm.cu:2899-2998): quantize each token once (unit global scale) into
+ * source_packed / source_scales, then scatter the bytes into expert-major rows and per-expert 128-row scale tiles. */
+EIDER_B200_API cudaError_t infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream(
+    const float* input, const uint32_t* sorted_routes, const uint32_t* sorted_experts, const uint32_t* expert_offsets,
+    uint8_t* source_packed, uint8_t* source_scales, uint8_t* packed, uint8_t* scales, uint32_t rows, uint32_t routes,
+    uint32_t routes_per_row, uint32_t in_features, uint32_t scale_tile_bytes, cudaStream_t stream);
+EIDER_B200_API cudaError_t eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream(
+    const uint16_t* input, const uint32_t* sorted_routes, const uint32_t* sorted_experts, const uint32_t* expert_offsets,
+    uint8_t* source_packed, uint8_t* source_scales, uint8_t* packed, uint8_t* scales, uint32_t rows, uint32_t routes,
+    uint32_t routes_per_row, uint32_t in_features, uint32_t scale_tile_bytes, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1754 (kernel non_gemm.cu:2805-2897). */
+EIDER_B200_API cudaError_t infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(
+    const uint16_t* gate_up, const uint32_t* sorted_experts, const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales,
+    uint32_t routes, uint32_t in_features, uint32_t scale_tile_bytes, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1799 (kernel non_gemm.cu:3066-3110). */
+EIDER_B200_API cudaError_t infer_moe_grouped_pointer_tables_on_stream(const uint32_t* expert_offsets, const uint8_t* packed,
+                                                                      const uint8_t* scales, uint16_t* output,
+                                                                      const uint8_t** packed_table, const uint8_t** scale_table,
+                                                                      uint16_t** output_table, uint32_t experts,
+                                                                      uint32_t in_features, uint32_t out_features,
+                                                                      uint32_t scale_tile_bytes, cudaStream_t stream);
+/* Supersedes infer_cutlass_fp4_grouped_gemm_{supported,create,destroy,on_stream} (crates/eider-cuda/src/ffi.rs:643-667):
+ * per expert e, rows [offsets[e], offsets[e+1]) of a_values times W_e^T, scaled by alpha[e], bf16 output [route][m].
+ * w_values is [groups][m][k/2], w_scales_tiled the tiled scales of the stacked [groups*m][k] matrix, a_scales the
+ * per-expert tile ranges the quantizers above write. */
+EIDER_B200_API int eider_b200_nvfp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups);
+EIDER_B200_API void* eider_b200_nvfp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups);
+EIDER_B200_API void eider_b200_nvfp4_grouped_gemm_destroy(void* plan);
+EIDER_B200_API cudaError_t eider_b200_nvfp4_grouped_gemm_on_stream(void* plan, const uint8_t* a_values,
+                                                                   const uint8_t* a_scales, const uint8_t* w_values,
+                                                                   const uint8_t* w_scales_tiled, uint16_t* output,
+                                                                   const float* alpha, const uint32_t* expert_offsets,
+                                                                   uint32_t total_routes, cudaStream_t stream);
+EIDER_B200_API cudaError_t eider_b200_grouped_plan_status(void* plan, uint32_t* host_status);
+/* crates/eider-cuda/src/ffi.rs:1931 (kernel non_gemm.cu:3735-3780): un-permute + weighted sum, f32 [rows][len]. */
+EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream(
+    const uint32_t* route_to_sorted, const float* route_weights, const uint16_t* sorted_inputs, float* output, uint32_t rows,
+    uint32_t len, uint32_t routes_per_row, cudaStream_t stream);
+
 /* Tile-shape override (64, 128, 192 or 256 weight rows per tile) and the kernel status word of a plan
  * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
 EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
