@@ -218,18 +218,25 @@ def main():
     x_dev = x_host.cuda()
     xq = ops.Nvfp4Matrix.zeros(M, K, "cuda", row_scales=True)
     y_local = torch.empty(M, n_local, dtype=torch.bfloat16, device="cuda")
-    y_full = torch.empty(world, M, n_local, dtype=torch.bfloat16, device="cuda") if world > 1 else None
     y_host = torch.empty(M, N if world == 1 else n_local * world, dtype=torch.bfloat16).pin_memory()
     plan = ops.Fp4TnMatmulPlan(M, n_local, K)
     if args.block_n:
         plan.set_block_n(args.block_n)
 
-    def step(i, x):
-        w = weights[i % rotate]
+    from eider_b200 import parallel
+    current = {"w": weights[0]}
+
+    def local_linear(x):
         ops.quantize_nvfp4_rowscale(x, out=xq)
-        plan.run(xq, w, out=y_local)
-        if world > 1:
-            dist.all_gather_into_tensor(y_full, y_local)
+        return plan.run(xq, current["w"], out=y_local)
+
+    sharded = parallel.ColumnShardedLinear(N, local_linear)
+    result = {}
+
+    def step(i, x):
+        current["w"] = weights[i % rotate]
+        y = sharded.forward(x)  # N > 1: all-gather of the bf16 slabs + re-assembly to row-major [M, N]
+        result["y"] = y if world == 1 else y.contiguous()
 
     def barrier():
         if world > 1:
@@ -274,10 +281,7 @@ def main():
     def e2e_step(i):
         x_stage.copy_(x_host, non_blocking=True)
         step(i, x_stage)
-        if world == 1:
-            y_host.copy_(y_local, non_blocking=True)
-        else:
-            y_host.view(world, M, n_local).copy_(y_full, non_blocking=True)
+        y_host.copy_(result["y"], non_blocking=True)
 
     for i in range(3):
         e2e_step(i)
