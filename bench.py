@@ -170,6 +170,118 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def _graph_time_us(torch, fn, iters, reps=5):
+    """Best-of-`reps` device time per call of fn(i) when `iters` calls are replayed as one CUDA graph."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(iters):
+                fn(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(reps):
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+    return best
+
+
+def config_decode(args):
+    """Decode configs on one GPU: NVFP4 W4A16 GEMV (M=1, K=5120, N=13824 and the down projection) and the FP8 QKV
+    projection for M in {1, 8, 32, 64}; HBM-bound, reported as GB/s of the algorithmic bytes."""
+    import torch
+
+    from eider_b200 import ops
+    peaks = load_peaks()
+    copies = 6
+    out = {"metric": "decode_hbm_gbs", "unit": "GB/s", "n_gpus": 1, "data": "synthetic", "peak_hbm_gbs": peaks["hbm_gbs"],
+           "peak_source": peaks["source"], "timing": f"CUDA-graph replay of {args.steps} calls, {copies} rotating weight copies",
+           "cases": []}
+    for tokens, n, k in [(1, 13824, 5120), (1, 5120, 13824), (8, 13824, 5120), (64, 13824, 5120)]:
+        ws = [ops.ModelOptWeight.quantize(torch.randn(n, k, device="cuda") * 0.02) for _ in range(copies)]
+        x = torch.randn(tokens, k, device="cuda").to(torch.bfloat16)
+        plan = ops.Nvfp4DecodePlan(tokens, n, k)
+        y = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda")
+        us = _graph_time_us(torch, lambda i: plan.run(x, ws[i % copies], out=y), args.steps)
+        assert plan.status() == 0
+        nbytes = n * k // 2 + n * k // 16 + 2 * tokens * k + 2 * tokens * n + 4
+        case = {"op": "nvfp4_w4a16_decode", "M": tokens, "K": k, "N": n, "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3,
+                "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"]}
+        if tokens == 1:
+            ys = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda")
+            case["cuda_core_gemv_us"] = _graph_time_us(torch, lambda i: ops.nvfp4_w4a16_matvec(x, ws[i % copies], out=ys), args.steps)
+        out["cases"].append(case)
+        del ws
+    n, k = 7168, 5120
+    wq = [torch.randint(0, 120, (n, k), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+    sw = torch.rand(n, device="cuda") * 0.01
+    plan = ops.Fp8DecodePlan(64, n, k)
+    for tokens in (1, 8, 32, 64):
+        x = torch.randn(tokens, k, device="cuda").to(torch.bfloat16)
+        y = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda")
+        us = _graph_time_us(torch, lambda i: plan.run(x, wq[i % copies], sw, out=y), args.steps)
+        assert plan.status() == 0
+        nbytes = n * k + 4 * n + 2 * tokens * k + 2 * tokens * n
+        out["cases"].append({"op": "fp8_w8a8_decode", "M": tokens, "K": k, "N": n, "us": us, "bytes": nbytes,
+                             "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                             "tflops": 2.0 * tokens * n * k / us / 1e6})
+    out["value"] = out["cases"][0]["gbs"]
+    out["config"] = {"workload": "decode: nvfp4 gemv M=1 K=5120 N=13824 (value), down projection, fp8 qkv M in {1,8,32,64}"}
+    print(json.dumps(out), flush=True)
+
+
+def config_moe(args):
+    """Routed-MoE prefill: 4096 tokens, 128 experts, top-8, hidden 2048, intermediate 768, one GPU."""
+    import torch
+
+    from eider_b200 import ops
+    t, e, k8, h, inter = 4096, 128, 8, 2048, 768
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(t, h, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(t, e, device="cuda", generator=g)
+    w_gu = ops.GroupedNvfp4Weights.quantize(torch.randn(e, 2 * inter, h, device="cuda", generator=g) * 0.02)
+    w_dn = ops.GroupedNvfp4Weights.quantize(torch.randn(e, h, inter, device="cuda", generator=g) * 0.02)
+    moe = ops.GroupedMoe(t, e, k8, h, inter)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps * 1e3
+
+    total = timed(lambda: moe.run(x, logits, w_gu, w_dn))
+    assert moe.gate_up_plan.status() == 0 and moe.down_plan.status() == 0
+    idx, wts = ops.moe_topk(logits, k8, True)
+    stages = {
+        "topk": timed(lambda: ops.moe_topk(logits, k8, True)),
+        "sort": timed(lambda: moe.routes.sort(idx.reshape(-1))),
+        "gather_quantize": timed(lambda: moe.gate_up_in.gather_quantize(x, moe.routes, k8)),
+        "gemm_gate_up": timed(lambda: moe.gate_up_plan.run(moe.gate_up_in, w_gu, moe.routes, out=moe.gate_up_out)),
+        "silu_mul_quantize": timed(lambda: moe.down_in.silu_mul_halves_quantize(moe.gate_up_out, moe.routes)),
+        "gemm_down": timed(lambda: moe.down_plan.run(moe.down_in, w_dn, moe.routes, out=moe.down_out)),
+        "combine": timed(lambda: ops.moe_weighted_accumulate(moe.routes, wts.reshape(-1), moe.down_out, t, k8, out=moe.out)),
+    }
+    flops = 2.0 * t * k8 * (h * 2 * inter + inter * h)
+    print(json.dumps({"metric": "moe_prefill_tflops", "value": flops / total / 1e6, "unit": "TFLOP/s", "n_gpus": 1,
+                      "us_per_step": total, "stage_us": stages, "min_bytes_gbs": 375391232 / total / 1e3, "data": "synthetic",
+                      "config": {"workload": "nvfp4 routed moe prefill: 4096 tokens, 128 experts, top-8, H=2048, I=768"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -178,8 +290,14 @@ def main():
     ap.add_argument("--impl", default="eider_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe"],
+                    help="prefill (default, the contract line), or the single-GPU decode / MoE configs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.impl != "reference" and args.config == "decode":
+        return config_decode(args)
+    if args.impl != "reference" and args.config == "moe":
+        return config_moe(args)
 
     if args.impl == "reference":
         reference_arm(args)
