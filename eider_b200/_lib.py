@@ -52,6 +52,8 @@ SIGNATURES = {
     "infer_moe_topk_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _I, _P]),
     "eider_b200_moe_sort_scratch_bytes": (_SZ, [_U32, _U32]),
     "eider_b200_moe_sort_routes_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P, _SZ, _P]),
+    "eider_b200_moe_sort_routes_noalloc_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P]),
+    "eider_b200_moe_sort_noalloc_max_entries": (_SZ, []),
     "infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _P]),
     "eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _P]),
     "infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),

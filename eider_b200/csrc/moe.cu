@@ -330,6 +330,36 @@ __global__ void __launch_bounds__(256) moe_combine_scalar_kernel(const uint32_t*
 }  // namespace
 }  // namespace eider
 
+// ---- scratch for the entry point that must not allocate ------------------------------------------------
+// Fixed-size chunk-histogram table for eider_b200_moe_sort_routes_noalloc_on_stream.  It lives in every GPU context
+// that loads the library (1 MiB) until the process exits.  In host code the name below is only a handle: kernels must
+// be given the device address that cudaGetSymbolAddress returns for the current device.
+namespace eider {
+namespace {
+constexpr uint32_t kNoAllocSortEntries = 262144;  // chunks * experts, 4 bytes each
+static __device__ __align__(256) uint32_t g_noalloc_sort_scratch[kNoAllocSortEntries];
+
+constexpr int kMaxDevices = 64;
+uint32_t* g_noalloc_sort_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch table on the current device, looked up once per device.
+cudaError_t noalloc_sort_scratch(uint32_t** out) {
+    int dev = -1;
+    cudaError_t st = cudaGetDevice(&dev);
+    if (st != cudaSuccess) return st;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (g_noalloc_sort_ptr[dev] == nullptr) {
+        uint32_t* ptr = nullptr;
+        st = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_sort_scratch);
+        if (st != cudaSuccess) return st;
+        g_noalloc_sort_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_sort_ptr[dev];
+    return cudaSuccess;
+}
+}  // namespace
+}  // namespace eider
+
 using namespace eider;
 
 extern "C" {
@@ -382,6 +412,37 @@ cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* indices, uint32
         indices, chunk_hist, expert_offsets, sorted_routes, sorted_experts, route_to_sorted, routes, experts);
     return cudaGetLastError();
 }
+
+// Route sort for callers that cannot hand over scratch memory and must not trigger an allocation: same outputs as
+// eider_b200_moe_sort_routes_on_stream, with the chunk histograms kept in a table that is part of the library image.
+// The first call on a device looks up the table's device address (make that call outside any stream capture); every
+// call shares the one table, so two sorts that overlap on the same GPU corrupt each other.  Nothing in the table has to
+// be cleared between calls: each sort overwrites every entry it later reads.
+cudaError_t eider_b200_moe_sort_routes_noalloc_on_stream(const uint32_t* indices, uint32_t* expert_counts,
+                                                         uint32_t* expert_offsets, uint32_t* expert_cursors,
+                                                         uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                                         uint32_t* route_to_sorted, uint32_t routes, uint32_t experts,
+                                                         cudaStream_t stream) {
+    if (!indices || !expert_counts || !expert_offsets || !expert_cursors || !sorted_routes || !sorted_experts ||
+        !route_to_sorted || routes == 0 || experts == 0 || experts > 1024)
+        return cudaErrorInvalidValue;
+    const uint32_t chunks = (routes + kSortChunk - 1) / kSortChunk;
+    if (static_cast<uint64_t>(chunks) * experts > kNoAllocSortEntries) return cudaErrorInvalidValue;  // beyond the built-in table
+    uint32_t* chunk_hist = nullptr;
+    cudaError_t st = noalloc_sort_scratch(&chunk_hist);
+    if (st != cudaSuccess) return st;
+    moe_chunk_hist_kernel<<<chunks, kSortChunk, experts * sizeof(uint32_t), stream>>>(indices, chunk_hist, routes, experts);
+    st = cudaGetLastError();
+    if (st != cudaSuccess) return st;
+    moe_prefix_kernel<<<1, 1024, 0, stream>>>(chunk_hist, expert_counts, expert_offsets, expert_cursors, chunks, experts);
+    st = cudaGetLastError();
+    if (st != cudaSuccess) return st;
+    moe_scatter_kernel<<<chunks, kSortChunk, (kSortChunk / 32) * experts * sizeof(uint32_t), stream>>>(
+        indices, chunk_hist, expert_offsets, sorted_routes, sorted_experts, route_to_sorted, routes, experts);
+    return cudaGetLastError();
+}
+
+size_t eider_b200_moe_sort_noalloc_max_entries(void) { return kNoAllocSortEntries; }
 
 cudaError_t infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream(const float* input, const uint32_t* sorted_routes,
                                                                     const uint32_t* sorted_experts,

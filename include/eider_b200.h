@@ -183,6 +183,19 @@ EIDER_B200_API cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* 
                                                                 uint32_t* sorted_routes, uint32_t* sorted_experts,
                                                                 uint32_t* route_to_sorted, uint32_t routes, uint32_t experts,
                                                                 void* scratch, size_t scratch_bytes, cudaStream_t stream);
+/* No counterpart in the reference.  The same route sort for callers that can neither pass scratch nor allocate: a
+ * binding that only has the seven output buffers of the reference's sort call to offer, or an engine whose memory plan
+ * is frozen after model load and whose step loop is forbidden to call the allocator (an allocation there would fail a
+ * stream capture or break the budget).  The chunk histograms live in a 1 MiB table inside the library image instead, so
+ * ceil(routes / 256) * experts must not exceed eider_b200_moe_sort_noalloc_max_entries() (262144; larger requests return
+ * cudaErrorInvalidValue).  The first call on each device resolves the table's address and should come before any stream
+ * capture; calls that overlap on one GPU share the table and race. */
+EIDER_B200_API cudaError_t eider_b200_moe_sort_routes_noalloc_on_stream(const uint32_t* indices, uint32_t* expert_counts,
+                                                                        uint32_t* expert_offsets, uint32_t* expert_cursors,
+                                                                        uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                                                        uint32_t* route_to_sorted, uint32_t routes,
+                                                                        uint32_t experts, cudaStream_t stream);
+EIDER_B200_API size_t eider_b200_moe_sort_noalloc_max_entries(void);
 /* crates/eider-cuda/src/ffi.rs:1783 (kernels non_gemm.cu:2899-2998): quantize each token once (unit global scale) into
  * source_packed / source_scales, then scatter the bytes into expert-major rows and per-expert 128-row scale tiles. */
 EIDER_B200_API cudaError_t infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream(
