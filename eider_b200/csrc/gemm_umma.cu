@@ -3,6 +3,7 @@
 // (crates/eider-cuda/src/cublaslt/fp4_tn.rs:264-796, fp8_tn.rs:13-292) and its CUTLASS grouped GEMM
 // (crates/eider-cuda/native/cutlass_grouped_gemm.cu) with one hand-written kernel family.
 #include "gemm_umma.cuh"
+#include "decode_umma.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -95,6 +96,7 @@ struct DecodePlan {
     float* workspace;
     uint32_t* counters;
     uint32_t* status;
+    uint32_t fused_splits, fused_per;  // single-launch path for one or two tokens (0 = not available)
     // activation expansion buffers (NVFP4 W4A16 path)
     uint8_t* act_packed;
     uint8_t* act_scales;
@@ -408,6 +410,45 @@ uint32_t pick_splits(uint32_t k_stages) {
     return splits;
 }
 
+// K splits of the single-launch decode kernel: every CTA keeps one split for the whole launch and walks row tiles, so
+// the cost is (row tiles per CTA group) x (stages per split); at most decode::kMaxLocalStages stages per split.
+void pick_fused_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_out, uint32_t* per_out) {
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    uint32_t best = 0, best_per = 0;
+    float best_cost = 1e30f;
+    for (uint32_t s = 1; s <= k_stages && s <= 32 && s <= sms; ++s) {
+        const uint32_t per = (k_stages + s - 1) / s;
+        if (per > decode::kMaxLocalStages) continue;
+        if (s > 1 && per * (s - 1) >= k_stages) continue;  // last split would be empty
+        const uint32_t groups = sms / s;
+        const uint32_t rounds = (row_tiles + groups - 1) / groups;
+        const float cost = static_cast<float>(rounds * per) + 0.05f * static_cast<float>(s);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = s;
+            best_per = per;
+        }
+    }
+    *splits_out = best;
+    *per_out = best_per;
+}
+
+extern "C++" {
+template <int TERMS, typename XT>
+cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, cudaStream_t stream) {
+    auto kernel = decode::nvfp4_decode_fused_kernel<TERMS, XT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(decode::kSmemBytes));
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    const uint32_t grid = (static_cast<uint32_t>(sm_count()) / p.splits) * p.splits;
+    kernel<<<grid, decode::kThreads, decode::kSmemBytes, stream>>>(map_w, p);
+    return cudaGetLastError();
+}
+}  // extern "C++"
+
 DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t k) {
     if (max_tokens == 0 || max_tokens > 64 || n == 0 || k == 0) return nullptr;
     if (kind == kNvf4 && (k % 32 != 0 || k / 8 > 4096)) return nullptr;
@@ -421,7 +462,9 @@ DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t
     const uint32_t k_bytes = kind == kNvf4 ? k / 2 : k;
     plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK);
     const uint32_t row_tiles = (n + kTileRows - 1) / kTileRows;
-    const size_t ws = static_cast<size_t>(plan->splits) * row_tiles * kTileRows * max_tokens * sizeof(float);
+    if (kind == kNvf4) pick_fused_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->fused_splits, &plan->fused_per);
+    const uint32_t ws_splits = plan->splits > plan->fused_splits ? plan->splits : plan->fused_splits;
+    const size_t ws = static_cast<size_t>(ws_splits) * row_tiles * kTileRows * max_tokens * sizeof(float);
     const uint32_t rows = max_tokens * plan->terms;
     bool ok = cudaMalloc(reinterpret_cast<void**>(&plan->workspace), ws) == cudaSuccess &&
               cudaMalloc(reinterpret_cast<void**>(&plan->counters), row_tiles * sizeof(uint32_t)) == cudaSuccess &&
@@ -479,6 +522,34 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
     if (!plan || plan->kind != kNvf4 || !input || !w_values || !w_scales_tiled || !d || tokens == 0 ||
         tokens > plan->max_tokens)
         return cudaErrorInvalidValue;
+    if (tokens <= 2 && plan->fused_splits != 0 && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
+        // one launch: the activation is expanded inside the GEMV CTAs
+        CUtensorMap map_w;
+        cudaError_t fst = make_map(&map_w, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);
+        if (fst != cudaSuccess) return fst;
+        decode::Params p{};
+        p.x = input;
+        p.tokens = tokens;
+        p.n = plan->n;
+        p.k = plan->k;
+        p.k_stages = (plan->k / 2 + kStageBytesK - 1) / kStageBytesK;
+        p.splits = plan->fused_splits;
+        p.per = plan->fused_per;
+        p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
+        p.sf_w = w_scales_tiled;
+        p.sf_tile_stride = ((plan->k / 16 + 3) / 4 * 4) * 128;
+        p.out = d;
+        p.c_in = c;
+        p.ld_out = plan->n;
+        p.out_is_bf16 = out_is_bf16;
+        p.alpha = weight_scale_2;
+        p.beta = beta;
+        p.workspace = plan->workspace;
+        p.counters = plan->counters;
+        p.status = plan->status;
+        if (beta != 0.0f && !c) return cudaErrorInvalidValue;
+        return input_is_bf16 ? launch_fused_decode<8, uint16_t>(map_w, p, stream) : launch_fused_decode<8, float>(map_w, p, stream);
+    }
     cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
                                                              plan->act_col_scale, tokens, plan->k, plan->terms, stream);
     if (st != cudaSuccess) return st;
