@@ -20,20 +20,38 @@ namespace decode {
 constexpr uint32_t kRows = 128;          // output features per tile (MMA M)
 constexpr uint32_t kCols = 16;           // MMA N: tokens x terms, zero padded
 constexpr uint32_t kStageK = 128;        // bytes of K per stage
-constexpr uint32_t kMaxLocalStages = 8;  // stages of one K split (its activation slice stays resident)
-constexpr uint32_t kRing = 10;           // weight stages in flight
-constexpr uint32_t kThreads = 192;
+constexpr uint32_t kMaxLocalStages = 20; // stages of one K split (its activation slice stays resident): 20 * 256 elements
+constexpr uint32_t kMaxRing = 12;        // weight stages in flight (the host picks how many fit beside the resident slice)
+constexpr uint32_t kMaxExpandThreads = 640;  // one thread per 8 activation elements of the slice
 constexpr uint32_t kWeightTile = kRows * kStageK;  // 16 KB
 constexpr uint32_t kSfTile = 4 * 512;              // scales of one stage for 128 rows
 constexpr uint32_t kActTile = kCols * kStageK;     // 2 KB
-constexpr uint32_t kSmemBytes = kRing * (kWeightTile + kSfTile) + kMaxLocalStages * (kActTile + kSfTile) + 1024 + 512;
+constexpr uint32_t kActSfStage = 4 * 256;          // activation scales of one stage: 16 rows x 16 bytes per MMA, packed
+constexpr uint32_t kSmemBytes = 226 * 1024;        // whole carve-out; ring depth = what is left beside the resident slice
+constexpr uint32_t kFixedBytes = 1024 /*alignment*/ + 256 /*scale window overrun*/ + 512 /*barriers, flags*/;
+__host__ __device__ inline uint32_t ring_depth(uint32_t per) {
+    const uint32_t left = kSmemBytes - kFixedBytes - per * (kActTile + kActSfStage);
+    const uint32_t r = left / (kWeightTile + kSfTile);
+    return r > kMaxRing ? kMaxRing : r;
+}
 constexpr uint32_t kTmemCols = 64;       // 2 x 16 accumulator columns + 16 + 16 scale columns
+
+#ifdef EIDER_GEMM_TRACE
+// bring-up instrumentation: [cta][0] entry, [1] after setup sync, [2] expansion done, [3] first weight stage landed,
+// [4] last MMA committed, [5] epilogue done, [6] producer done
+__device__ long long g_dtrace[256][8];
+#define DTRACE(slot) g_dtrace[blockIdx.x][slot] = clock64()
+#else
+#define DTRACE(slot) ((void)0)
+#endif
 
 struct Params {
     const void* x;            // [tokens][k] bf16 or f32
     uint32_t tokens, n, k;
     uint32_t k_stages;        // ceil(k / 256)
     uint32_t splits, per;     // K splits and stages per split (per <= kMaxLocalStages)
+    uint32_t ring;            // weight stages in flight = ring_depth(per)
+    uint32_t expand_threads;  // multiple of 32, >= 128: threads 64 .. 64 + expand_threads
     uint32_t row_tiles;
     const uint8_t* sf_w;      // tiled weight scales
     uint32_t sf_tile_stride;
@@ -47,47 +65,56 @@ struct Params {
     uint32_t* status;
 };
 
-template <typename XT> __device__ __forceinline__ void load16(const XT* p, float (&v)[16]);
-template <> __device__ __forceinline__ void load16<uint16_t>(const uint16_t* p, float (&v)[16]) {
+template <typename XT> __device__ __forceinline__ void load8(const XT* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<uint16_t>(const uint16_t* p, float (&v)[8]) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p) + h);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            v[8 * h + 2 * j] = __uint_as_float(w[j] << 16);
-            v[8 * h + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-        }
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
     }
 }
-template <> __device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
+    for (int h = 0; h < 2; ++h) {
         const float4 f = __ldg(reinterpret_cast<const float4*>(p) + h);
         v[4 * h] = f.x; v[4 * h + 1] = f.y; v[4 * h + 2] = f.z; v[4 * h + 3] = f.w;
     }
 }
 
+// Decodes through the conversion instructions (the expansion only needs x ~= sum of terms, not the oracle's bit pattern).
+__device__ __forceinline__ float fast_e4m3(uint8_t code) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(code), __NV_E4M3);
+    return __half2float(__half(__half_raw{h.x}));
+}
+__device__ __forceinline__ float2 fast_e2m1x2(uint32_t byte) {
+    const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+    return make_float2(__half2float(__half(__half_raw{h.x})), __half2float(__half(__half_raw{h.y})));
+}
+
 template <int TERMS, typename XT>
-__global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+__global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t kRing = p.ring;
     uint8_t* ring_w = smem;
-    uint8_t* act = ring_w + kRing * kWeightTile;            // [kMaxLocalStages][16 rows][128 B], swizzled
-    uint8_t* ring_sf = act + kMaxLocalStages * kActTile;    // [kRing][2 KB]
-    uint8_t* act_sf = ring_sf + kRing * kSfTile;            // [kMaxLocalStages][2 KB]
-    uint8_t* tail = act_sf + kMaxLocalStages * kSfTile;
-    uint64_t* full = reinterpret_cast<uint64_t*>(tail);     // [kRing]
-    uint64_t* empty = full + kRing;                         // [kRing]
-    uint64_t* acc_full = empty + kRing;                     // [2]
+    uint8_t* act = ring_w + kRing * kWeightTile;            // [per][16 rows][128 B], swizzled
+    uint8_t* ring_sf = act + p.per * kActTile;              // [ring][2 KB]
+    uint8_t* act_sf = ring_sf + kRing * kSfTile;            // [per][4][16 rows][16 B] (+ 256 bytes the last copy window overruns)
+    uint8_t* tail = act_sf + p.per * kActSfStage + 256;
+    uint64_t* full = reinterpret_cast<uint64_t*>(tail);     // [kMaxRing]
+    uint64_t* empty = full + kMaxRing;                      // [kMaxRing]
+    uint64_t* acc_full = empty + kMaxRing;                  // [2]
     uint64_t* acc_empty = acc_full + 2;                     // [2]
     uint64_t* act_ready = acc_empty + 2;                    // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(act_ready + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* last_flag = tmem_slot + 2;
-    float* red = reinterpret_cast<float*>(tmem_slot + 4);   // [4]
-    float* col_scale = red + 4;                              // [kCols]
+    float* red = reinterpret_cast<float*>(tmem_slot + 4);   // [32]
+    float* col_scale = red + 32;                              // [kCols]
 
+    if (threadIdx.x == 0) DTRACE(0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t split = blockIdx.x % p.splits;
     const uint32_t group = blockIdx.x / p.splits, groups = gridDim.x / p.splits;
@@ -95,8 +122,22 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
     const uint32_t stage1 = min(p.k_stages, stage0 + p.per);
     const uint32_t k_bytes = p.k / 2;
 
+    // The expansion warps start on their slice of x (and clear their operand tiles) before the CTA-wide setup barrier,
+    // so the global-load latency hides behind barrier initialisation and the tensor-memory allocation.
+    const uint32_t k_begin = stage0 * 256, k_end = min(p.k, stage1 * 256);
+    const uint32_t nhalf = k_end > k_begin ? (k_end - k_begin) / 8 : 0;  // 8-element half blocks, one per expansion thread
+    float pre[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    if (warp >= 2) {
+        const uint32_t te = threadIdx.x - 64;
+        if (te < nhalf) load8<XT>(static_cast<const XT*>(p.x) + k_begin + te * 8, pre);
+        uint4* z = reinterpret_cast<uint4*>(act);
+        for (uint32_t i = te; i < p.per * kActTile / 16; i += p.expand_threads) z[i] = make_uint4(0, 0, 0, 0);
+        z = reinterpret_cast<uint4*>(act_sf);
+        for (uint32_t i = te; i < (p.per * kActSfStage + 256) / 16; i += p.expand_threads) z[i] = make_uint4(0, 0, 0, 0);
+        if (te < kCols) col_scale[te] = 0.0f;
+    }
     if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < kRing; ++i) {
+        for (uint32_t i = 0; i < kMaxRing; ++i) {
             umma::mbar_init(&full[i], 1);
             umma::mbar_init(&empty[i], 1);
         }
@@ -118,6 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
     __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) DTRACE(1);
 
     if (warp == 0) {
         // ---------------------------------------------------------------- weight producer
@@ -139,6 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
                 __syncwarp();
             }
         }
+        if (leader) DTRACE(6);
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         const bool leader = umma::elect_one();
@@ -161,19 +204,33 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
                 const uint32_t slot = it % kRing, phase = (it / kRing) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[slot], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
                 umma::tc_fence_after();
+                if (leader && it == 0) DTRACE(3);
                 if (leader) {
                     const uint32_t ls = s - stage0;
                     const uint32_t w_lo = w_lo0 + slot * (kWeightTile >> 4), a_lo = a_lo0 + ls * (kActTile >> 4);
-                    const uint32_t wsf_lo = wsf_lo0 + slot * (kSfTile >> 4), asf_lo = asf_lo0 + ls * (kSfTile >> 4);
-                    const uint32_t kb = (s + 1 < p.k_stages) ? 4u : tail_kb;
-                    for (uint32_t j = 0; j < kb; ++j) {
-                        umma::tc_copy_scales(sfw_tmem + j * 4, umma::make_desc(wsf_lo + j * 32, umma::kDescHiScales));
-                        umma::tc_copy_scales(sfa_tmem + j * 4, umma::make_desc(asf_lo + j * 32, umma::kDescHiScales));
+                    const uint32_t wsf_lo = wsf_lo0 + slot * (kSfTile >> 4), asf_lo = asf_lo0 + ls * (kActSfStage >> 4);
+                    const uint32_t first = s > stage0 ? 1u : 0u;
+                    if (s + 1 < p.k_stages || tail_kb == 4) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            umma::tc_copy_scales(sfw_tmem + j * 4, umma::make_desc(wsf_lo + j * 32, umma::kDescHiScales));
+                            umma::tc_copy_scales(sfa_tmem + j * 4, umma::make_desc(asf_lo + j * 16, umma::kDescHiScales));
+                        }
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j)
+                            umma::mma_nvf4(d_tmem, umma::make_desc(w_lo + j * 2, umma::kDescHiSw128),
+                                           umma::make_desc(a_lo + j * 2, umma::kDescHiSw128), idesc, sfw_tmem + j * 4,
+                                           sfa_tmem + j * 4, j == 0 ? first : 1u);
+                    } else {
+                        for (uint32_t j = 0; j < tail_kb; ++j) {
+                            umma::tc_copy_scales(sfw_tmem + j * 4, umma::make_desc(wsf_lo + j * 32, umma::kDescHiScales));
+                            umma::tc_copy_scales(sfa_tmem + j * 4, umma::make_desc(asf_lo + j * 16, umma::kDescHiScales));
+                        }
+                        for (uint32_t j = 0; j < tail_kb; ++j)
+                            umma::mma_nvf4(d_tmem, umma::make_desc(w_lo + j * 2, umma::kDescHiSw128),
+                                           umma::make_desc(a_lo + j * 2, umma::kDescHiSw128), idesc, sfw_tmem + j * 4,
+                                           sfa_tmem + j * 4, j == 0 ? first : 1u);
                     }
-                    for (uint32_t j = 0; j < kb; ++j)
-                        umma::mma_nvf4(d_tmem, umma::make_desc(w_lo + j * 2, umma::kDescHiSw128),
-                                       umma::make_desc(a_lo + j * 2, umma::kDescHiSw128), idesc, sfw_tmem + j * 4, sfa_tmem + j * 4,
-                                       (s > stage0 || j > 0) ? 1u : 0u);
                     umma::tc_commit(&empty[slot]);
                 }
                 __syncwarp();
@@ -181,76 +238,84 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
             if (ok && leader) umma::tc_commit(&acc_full[acc]);
             __syncwarp();
         }
+        if (leader) DTRACE(4);
     } else {
         // ---------------------------------------------------------------- activation expansion, then epilogue
-        const uint32_t te = threadIdx.x - 64;  // 0..127
+        const uint32_t te = threadIdx.x - 64;  // 0 .. expand_threads - 1; the first 128 go on to be the epilogue
         const uint32_t quad = warp & 3;
-        // zero the resident activation tiles and their scales (rows past tokens * TERMS and the K tail stay zero)
-        {
-            uint4* z = reinterpret_cast<uint4*>(act);
-            for (uint32_t i = te; i < kMaxLocalStages * kActTile / 16; i += 128) z[i] = make_uint4(0, 0, 0, 0);
-            z = reinterpret_cast<uint4*>(act_sf);
-            for (uint32_t i = te; i < kMaxLocalStages * kSfTile / 16; i += 128) z[i] = make_uint4(0, 0, 0, 0);
-            if (te < kCols) col_scale[te] = 0.0f;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const uint32_t k_begin = stage0 * 256, k_end = min(p.k, stage1 * 256);
-        const uint32_t nblk = k_end > k_begin ? (k_end - k_begin) / 16 : 0;
+        // (operand tiles were cleared before the setup barrier: rows past tokens * TERMS and the K tail stay zero)
         for (uint32_t m = 0; m < p.tokens; ++m) {
-            float r[16];
+            float r[8];
             float amax = 0.0f;
-            if (te < nblk) {
-                load16<XT>(static_cast<const XT*>(p.x) + static_cast<size_t>(m) * p.k + k_begin + te * 16, r);
+            if (te < nhalf) {
+                if (m == 0) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                    for (int i = 0; i < 8; ++i) r[i] = pre[i];
+                } else {
+                    load8<XT>(static_cast<const XT*>(p.x) + static_cast<size_t>(m) * p.k + k_begin + te * 8, r);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
                     if (!(fabsf(r[i]) < __int_as_float(0x7f800000))) r[i] = 0.0f;
                     amax = fmaxf(amax, fabsf(r[i]));
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) r[i] = 0.0f;
+                for (int i = 0; i < 8; ++i) r[i] = 0.0f;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (lane == 0) red[quad] = amax;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (lane == 0) red[te >> 5] = amax;
+            asm volatile("bar.sync 1, %0;" ::"r"(p.expand_threads) : "memory");
+            {
+                float mx = 0.0f;
+                for (uint32_t w = 0; w < p.expand_threads / 32; ++w) mx = fmaxf(mx, red[w]);
+                amax = mx;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(p.expand_threads) : "memory");
             float g = amax == 0.0f ? 1.0f : amax * (1.0f / kRowScaleDivisor);
-#pragma unroll 1
+            float inv_g = __fdividef(1.0f, g);
+            const uint32_t blk = te >> 1, half = te & 1;
+            const uint32_t ls = blk >> 4, chunk = (blk & 15) >> 1;
+#pragma unroll
             for (uint32_t j = 0; j < TERMS; ++j) {
                 const uint32_t row = m * TERMS + j;
                 if (te == 0) col_scale[row] = g;
-                if (te < nblk) {
-                    const float inv_g = __frcp_rn(g);
-                    float bmax = 0.0f;
+                float bmax = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i] * inv_g));
-                    const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(bmax * (1.0f / 6.0f));
-                    const float sv = e4m3_value(sc);
-                    const float inv = sv == 0.0f ? 0.0f : __frcp_rn(sv) * inv_g;
-                    const float back = sv * g;
-                    uint32_t w[2] = {0u, 0u};
+                for (int i = 0; i < 8; ++i) bmax = fmaxf(bmax, fabsf(r[i] * inv_g));
+                bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));  // the other half of the block
+                const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(bmax * (1.0f / 6.0f));
+                const float sv = fast_e4m3(sc);
+                const float inv = sv == 0.0f ? 0.0f : __fdividef(inv_g, sv);
+                const float back = sv * g;
+                uint32_t w = 0;
 #pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        const uint32_t byte = e2m1x2_code(r[i] * inv, r[i + 1] * inv);
-                        w[i / 8] |= byte << ((i % 8) * 4);
-                        r[i] = fmaf(-e2m1_value(byte & 0xfu), back, r[i]);
-                        r[i + 1] = fmaf(-e2m1_value(byte >> 4), back, r[i + 1]);
-                    }
-                    // block te of the slice: stage te / 16, 16-byte chunk (te % 16) / 2 (XOR-swizzled by the row), half te % 2
-                    const uint32_t ls = te >> 4, chunk = (te & 15) >> 1, half = te & 1;
-                    uint8_t* dst = act + ls * kActTile + row * 128 + ((chunk ^ (row & 7)) << 4) + half * 8;
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-                    // scale byte: 512-byte tile per 64 elements, [row % 32][row / 32][block % 4]
-                    act_sf[ls * kSfTile + ((te & 15) >> 2) * 512 + (row & 31) * 16 + (row >> 5) * 4 + (te & 3)] = sc;
+                for (int i = 0; i < 8; i += 2) {
+                    const uint32_t byte = e2m1x2_code(r[i] * inv, r[i + 1] * inv);
+                    w |= byte << (i * 4);
+                    const float2 q = fast_e2m1x2(byte);  // what the tensor core will read back for these two codes
+                    r[i] = fmaf(-q.x, back, r[i]);
+                    r[i + 1] = fmaf(-q.y, back, r[i + 1]);
+                }
+                if (te < nhalf) {
+                    // block blk of the slice: stage blk / 16, 16-byte chunk (blk % 16) / 2 XOR-swizzled by the row,
+                    // 8 bytes per block, 4 per half
+                    uint8_t* dst = act + ls * kActTile + row * 128 + ((chunk ^ (row & 7)) << 4) + (blk & 1) * 8 + half * 4;
+                    *reinterpret_cast<uint32_t*>(dst) = w;
+                    // scale byte: 256 bytes per 64 elements, [row < 16][16 bytes, the first four = block % 4]; the 512-byte copy
+                    // window of the next group overlaps it, the extra rows feed MMA columns that do not exist
+                    if (half == 0) act_sf[ls * kActSfStage + ((blk & 15) >> 2) * 256 + row * 16 + (blk & 3)] = sc;
                 }
                 g *= 0.25f;
+                inv_g *= 4.0f;
             }
         }
         umma::fence_proxy_async();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(p.expand_threads) : "memory");
         if (te == 0) umma::mbar_arrive(act_ready);
+        if (te == 0) DTRACE(2);
+        if (te >= 128) goto teardown;  // the extra expansion warps are done
 
         uint32_t tile = 0;
         bool ok = true;
@@ -311,17 +376,27 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_decode_fused_kernel(const _
                     __threadfence();
                     if (row_ok)
                         for (uint32_t m = 0; m < p.tokens; ++m) {
+                            // all partials are requested before any is used (one memory round trip), summed in split order
                             float sum = 0.0f;
-                            for (uint32_t s = 0; s < p.splits; ++s)
-                                sum += __ldcg(&p.workspace[(static_cast<size_t>(s) * p.tokens + m) * padded_rows + row]);
+                            for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+                                float v[8];
+#pragma unroll
+                                for (uint32_t u = 0; u < 8; ++u)
+                                    v[u] = (s0 + u < p.splits)
+                                               ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.tokens + m) * padded_rows + row])
+                                               : 0.0f;
+#pragma unroll
+                                for (uint32_t u = 0; u < 8; ++u) sum += v[u];
+                            }
                             emit(m, sum);
                         }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
         }
+        if (threadIdx.x == 64) DTRACE(5);
     }
-
+teardown:
     umma::tc_fence_before();
     __syncthreads();
     if (warp == 1) {

@@ -318,6 +318,9 @@ using namespace eider;
 using namespace eider::gemm;
 
 #ifdef EIDER_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_dtrace(long long* host) {
+    return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 256 * 8);
+}
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
     cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
     if (st != cudaSuccess) return st;
@@ -418,11 +421,13 @@ void pick_fused_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_o
     float best_cost = 1e30f;
     for (uint32_t s = 1; s <= k_stages && s <= 32 && s <= sms; ++s) {
         const uint32_t per = (k_stages + s - 1) / s;
-        if (per > decode::kMaxLocalStages) continue;
+        if (per > decode::kMaxLocalStages || decode::ring_depth(per) < 4) continue;
         if (s > 1 && per * (s - 1) >= k_stages) continue;  // last split would be empty
         const uint32_t groups = sms / s;
         const uint32_t rounds = (row_tiles + groups - 1) / groups;
-        const float cost = static_cast<float>(rounds * per) + 0.05f * static_cast<float>(s);
+        // cycles: four MMAs per stage retire in about 560 cycles whatever their width; meeting the other splits in
+        // global memory costs a few memory round trips at the end of the launch
+        const float cost = static_cast<float>(rounds * per) * 560.0f + (s > 1 ? 5000.0f : 0.0f);
         if (cost < best_cost) {
             best_cost = cost;
             best = s;
@@ -444,7 +449,7 @@ cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& 
         configured = true;
     }
     const uint32_t grid = (static_cast<uint32_t>(sm_count()) / p.splits) * p.splits;
-    kernel<<<grid, decode::kThreads, decode::kSmemBytes, stream>>>(map_w, p);
+    kernel<<<grid, 64 + p.expand_threads, decode::kSmemBytes, stream>>>(map_w, p);
     return cudaGetLastError();
 }
 }  // extern "C++"
@@ -535,6 +540,8 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         p.k_stages = (plan->k / 2 + kStageBytesK - 1) / kStageBytesK;
         p.splits = plan->fused_splits;
         p.per = plan->fused_per;
+        p.ring = decode::ring_depth(p.per);
+        p.expand_threads = p.per * 32 < 128 ? 128 : p.per * 32;
         p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
         p.sf_w = w_scales_tiled;
         p.sf_tile_stride = ((plan->k / 16 + 3) / 4 * 4) * 128;
@@ -548,7 +555,8 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         p.counters = plan->counters;
         p.status = plan->status;
         if (beta != 0.0f && !c) return cudaErrorInvalidValue;
-        return input_is_bf16 ? launch_fused_decode<8, uint16_t>(map_w, p, stream) : launch_fused_decode<8, float>(map_w, p, stream);
+        // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 gets eight
+        return input_is_bf16 ? launch_fused_decode<4, uint16_t>(map_w, p, stream) : launch_fused_decode<8, float>(map_w, p, stream);
     }
     cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
                                                              plan->act_col_scale, tokens, plan->k, plan->terms, stream);

@@ -56,7 +56,10 @@ def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
     assert plan.status() == 0
     ref = oracle.nvfp4_linear_host(x, packed, scales, float(g))
     # eight residual terms carry the activation essentially exactly; four terms keep ~1e-3 of the block maximum
+    # and that is also what the single-launch path uses for one or two bf16 tokens (bf16 itself resolves 4e-3)
     tol = 1e-4 if tokens <= 32 else 1e-2
+    if dtype == "bf16" and tokens <= 2:
+        tol = 2e-3
     ok, stats = gemm_close(to_np(y), ref, rel=tol, abs_frac=tol)
     assert ok, stats
     assert torch.equal(y, y2)
@@ -78,7 +81,7 @@ def test_nvfp4_decode_bf16_out_and_beta(ops, oracle):
     res = rng.standard_normal((2, n)).astype(np.float32)
     out = _dev(res)
     plan.run(_dev(x, torch.bfloat16), wd, out=out, beta=1.0)  # residual add fused, as LinearDecodeOp does with beta = 1
-    ok, stats = gemm_close(to_np(out), ref + res, rel=1e-4, abs_frac=1e-4)
+    ok, stats = gemm_close(to_np(out), ref + res, rel=2e-3, abs_frac=2e-3)  # bf16 input: four residual terms
     assert ok, stats
 
 
