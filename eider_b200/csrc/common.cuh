@@ -122,6 +122,18 @@ __device__ __forceinline__ float div_rn(float x, const Divisor& D) {
     const float aq = fabsf(q0);
     return (aq == 0.0f || aq == __int_as_float(0x7f800000)) ? q0 : q;
 }
+// Row scale of the on-the-fly quantizer: the smallest power of two g with amax / g <= 2688 (1 for amax == 0), so that
+// x / g is exact and the largest block scale still fits E4M3.  2688 = 1.3125 * 2^11.
+__device__ __forceinline__ float row_scale_pow2(float amax) {
+    if (!(amax > 0.0f)) return 1.0f;
+    const uint32_t bits = __float_as_uint(amax);
+    int ge = static_cast<int>(bits >> 23) - 11 + ((bits & 0x7fffffu) > 0x280000u ? 1 : 0);
+    ge = max(1, min(254, ge));
+    return __uint_as_float(static_cast<uint32_t>(ge) << 23);
+}
+// 1 / g for a power of two g in the normal range (exact).
+__device__ __forceinline__ float pow2_reciprocal(float g) { return __uint_as_float((254u << 23) - __float_as_uint(g)); }
+
 // |v| for finite v, 0 otherwise (NaN compares false): the quantizers ignore non-finite values in maxima.
 __device__ __forceinline__ float finite_abs(float v) {
     const float a = fabsf(v);

@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
                 amax = mx;
             }
             asm volatile("bar.sync 1, %0;" ::"r"(p.expand_threads) : "memory");
-            float g = amax == 0.0f ? 1.0f : amax * (1.0f / kRowScaleDivisor);
-            float inv_g = __fdividef(1.0f, g);
+            float g = row_scale_pow2(amax);
+            float inv_g = pow2_reciprocal(g);
             const uint32_t blk = te >> 1, half = te & 1;
             const uint32_t ls = blk >> 4, chunk = (blk & 15) >> 1;
 #pragma unroll

@@ -75,8 +75,19 @@ cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, con
     uint32_t grid = static_cast<uint32_t>(sm_count());
     if (work_items < grid) grid = work_items;
     if (grid == 0) return cudaSuccess;
-    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_rows, map_cols, p);
-    return cudaGetLastError();
+    // Programmatic dependent launch: this kernel's prologue (barriers, tensor memory, first weight tiles) may overlap the
+    // tail of the kernel before it; everything that kernel wrote is read only after griddepcontrol.wait.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, map_rows, map_cols, p);
 }
 
 }  // namespace

@@ -261,6 +261,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (GROUPED) umma::griddep_wait();  // the expert offsets come from a preceding kernel
     GroupWalker walker{p.group_offsets, p.groups, p.col_tiles};
     const long long tr_e0_outer = TRACE_NOW();
     (void)tr_e0_outer;
@@ -273,6 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             uint32_t it = 0;
             TileCoord t;
             bool ok = true;
+            bool dep_waited = false;
             const long long tr_p0 = TRACE_NOW();
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x) {
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
@@ -291,23 +293,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     const bool second_sf = BLOCK_N > 128 && (sf_col_tile0 + 1 < sf_col_tiles);
                     if (kNv) bytes += kb * kScaleTileBytes * (2 + (second_sf ? 1 : 0));
                     umma::mbar_arrive_expect_tx(&full[stage], bytes);
-                    umma::tma_load_2d(smem_a + stage * L::kA, &map_rows, &full[stage], static_cast<int32_t>(s * kStageBytesK),
-                                      static_cast<int32_t>(t.row0));
-                    umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
-                                      static_cast<int32_t>(t.col0));
-                    if (kNv) {
-                        const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
-                        umma::bulk_load_1d(smem_sfa + stage * L::kSfA,
-                                           p.sf_rows + static_cast<size_t>(t.sf_row_tile) * p.sf_tile_stride + k_off,
-                                           kb * kScaleTileBytes, &full[stage]);
-                        umma::bulk_load_1d(smem_sfb + stage * L::kSfB,
-                                           p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
-                                           kb * kScaleTileBytes, &full[stage]);
-                        if (second_sf)
-                            umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes,
-                                               p.sf_cols + static_cast<size_t>(sf_col_tile0 + 1) * p.sf_tile_stride + k_off,
+                    const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
+                    // Weights do not depend on the kernel that ran before this one, activations usually do (the
+                    // quantizer): under a programmatic dependent launch the weight side of the first stage is
+                    // requested before the dependency is awaited.
+                    auto load_rows = [&]() {
+                        umma::tma_load_2d(smem_a + stage * L::kA, &map_rows, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                          static_cast<int32_t>(t.row0));
+                        if (kNv)
+                            umma::bulk_load_1d(smem_sfa + stage * L::kSfA,
+                                               p.sf_rows + static_cast<size_t>(t.sf_row_tile) * p.sf_tile_stride + k_off,
                                                kb * kScaleTileBytes, &full[stage]);
+                    };
+                    auto load_cols = [&]() {
+                        umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                          static_cast<int32_t>(t.col0));
+                        if (kNv) {
+                            umma::bulk_load_1d(smem_sfb + stage * L::kSfB,
+                                               p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
+                                               kb * kScaleTileBytes, &full[stage]);
+                            if (second_sf)
+                                umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes,
+                                                   p.sf_cols + static_cast<size_t>(sf_col_tile0 + 1) * p.sf_tile_stride + k_off,
+                                                   kb * kScaleTileBytes, &full[stage]);
+                        }
+                    };
+                    if (TRANSPOSED) load_rows(); else load_cols();
+                    if (!dep_waited) {
+                        umma::griddep_wait();
+                        dep_waited = true;
                     }
+                    if (TRANSPOSED) load_cols(); else load_rows();
                 }
             }
             if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
@@ -410,6 +426,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        umma::griddep_wait();            // scales / C written by the preceding kernel are read below
         uint32_t tile_count = 0;
         TileCoord t;
         bool ok = true;

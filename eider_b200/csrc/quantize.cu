@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
                                                                    float* __restrict__ row_scales, uint32_t rows, uint32_t k,
                                                                    float input_scale) {
     __shared__ float red[32];
+    // a GEMM launched behind this kernel may begin its prologue right away (it waits for this grid before it reads)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t row = blockIdx.x;
     const T* src = input + static_cast<size_t>(row) * k;
     const uint32_t halves = k / 8;
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
         __syncthreads();
         amax = red[0];
         for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
-        g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+        g = row_scale_pow2(amax);
         if (threadIdx.x == 0) row_scales[row] = g;
     }
     const Divisor dg = make_divisor(g);
@@ -163,6 +165,58 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
     }
 }
 
+// Per-row-scale quantizer of the prefill GEMM: one CTA per row, one thread per 16-element block, the whole grid
+// resident in one wave.  With the power-of-two row scale the first division is an exact multiply, the block maximum
+// needs no shuffle, and the scale byte, its reciprocal and the tile offset are computed once per 16 elements.
+template <typename T, bool TILED>
+__global__ void __launch_bounds__(1024) quantize_nvfp4_rowscale_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
+                                                                       uint8_t* __restrict__ scales,
+                                                                       float* __restrict__ row_scales, uint32_t k) {
+    __shared__ float red[32];
+    __shared__ float row_amax;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t row = blockIdx.x;
+    const uint32_t blocks = k / 16;
+    const uint32_t b = threadIdx.x;
+    float v[16];
+    float amax = 0.0f;
+    if (b < blocks) {
+        Loader<T>::load16(input + static_cast<size_t>(row) * k + b * 16, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, finite_abs(v[i]));
+    }
+    float bmax = amax;  // maximum of this thread's block, before scaling
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) row_amax = m;
+    }
+    __syncthreads();
+    const float g = row_scale_pow2(row_amax);
+    if (threadIdx.x == 0) row_scales[row] = g;
+    if (b >= blocks) return;
+    const float inv_g = pow2_reciprocal(g);
+    bmax *= inv_g;  // exact: scaling by a power of two commutes with the maximum
+    const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(div6_rn(bmax));
+    const float sv = e4m3_value(sc);
+    const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        const float lo = sv == 0.0f ? 0.0f : div_rn(v[i] * inv_g, ds);
+        const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1] * inv_g, ds);
+        w[i / 8] |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << ((i % 8) * 4);
+    }
+    *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (k / 2) + b * 8) = make_uint2(w[0], w[1]);
+    if (TILED) scales[tiled_scale_offset(row, b, k)] = sc;
+    else scales[static_cast<size_t>(row) * blocks + b] = sc;
+}
+
 // Generic kernel: any K (ragged last block, odd K) and any alignment.  One CTA per row, one thread per block.
 template <typename T, int MODE, bool TILED>
 __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
@@ -185,7 +239,7 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const T* __restrict
                 if (isfinite(v[i])) amax = fmaxf(amax, fabsf(v[i]));
         }
         amax = block_max(amax, red);
-        g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+        g = row_scale_pow2(amax);
         if (threadIdx.x == 0) row_scales[row] = g;
     }
     const Divisor dg = make_divisor(g);
@@ -222,6 +276,11 @@ cudaError_t launch_quantize_nvfp4(const T* input, uint8_t* packed, uint8_t* scal
     const bool aligned = (k % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0) &&
                          ((reinterpret_cast<uintptr_t>(packed) & 3) == 0);
     const uint32_t halves = k / 8;
+    if (MODE == kPerRow && aligned && k / 16 <= 1024 && (reinterpret_cast<uintptr_t>(packed) & 7) == 0) {
+        const uint32_t threads = (k / 16 + 31) / 32 * 32;
+        quantize_nvfp4_rowscale_kernel<T, TILED><<<rows, threads, 0, stream>>>(input, packed, scales, row_scales, k);
+        return cudaGetLastError();
+    }
     if (aligned && halves <= 4096) {
         // an even number of threads, a multiple of 32, so both halves of a block sit in one warp
         const uint32_t passes = (halves + 1023) / 1024;
@@ -278,7 +337,7 @@ __global__ void __launch_bounds__(1024) expand_nvfp4_terms_kernel(const T* __res
     __syncthreads();
     amax = red[0];
     for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
-    float g = amax == 0.0f ? 1.0f : __fdiv_rn(amax, kRowScaleDivisor);
+    float g = row_scale_pow2(amax);
     for (uint32_t term = 0; term < terms; ++term) {
         const uint32_t row = token * terms + term;
         if (threadIdx.x == 0) col_scale[row] = g;

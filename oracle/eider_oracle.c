@@ -235,10 +235,27 @@ ORACLE_API void oracle_quantize_nvfp4(const float* x, size_t tokens, size_t k, f
     free(tmp);
 }
 
+/* Row scale of the on-the-fly quantizer: the smallest power of two g with amax / g <= 2688 (= 6 * 448, so the
+ * largest block scale still fits E4M3), 1 for amax == 0, clamped to the normal range.  A power of two makes
+ * x / g exact.  2688 = 1.3125 * 2^11, so g = 2^(e - 11) when the significand of amax is <= 1.3125, else 2^(e - 10). */
+ORACLE_API float oracle_row_scale(float amax) {
+    if (!(amax > 0.0f)) return 1.0f;
+    uint32_t bits;
+    memcpy(&bits, &amax, 4);
+    int e = (int)(bits >> 23);
+    uint32_t mant = bits & 0x7fffffu;
+    int ge = e - 11 + (mant > 0x280000u ? 1 : 0);
+    if (ge < 1) ge = 1;
+    if (ge > 254) ge = 254;
+    uint32_t gb = (uint32_t)ge << 23;
+    float g;
+    memcpy(&g, &gb, 4);
+    return g;
+}
+
 /* Per-row global scale (the on-the-fly quantizer of the prefill GEMM configs; not a
- * reference operator): g_t = amax_t / 2688.0f with one IEEE divide over the finite
- * entries of the row (g_t = 1 when the row has no finite non-zero entry), then the
- * reference quantizer above with input_scale = g_t. */
+ * reference operator): g_t = oracle_row_scale(amax_t) over the finite entries of the row,
+ * then the reference quantizer above with input_scale = g_t. */
 ORACLE_API void oracle_quantize_nvfp4_rowscale(const float* x, size_t tokens, size_t k,
                                                uint8_t* packed, uint8_t* scales,
                                                float* row_scales) {
@@ -251,7 +268,7 @@ ORACLE_API void oracle_quantize_nvfp4_rowscale(const float* x, size_t tokens, si
             float v = x[t * k + i];
             if (isfinite(v)) amax = fmaxf(amax, fabsf(v));
         }
-        float g = amax == 0.0f ? 1.0f : amax / 2688.0f;
+        float g = oracle_row_scale(amax);
         row_scales[t] = g;
         quantize_row(x + t * k, k, g, packed + t * (k / 2), tmp);
         for (size_t b = 0; b < blocks; ++b) scales[oracle_tiled_scale_offset(t, b, k)] = tmp[b];
