@@ -204,6 +204,23 @@ template <> __device__ __forceinline__ void store_chunk32<false>(void* out, size
     for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 
+// 32 fp32 accumulator columns -> 32 bf16 (scaled), written with two 32-byte stores.  A thread owns one output row, so
+// every store instruction of a warp touches 32 different lines; wider stores halve the number of such instructions.
+__device__ __forceinline__ void store_bf16x32_scaled(uint16_t* dst, const uint32_t* raw, float scale) {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[2 * i]) * scale, __uint_as_float(raw[2 * i + 1]) * scale);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * i), "r"(w[8 * i]),
+                     "r"(w[8 * i + 1]), "r"(w[8 * i + 2]), "r"(w[8 * i + 3]), "r"(w[8 * i + 4]), "r"(w[8 * i + 5]),
+                     "r"(w[8 * i + 6]), "r"(w[8 * i + 7])
+                     : "memory");
+}
+
 // KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
 // [col][row] (decode: rows are output features, columns are tokens).  TERMS: consecutive columns that
 // are summed (with their column scales) into one output column.  GROUPED: MoE schedule.
@@ -444,6 +461,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             if (p.row_scale && row_ok) rs *= p.row_scale[row];
             const uint32_t buf = T::kOverlap ? (tile_count & 1) : acc;
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * T::kAccStride;
+            // Fast path (warp-uniform test): a full-width bf16 tile with no column scale and no C input.  64 columns
+            // per step, the next step's tensor-memory loads in flight while this one is converted and stored.
+            constexpr bool kWide = !TRANSPOSED && (BLOCK_N % 64 == 0);
+            bool wide = false;
+            if (kWide) {
+                const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
+                wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
+                       t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+            }
+            if (kWide && wide) {
+                constexpr uint32_t kSteps = BLOCK_N / 64;
+                uint16_t* dst_row = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + t.out_col0;
+                uint32_t raw[2][64];
+                auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (BLOCK_N - 64 - step * 64) : step * 64; };
+                auto issue = [&](uint32_t step, uint32_t (&r)[64]) {
+                    const uint32_t c = col_of(step);
+                    umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    umma::tmem_load_32x32(taddr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                };
+                issue(0, raw[0]);
+#pragma unroll
+                for (uint32_t step = 0; step < kSteps; ++step) {
+                    umma::tmem_load_wait();
+                    if (step + 1 < kSteps) issue(step + 1, raw[(step + 1) & 1]);
+                    if (T::kOverlap && step == 0) {
+                        // the shared columns are in registers: the MMA warp may start the next tile in the other buffer
+                        umma::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+                    }
+                    if (row_ok) {
+                        const uint32_t c = col_of(step);
+                        store_bf16x32_scaled(dst_row + c, &raw[step & 1][0], rs);
+                        store_bf16x32_scaled(dst_row + c + 32, &raw[step & 1][32], rs);
+                    }
+                }
+                if (!T::kOverlap) {
+                    umma::tmem_load_wait();
+                    umma::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+                }
+                continue;
+            }
 #pragma unroll 1
             for (uint32_t ci = 0; ci < BLOCK_N; ci += 32) {
                 constexpr uint32_t kChunk = BLOCK_N < 32 ? BLOCK_N : 32;
