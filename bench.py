@@ -32,6 +32,7 @@ WORKLOAD = "nvfp4_w4a4_prefill_gemm_M512_K5120_N27648"
 METRIC = "nvfp4_gemm_tflops"
 UNIT = "TFLOP/s"
 FLOPS_PER_STEP = 2.0 * M * N * K
+NCU_DRAM_BYTES_FULL_LAUNCH = 81190144 + 4600064
 NOMINAL_NVFP4_TFLOPS = 9000.0
 
 
@@ -387,7 +388,13 @@ def main():
 
     # ---- dominant kernel alone (roofline): CUDA events around the GEMM launches only ----------------------
     gemm_ms = timed(lambda i: plan.run(xq, weights[i % rotate], out=y_local), args.steps) / args.steps
-    quant_ms = timed(lambda i: ops.quantize_nvfp4_rowscale(x_dev, out=xq), args.steps) / args.steps
+    # the quantizer runs for a few microseconds, less than a Python launch takes: time it as one graph of launches
+    quant_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(quant_graph):
+        for _ in range(args.steps):
+            ops.quantize_nvfp4_rowscale(x_dev, out=xq)
+    quant_graph.replay()
+    quant_ms = timed(lambda i: quant_graph.replay(), 1) / args.steps
     if rank == 0:
         clocks = sampler.stop()
     status = plan.status()
@@ -415,13 +422,18 @@ def main():
     achieved = gemm_flops_local / (gemm_ms * 1e-3) / 1e12
     nvfp4_peak = 4.0 * peaks["bf16_tflops"]
     roofline = {
-        "bound": "tensor", "kernel": "gemm_kernel<nvfp4> (tcgen05.mma kind::mxf4nvf4.block_scale)",
+        "bound": "tensor",
+        "kernel": ("gemm_pair_kernel<nvfp4> (tcgen05.mma cta_group::2 kind::mxf4nvf4.block_scale, 256x256 tiles on CTA pairs)"
+                   if plan.block_n == 512 else
+                   f"gemm_kernel<nvfp4, {plan.block_n}> (tcgen05.mma kind::mxf4nvf4.block_scale)"),
         "achieved": achieved, "peak": nvfp4_peak, "unit": "TFLOP/s", "frac": achieved / nvfp4_peak,
         "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TF/s); NVFP4 is not measured by the driver",
         "frac_of_nominal_9pf": achieved / NOMINAL_NVFP4_TFLOPS,
         "kernel_ms": gemm_ms, "quantize_kernel_ms": quant_ms,
         "hbm_gbs_at_min_bytes": (n_local * K * 9 / 16 + M * K * 9 / 16 + 2.0 * M * n_local) / (gemm_ms * 1e-3) / 1e9,
-        "traffic": None,
+        # dram__bytes_read + dram__bytes_write of one launch of this kernel at the full shape (85.8 MB, one ncu
+        # capture, see profiles/), scaled by this rank's share of the weight rows
+        "traffic": NCU_DRAM_BYTES_FULL_LAUNCH * n_local / N, "traffic_unit": "bytes per launch",
     }
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -1,0 +1,365 @@
+// Dense prefill GEMM on CTA pairs: a cluster of two CTAs computes one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 activation rows, its own activation scale tile and
+// only HALF of the 256 weight rows of the tile (the tensor cores of both SMs read both halves), so the
+// shared-memory fill traffic per output tile drops from 54 KB to 38 KB per stage and CTA compared with the
+// one-CTA kernel, which is what bounds that kernel on large prefill shapes.
+//
+// Roles per CTA (192 threads, as in the one-CTA kernel):
+//   warp 0      TMA producer for this CTA's share of the stage;
+//   warp 1      even CTA: issues the scale copies and the MMAs for the pair, and hands stages / accumulators back
+//               to BOTH CTAs with tcgen05.commit on each CTA's barrier;
+//               odd CTA: forwards "my share of stage s has landed" to the even CTA's full barrier;
+//   warps 2..5  epilogue of this CTA's 128 accumulator rows; accumulator hand-back goes to the even CTA.
+// Barriers: full[s] of the even CTA counts two arrivals (its own producer and the odd CTA's forwarder) plus its
+// own bytes; acc_empty of the even CTA counts the eight epilogue warps of the pair.  Every wait is bounded.
+#pragma once
+
+#include "gemm_umma.cuh"
+
+namespace eider {
+namespace gemm {
+
+#ifdef EIDER_GEMM_TRACE
+// Bring-up event log of pair 0 (never in the shipped library): [rank][kind][iteration] global-timer stamps.
+// kinds: 0 producer saw the stage empty, 1 producer issued its copies, 2 MMA warp / forwarder saw the stage full,
+// 3 MMA warp issued the stage's MMAs and commit
+__device__ unsigned long long g_pair_log[2][4][64];
+__device__ __forceinline__ unsigned long long pair_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define PAIR_LOG(kind, it) do { if (pair == 0 && (it) < 64) g_pair_log[rank][kind][it] = pair_now(); } while (0)
+#else
+#define PAIR_LOG(kind, it) ((void)0)
+#endif
+
+constexpr uint32_t kPairN = 256;      // weight rows per pair tile
+constexpr uint32_t kPairHalfN = 128;  // of which each CTA loads half
+
+template <int KIND> struct PairSmem {
+    static constexpr bool kNv = KIND == kNvf4;
+    static constexpr uint32_t kA = kTileRows * kStageBytesK;          // this CTA's 128 rows
+    static constexpr uint32_t kB = kPairHalfN * kStageBytesK;         // this CTA's half of the weight rows
+    static constexpr uint32_t kSfA = kNv ? 4 * kScaleTileBytes : 0;   // scales of this CTA's rows
+    static constexpr uint32_t kSfB = kNv ? 8 * kScaleTileBytes : 0;   // scales of all 256 weight rows
+    static constexpr uint32_t kStage = kA + kB + kSfA + kSfB;
+    static constexpr int kStages = (226u * 1024u) / kStage > 8 ? 8 : static_cast<int>((226u * 1024u) / kStage);
+    static constexpr uint32_t kBytes = kStage * kStages + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct PairTile {
+    uint32_t row_tile;  // this CTA's 128-row tile (may be one past the last when the row-tile count is odd)
+    uint32_t row0;
+    uint32_t col0;      // first weight row of the pair tile
+};
+
+__device__ __forceinline__ bool pair_tile(const Params& p, uint32_t item, uint32_t rank, PairTile& t) {
+    const uint32_t row_pairs = (p.row_tiles + 1) / 2;
+    if (item >= row_pairs * p.col_tiles) return false;
+    const uint32_t rp = item % row_pairs;  // row pairs fastest: neighbouring pairs share the weight tile in L2
+    t.row_tile = rp * 2 + rank;
+    t.row0 = t.row_tile * kTileRows;
+    t.col0 = (item / row_pairs) * kPairN;
+    return true;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, const Params p) {
+    using L = PairSmem<KIND>;
+    using T = TmemPlan<KIND, kPairN>;
+    constexpr bool kNv = KIND == kNvf4;
+    constexpr int STAGES = L::kStages;
+    constexpr uint32_t kAcc = T::kAccStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem_a + STAGES * L::kA;
+    uint8_t* smem_sfa = smem_b + STAGES * L::kB;
+    uint8_t* smem_sfb = smem_sfa + STAGES * L::kSfA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);
+    uint64_t* full = bars;                    // [STAGES]
+    uint64_t* empty = bars + STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;   // [kAcc]
+    uint64_t* acc_empty = acc_full + kAcc;    // [kAcc] (used in the even CTA)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAcc);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rank = umma::cluster_ctarank();
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            umma::mbar_init(&full[i], rank == 0 ? 2 : 1);
+            umma::mbar_init(&empty[i], 1);
+        }
+        for (uint32_t i = 0; i < kAcc; ++i) {
+            umma::mbar_init(&acc_full[i], 1);
+            umma::mbar_init(&acc_empty[i], 8);  // four epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        umma::fence_barrier_init();
+        umma::prefetch_tensormap(&map_rows);
+        umma::prefetch_tensormap(&map_cols);
+    }
+    if (warp == 1) {
+        umma::tmem_alloc_pair(tmem_slot, T::kAlloc);
+        umma::tmem_relinquish_pair();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const long long tr_start = TRACE_NOW();
+    (void)tr_start;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        const bool leader = umma::elect_one();
+        const uint32_t sf_col_tiles = (p.cols + kTileRows - 1) / kTileRows;
+        uint32_t it = 0;
+        PairTile t;
+        bool ok = true;
+        bool dep_waited = false;
+        const long long tr_p0 = TRACE_NOW();
+        (void)tr_p0;
+        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
+            const bool row_sf = kNv && t.row_tile < p.row_tiles;
+            const uint32_t sf_col_tile0 = t.col0 / kTileRows;
+            const bool second_sf = sf_col_tile0 + 1 < sf_col_tiles;
+            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+                const uint32_t stage = it % STAGES;
+                const uint32_t phase = (it / STAGES) & 1;
+                const long long tr_w = TRACE_NOW();
+                (void)tr_w;
+                if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
+                if (!leader) continue;
+                TRACE_ADD(5, TRACE_NOW() - tr_w);
+                PAIR_LOG(0, it);
+                const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
+                uint32_t bytes = L::kA + L::kB;
+                if (kNv) bytes += kb * kScaleTileBytes * ((row_sf ? 1 : 0) + 1 + (second_sf ? 1 : 0));
+                umma::mbar_arrive_expect_tx(&full[stage], bytes);
+                const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
+                // weights first: they do not depend on the kernel that ran before this one
+                umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                  static_cast<int32_t>(t.col0 + rank * kPairHalfN));
+                if (kNv) {
+                    umma::bulk_load_1d(smem_sfb + stage * L::kSfB, p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
+                                       kb * kScaleTileBytes, &full[stage]);
+                    if (second_sf)
+                        umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes,
+                                           p.sf_cols + static_cast<size_t>(sf_col_tile0 + 1) * p.sf_tile_stride + k_off,
+                                           kb * kScaleTileBytes, &full[stage]);
+                }
+                if (!dep_waited) {
+                    umma::griddep_wait();
+                    dep_waited = true;
+                }
+                umma::tma_load_2d(smem_a + stage * L::kA, &map_rows, &full[stage], static_cast<int32_t>(s * kStageBytesK),
+                                  static_cast<int32_t>(t.row0));
+                if (row_sf)
+                    umma::bulk_load_1d(smem_sfa + stage * L::kSfA, p.sf_rows + static_cast<size_t>(t.row_tile) * p.sf_tile_stride + k_off,
+                                       kb * kScaleTileBytes, &full[stage]);
+                PAIR_LOG(1, it);
+            }
+        }
+        if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
+    } else if (warp == 1 && rank != 0) {
+        // ------------------------------------------------------------------ odd CTA: forward stage arrivals
+        const bool leader = umma::elect_one();
+        const uint32_t full0_remote = umma::map_to_cta(umma::smem_u32(&full[0]), 0);
+        uint32_t it = 0;
+        PairTile t;
+        bool ok = true;
+        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
+            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+                const uint32_t stage = it % STAGES;
+                const uint32_t phase = (it / STAGES) & 1;
+                const long long tr_f = TRACE_NOW();
+                (void)tr_f;
+                if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
+                if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
+                if (leader) PAIR_LOG(2, it);
+                if (leader) umma::mbar_arrive_cluster(full0_remote + stage * 8);
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ even CTA: MMA issuer for the pair
+        const bool leader = umma::elect_one();
+        constexpr uint32_t idesc = kNv ? umma::idesc_nvf4_pair(kPairN) : umma::idesc_f8_pair(kPairN);
+        const uint32_t a_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_a));
+        const uint32_t b_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_b));
+        const uint32_t sfa_lo0 = umma::desc_lo_scales(umma::smem_u32(smem_sfa));
+        const uint32_t sfb_lo0 = umma::desc_lo_scales(umma::smem_u32(smem_sfb));
+        const uint32_t sfa_tmem = tmem_base + T::kSfAOffset;
+        const uint32_t sfb_tmem = tmem_base + T::kSfBOffset;
+        const uint32_t empty0_local = umma::smem_u32(&empty[0]);
+        const uint32_t accfull0_local = umma::smem_u32(&acc_full[0]);
+        const uint32_t tail_kb = ((p.k_bytes - (p.k_stages - 1) * kStageBytesK) + 31) / 32;  // MMAs in the last stage
+        uint32_t it = 0, tile_count = 0;
+        PairTile t;
+        bool ok = true;
+        const long long tr_m0 = TRACE_NOW();
+        (void)tr_m0;
+        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
+            const uint32_t acc = tile_count % kAcc;
+            const uint32_t acc_phase = (tile_count / kAcc) & 1;
+            const long long tr_a = TRACE_NOW();
+            (void)tr_a;
+            if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
+            if (leader) { TRACE_ADD(2, TRACE_NOW() - tr_a); TRACE_ADD(7, 1); }
+            umma::tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
+            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+                const uint32_t stage = it % STAGES;
+                const uint32_t phase = (it / STAGES) & 1;
+                const long long tr_f = TRACE_NOW();
+                (void)tr_f;
+                if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
+                if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
+                umma::tc_fence_after();
+                if (leader) {
+                    PAIR_LOG(2, it);
+                    const uint32_t a_lo = a_lo0 + stage * (L::kA >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (L::kB >> 4);
+                    const uint32_t sfa_lo = sfa_lo0 + stage * (L::kSfA >> 4);
+                    const uint32_t sfb_lo = sfb_lo0 + stage * (L::kSfB >> 4);
+                    const uint32_t nkb = (s + 1 < p.k_stages) ? 4u : tail_kb;
+                    if (nkb == 4) {
+#ifndef EIDER_EXP_SKIP_SFCP
+                        if (kNv) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                umma::tc_copy_scales_pair(sfa_tmem + j * 4, umma::make_desc(sfa_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales_pair(sfb_tmem + j * 8, umma::make_desc(sfb_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales_pair(sfb_tmem + j * 8 + 4, umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
+                            }
+                        }
+#endif
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
+                            const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
+                            const uint32_t accumulate = (s > 0 || j > 0) ? 1u : 0u;
+                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
+                            else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+                        }
+                    } else {
+                        for (uint32_t j = 0; j < nkb; ++j) {
+                            if (kNv) {
+                                umma::tc_copy_scales_pair(sfa_tmem + j * 4, umma::make_desc(sfa_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales_pair(sfb_tmem + j * 8, umma::make_desc(sfb_lo + j * 32, umma::kDescHiScales));
+                                umma::tc_copy_scales_pair(sfb_tmem + j * 8 + 4, umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
+                            }
+                        }
+                        for (uint32_t j = 0; j < nkb; ++j) {
+                            const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
+                            const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
+                            const uint32_t accumulate = (s > 0 || j > 0) ? 1u : 0u;
+                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
+                            else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+                        }
+                    }
+                    // the stage is free in both CTAs once these MMAs (and scale copies) retire
+                    umma::tc_commit_pair_both(empty0_local + stage * 8);
+                    PAIR_LOG(3, it);
+                }
+                __syncwarp();
+            }
+            if (ok && leader) {
+                umma::tc_commit_pair_both(accfull0_local + acc * 8);
+            }
+            __syncwarp();
+        }
+        if (leader) TRACE_ADD(0, TRACE_NOW() - tr_m0);
+    } else {
+        // ------------------------------------------------------------------ epilogue warps (both CTAs)
+        const uint32_t quad = warp & 3;
+        umma::griddep_wait();  // row scales written by the preceding kernel are read below
+        const uint32_t accempty0_remote = umma::map_to_cta(umma::smem_u32(&acc_empty[0]), 0);
+        uint32_t tile_count = 0;
+        PairTile t;
+        bool ok = true;
+        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
+            const uint32_t acc = tile_count % kAcc;
+            const uint32_t acc_phase = (tile_count / kAcc) & 1;
+            const long long tr_w = TRACE_NOW();
+            (void)tr_w;
+            if (!umma::mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
+            if (threadIdx.x == 64) TRACE_ADD(4, TRACE_NOW() - tr_w);
+            umma::tc_fence_after();
+            const uint32_t row = t.row0 + quad * 32 + lane;
+            const bool row_ok = row < p.rows;
+            float rs = p.alpha;
+            if (p.row_scale && row_ok) rs *= p.row_scale[row];
+            const uint32_t buf = T::kOverlap ? (tile_count & 1) : acc;
+            const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * T::kAccStride;
+            // overlapping buffers: buffer 0 shares its last 64 columns, buffer 1 its first ones; drain those first
+            auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (kPairN - 64 - step * 64) : step * 64; };
+            auto issue = [&](uint32_t step, uint32_t (&r)[64]) {
+                const uint32_t c = col_of(step);
+                umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                umma::tmem_load_32x32(taddr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            };
+            const bool wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
+                              (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+            constexpr uint32_t kSteps = kPairN / 64;
+            uint32_t raw[2][64];
+            issue(0, raw[0]);
+#pragma unroll
+            for (uint32_t step = 0; step < kSteps; ++step) {
+                umma::tmem_load_wait();
+                if (step + 1 < kSteps) issue(step + 1, raw[(step + 1) & 1]);
+                if ((T::kOverlap && step == 0) || (!T::kOverlap && step + 1 == kSteps)) {
+                    // (the shared columns of) the accumulator are in registers: the next tile's MMAs may start
+                    umma::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) umma::mbar_arrive_cluster(accempty0_remote + acc * 8);
+                }
+                if (!row_ok) continue;
+                const uint32_t c = col_of(step);
+                if (wide) {
+                    uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + t.col0 + c;
+                    store_bf16x32_scaled(dst, &raw[step & 1][0], rs);
+                    store_bf16x32_scaled(dst + 32, &raw[step & 1][32], rs);
+                } else {
+#pragma unroll
+                    for (uint32_t i = 0; i < 64; ++i) {  // fully unrolled: the accumulator stays in registers
+                        const uint32_t col = t.col0 + c + i;
+                        if (col >= p.cols) continue;
+                        const size_t index = static_cast<size_t>(row) * p.ld_out + col;
+                        float x = __uint_as_float(raw[step & 1][i]) * rs;
+                        if (p.col_scale) x *= p.col_scale[col];
+                        if (p.beta != 0.0f && p.c_in)
+                            x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
+                                                           : static_cast<const float*>(p.c_in)[index], x);
+                        if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
+                        else static_cast<float*>(p.out)[index] = x;
+                    }
+                }
+            }
+        }
+    }
+
+    if (threadIdx.x == 64) TRACE_ADD(3, TRACE_NOW() - tr_start);
+    // ---------------------------------------------------------------------- teardown
+    // Neither CTA may leave (or free tensor memory) while the other can still reach its shared or tensor memory.
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::cluster_sync_all();
+    if (warp == 1) {
+        umma::tc_fence_after();
+        umma::tmem_dealloc_pair(tmem_base, T::kAlloc);
+    }
+}
+
+}  // namespace gemm
+}  // namespace eider

@@ -4,6 +4,7 @@
 // (crates/eider-cuda/native/cutlass_grouped_gemm.cu) with one hand-written kernel family.
 #include "gemm_umma.cuh"
 #include "decode_umma.cuh"
+#include "gemm_pair_umma.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -90,9 +91,49 @@ cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, con
     return cudaLaunchKernelEx(&cfg, kernel, map_rows, map_cols, p);
 }
 
+// CTA-pair kernel: clusters of two along x, as many pairs as can be co-resident (one CTA per SM).
+template <int KIND>
+cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols, const Params& p, uint32_t pair_items,
+                        cudaStream_t stream) {
+    using L = PairSmem<KIND>;
+    auto kernel = gemm_pair_kernel<KIND>;
+    static int max_pairs = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    if (max_pairs == 0) {
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::kBytes));
+        if (st != cudaSuccess) return st;
+        cfg.gridDim = dim3(static_cast<uint32_t>(sm_count()) & ~1u);
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        st = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+        if (st != cudaSuccess) return st;
+        if (clusters <= 0) return cudaErrorLaunchOutOfResources;
+        max_pairs = clusters;
+    }
+    uint32_t grid_pairs = static_cast<uint32_t>(max_pairs);
+    if (pair_items < grid_pairs) grid_pairs = pair_items;
+    if (grid_pairs == 0) return cudaSuccess;
+    cfg.gridDim = dim3(grid_pairs * 2);
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, map_rows, map_cols, p);
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------ plans
+constexpr uint32_t kPairBlockCode = 512;  // DensePlan::block_n value that selects the CTA-pair kernel
+
 struct DensePlan {
     int kind;
     uint32_t m, n, k;       // tokens, out features, in features
@@ -137,6 +178,12 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
     // Fill the machine: prefer 256-wide weight tiles, fall back to narrower ones when the tile count is small.
     const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
+    // Two or more row tiles and enough 256 x 256 tiles for every pair of SMs: CTA pairs (half the weight-tile fill
+    // per CTA).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
+    if (row_tiles >= 2 && (row_tiles % 2 == 0 || row_tiles >= 9)) {
+        const uint32_t pair_items = ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN);
+        if (pair_items >= sms / 2) return kPairBlockCode;
+    }
     for (uint32_t bn : {256u, 128u, 64u}) {
         uint32_t tiles = row_tiles * ((n + bn - 1) / bn);
         if (tiles >= sms || bn == 64u) return bn;
@@ -156,7 +203,8 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
     CUtensorMap map_rows, map_cols;
     cudaError_t st = make_map(&map_rows, x_values, plan.m, k_bytes, k_bytes, kTileRows);
     if (st != cudaSuccess) return st;
-    st = make_map(&map_cols, w_values, plan.n, k_bytes, k_bytes, plan.block_n);
+    // (the CTA-pair kernel loads the weight tile in two 128-row halves)
+    st = make_map(&map_cols, w_values, plan.n, k_bytes, k_bytes, plan.block_n == kPairBlockCode ? kPairHalfN : plan.block_n);
     if (st != cudaSuccess) return st;
     Params p{};
     p.rows = plan.m;
@@ -179,6 +227,13 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
     p.out_cols = plan.n;
     p.splits = 1;
     p.status = plan.status;
+    if (plan.block_n == kPairBlockCode) {
+        // 256 x 256 tiles on CTA pairs
+        p.col_tiles = (plan.n + kPairN - 1) / kPairN;
+        const uint32_t pair_items = ((p.row_tiles + 1) / 2) * p.col_tiles;
+        return nv ? launch_pair<kNvf4>(map_rows, map_cols, p, pair_items, stream)
+                  : launch_pair<kFp8>(map_rows, map_cols, p, pair_items, stream);
+    }
     const uint32_t items = p.row_tiles * p.col_tiles;
 #define EIDER_DENSE(KIND, BN) launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream)
     if (nv) {
@@ -332,6 +387,9 @@ using namespace eider::gemm;
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_dtrace(long long* host) {
     return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 256 * 8);
 }
+extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_pair_log(unsigned long long* host) {
+    return cudaMemcpyFromSymbol(host, eider::gemm::g_pair_log, sizeof(unsigned long long) * 2 * 4 * 64);
+}
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
     cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
     if (st != cudaSuccess) return st;
@@ -377,9 +435,14 @@ cudaError_t eider_b200_nvfp4_gemm_tn_on_stream(void* raw, const uint8_t* x_value
 
 int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     auto* plan = static_cast<DensePlan*>(raw);
-    if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256)) return 0;
+    if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256 && block_n != kPairBlockCode)) return 0;
     plan->block_n = block_n;
     return 1;
+}
+
+uint32_t eider_b200_gemm_plan_block_n(void* raw) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    return plan ? plan->block_n : 0;
 }
 
 cudaError_t eider_b200_gemm_plan_status(void* raw, uint32_t* host_status) {

@@ -465,12 +465,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             // per step, the next step's tensor-memory loads in flight while this one is converted and stored.
             constexpr bool kWide = !TRANSPOSED && (BLOCK_N % 64 == 0);
             bool wide = false;
-            if (kWide) {
+            if constexpr (kWide) {
                 const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
                 wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
                        t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             }
-            if (kWide && wide) {
+            if constexpr (kWide) if (wide) {
                 constexpr uint32_t kSteps = BLOCK_N / 64;
                 uint16_t* dst_row = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + t.out_col0;
                 uint32_t raw[2][64];

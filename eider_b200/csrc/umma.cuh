@@ -233,5 +233,105 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
         : "memory");
 }
 
+// ---- CTA pairs (cluster of two, tcgen05 cta_group::2) -----------------------------------------------
+// One MMA spans two SMs: each CTA supplies its own 128 rows of the row operand and half of the column
+// operand from its own shared memory and holds its 128 accumulator rows in its own tensor memory.  The
+// even CTA of the pair issues; barriers of the other CTA are reached through shared::cluster addresses.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait on a barrier of this CTA that threads (or tensor cores) of the other CTA arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > kWaitLimitCycles) {
+            *abort_flag = 1u;
+            if (status) atomicCAS(status, 0u, code | (blockIdx.x << 8));
+            return false;
+        }
+    }
+}
+// Whole-warp calls, executed by the same warp of both CTAs of the pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// All pair MMAs (and scale copies) issued so far by this thread arrive on the barrier at `cluster_addr`
+// (a shared::cluster address: this CTA's own barrier or, through map_to_cta, the other CTA's).
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same, arriving on the barrier at this shared-memory offset in BOTH CTAs of the pair (one instruction; this is
+// a barrier arrival broadcast, not a data copy).
+__device__ __forceinline__ void tc_commit_pair_both(uint32_t local_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(local_addr),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+// Scale tile copy in both CTAs: each copies from its own shared memory (same offset) into its own tensor memory.
+__device__ __forceinline__ void tc_copy_scales_pair(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Instruction descriptors with M = 256 (128 rows in each CTA).
+__host__ __device__ constexpr uint32_t idesc_f8_pair(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((256u >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_nvf4_pair(uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((256u >> 4) << 24);
+}
+__device__ __forceinline__ void mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+            d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
 }  // namespace umma
 }  // namespace eider

@@ -167,9 +167,14 @@ class Fp4TnMatmulPlan:
         if not self._plan:
             raise RuntimeError("eider_b200_nvfp4_gemm_tn_create failed")
 
+    @property
+    def block_n(self) -> int:
+        """Tile code in use: weight rows per tile, 512 = 256 x 256 tiles on CTA pairs."""
+        return int(self._lib.eider_b200_gemm_plan_block_n(self._plan))
+
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128, 192 or 256, got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
 
     def run(self, x: Nvfp4Matrix, w: ModelOptWeight, out: torch.Tensor | None = None, alpha: float | None = None,
             beta: float = 0.0, c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
@@ -220,9 +225,14 @@ class Fp8TnMatmulPlan:
         if not self._plan:
             raise RuntimeError("eider_b200_fp8_gemm_tn_create failed")
 
+    @property
+    def block_n(self) -> int:
+        """Tile code in use: weight rows per tile, 512 = 256 x 256 tiles on CTA pairs."""
+        return int(self._lib.eider_b200_gemm_plan_block_n(self._plan))
+
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128, 192 or 256, got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
 
     def run(self, xq: torch.Tensor, wq: torch.Tensor, token_scale: torch.Tensor | None,
             channel_scale: torch.Tensor | None, out: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0,

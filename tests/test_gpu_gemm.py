@@ -101,6 +101,25 @@ def test_nvfp4_gemm_random(ops, oracle, m, n, k, block_n):
     _nvfp4_case(ops, oracle, x, w, block_n=block_n, rowscale=True, out_dtype="bf16")
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (130, 264, 1056), (384, 640, 288), (512, 1024, 5120), (1000, 2304, 2048)])
+def test_nvfp4_gemm_cta_pairs(ops, oracle, m, n, k):
+    # tile code 512: 256 x 256 tiles computed by clusters of two CTAs (tcgen05 cta_group::2); odd row-tile counts,
+    # partial tiles in both directions and a K that is not a multiple of the stage depth are all in the list
+    rng = np.random.default_rng(m * 7 + n + k)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    _nvfp4_case(ops, oracle, x, w, block_n=512, rowscale=True, out_dtype="bf16")
+
+
+def test_nvfp4_gemm_cta_pairs_general_epilogue(ops, oracle):
+    # fp32 output and beta * C go through the element-wise epilogue of the pair kernel
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((300, 512)).astype(np.float32)
+    w = rng.standard_normal((328, 512)).astype(np.float32)
+    _nvfp4_case(ops, oracle, x, w, block_n=512, out_dtype="f32")
+    _nvfp4_case(ops, oracle, x, w, block_n=512, beta=0.5, out_dtype="bf16", alpha=0.01)
+
+
 def test_nvfp4_gemm_beta_accumulate(ops, oracle):
     # D = alpha * X.W^T + beta * C with C = D in place (fp4_tn.rs:603-678, residual add fused with beta = 1)
     rng = np.random.default_rng(5)
@@ -160,6 +179,23 @@ def test_fp8_gemm_scaled(ops, oracle, m, n, k):
     y = plan.run(xq, wq, xs, ws, out_dtype=torch.bfloat16)
     assert plan.status() == 0
     ref = oracle.fp8_linear(xqo, xso, wqo, wso)
+    ok, stats = gemm_close(to_np(y), ref)
+    assert ok, stats
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (300, 328, 1040)])
+def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k):
+    import torch
+    rng = np.random.default_rng(m + n + 1)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = oracle.bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    wq, ws = ops.quantize_fp8_weight(_dev(w))
+    xq, xs = ops.quantize_fp8_dynamic(_dev(x, torch.bfloat16))
+    plan = ops.Fp8TnMatmulPlan(m, n, k)
+    plan.set_block_n(512)
+    y = plan.run(xq, wq, xs, ws, out_dtype=torch.bfloat16)
+    assert plan.status() == 0
+    ref = oracle.fp8_linear(xq.cpu().numpy(), xs.cpu().numpy(), wq.cpu().numpy(), ws.cpu().numpy())
     ok, stats = gemm_close(to_np(y), ref)
     assert ok, stats
 
