@@ -19,21 +19,6 @@
 namespace eider {
 namespace gemm {
 
-#ifdef EIDER_GEMM_TRACE
-// Bring-up event log of pair 0 (never in the shipped library): [rank][kind][iteration] global-timer stamps.
-// kinds: 0 producer saw the stage empty, 1 producer issued its copies, 2 MMA warp / forwarder saw the stage full,
-// 3 MMA warp issued the stage's MMAs and commit
-__device__ unsigned long long g_pair_log[2][4][64];
-__device__ __forceinline__ unsigned long long pair_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define PAIR_LOG(kind, it) do { if (pair == 0 && (it) < 64) g_pair_log[rank][kind][it] = pair_now(); } while (0)
-#else
-#define PAIR_LOG(kind, it) ((void)0)
-#endif
-
 constexpr uint32_t kPairN = 256;      // weight rows per pair tile
 constexpr uint32_t kPairHalfN = 128;  // of which each CTA loads half
 
@@ -141,7 +126,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
                 if (!leader) continue;
                 TRACE_ADD(5, TRACE_NOW() - tr_w);
-                PAIR_LOG(0, it);
                 const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
                 uint32_t bytes = L::kA + L::kB;
                 if (kNv) bytes += kb * kScaleTileBytes * ((row_sf ? 1 : 0) + 1 + (second_sf ? 1 : 0));
@@ -167,7 +151,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 if (row_sf)
                     umma::bulk_load_1d(smem_sfa + stage * L::kSfA, p.sf_rows + static_cast<size_t>(t.row_tile) * p.sf_tile_stride + k_off,
                                        kb * kScaleTileBytes, &full[stage]);
-                PAIR_LOG(1, it);
             }
         }
         if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
@@ -186,7 +169,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 (void)tr_f;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
                 if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
-                if (leader) PAIR_LOG(2, it);
                 if (leader) umma::mbar_arrive_cluster(full0_remote + stage * 8);
                 __syncwarp();
             }
@@ -227,14 +209,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
                 umma::tc_fence_after();
                 if (leader) {
-                    PAIR_LOG(2, it);
                     const uint32_t a_lo = a_lo0 + stage * (L::kA >> 4);
                     const uint32_t b_lo = b_lo0 + stage * (L::kB >> 4);
                     const uint32_t sfa_lo = sfa_lo0 + stage * (L::kSfA >> 4);
                     const uint32_t sfb_lo = sfb_lo0 + stage * (L::kSfB >> 4);
                     const uint32_t nkb = (s + 1 < p.k_stages) ? 4u : tail_kb;
                     if (nkb == 4) {
-#ifndef EIDER_EXP_SKIP_SFCP
                         if (kNv) {
 #pragma unroll
                             for (uint32_t j = 0; j < 4; ++j) {
@@ -243,7 +223,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                                 umma::tc_copy_scales_pair(sfb_tmem + j * 8 + 4, umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
                             }
                         }
-#endif
 #pragma unroll
                         for (uint32_t j = 0; j < 4; ++j) {
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
@@ -270,7 +249,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     }
                     // the stage is free in both CTAs once these MMAs (and scale copies) retire
                     umma::tc_commit_pair_both(empty0_local + stage * 8);
-                    PAIR_LOG(3, it);
                 }
                 __syncwarp();
             }

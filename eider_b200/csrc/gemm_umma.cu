@@ -387,9 +387,6 @@ using namespace eider::gemm;
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_dtrace(long long* host) {
     return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 256 * 8);
 }
-extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_pair_log(unsigned long long* host) {
-    return cudaMemcpyFromSymbol(host, eider::gemm::g_pair_log, sizeof(unsigned long long) * 2 * 4 * 64);
-}
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
     cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
     if (st != cudaSuccess) return st;
