@@ -120,35 +120,77 @@ __global__ void __launch_bounds__(kSortChunk) moe_chunk_hist_kernel(const uint32
     for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) chunk_hist[static_cast<size_t>(blockIdx.x) * experts + e] = hist[e];
 }
 
-// one thread per expert: exclusive prefix over chunks (in place), totals, then a block scan over experts
+// Exclusive prefix over chunks per expert (in place), totals, then a block scan over experts.  The chunk range of an
+// expert is split over 1024 / experts threads: each sums its segment with independent loads, the segment bases come from
+// shared memory, and a second pass over the (cache-resident) segment writes the prefixes; the dependent chain is a few
+// loads long instead of one load per chunk.
 __global__ void __launch_bounds__(1024) moe_prefix_kernel(uint32_t* __restrict__ chunk_hist, uint32_t* __restrict__ counts,
                                                           uint32_t* __restrict__ offsets, uint32_t* __restrict__ cursors,
                                                           uint32_t chunks, uint32_t experts) {
     __shared__ uint32_t scan[1024];
-    const uint32_t e = threadIdx.x;
-    uint32_t running = 0;
-    if (e < experts) {
-        for (uint32_t c = 0; c < chunks; ++c) {
+    __shared__ uint32_t partial[1024];
+    const uint32_t parts = 1024 / experts;  // experts <= 1024 is checked on the host
+    const uint32_t e = threadIdx.x % experts;
+    const uint32_t part = threadIdx.x / experts;
+    const bool active = part < parts;
+    const uint32_t seg = (chunks + parts - 1) / parts;
+    const uint32_t c0 = min(chunks, part * seg), c1 = min(chunks, c0 + seg);
+    uint32_t sum = 0;
+    if (active) {
+        uint32_t c = c0;
+        for (; c + 8 <= c1; c += 8) {
+            uint32_t h[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = chunk_hist[static_cast<size_t>(c + i) * experts + e];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += h[i];
+        }
+        for (; c < c1; ++c) sum += chunk_hist[static_cast<size_t>(c) * experts + e];
+        partial[part * experts + e] = sum;
+    }
+    __syncthreads();
+    uint32_t running = 0, total = 0;
+    if (active) {
+        for (uint32_t q = 0; q < parts; ++q) {
+            const uint32_t v = partial[q * experts + e];
+            if (q < part) running += v;
+            total += v;
+        }
+        uint32_t c = c0;
+        for (; c + 8 <= c1; c += 8) {
+            uint32_t h[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] = chunk_hist[static_cast<size_t>(c + i) * experts + e];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                chunk_hist[static_cast<size_t>(c + i) * experts + e] = running;
+                running += h[i];
+            }
+        }
+        for (; c < c1; ++c) {
             const uint32_t h = chunk_hist[static_cast<size_t>(c) * experts + e];
             chunk_hist[static_cast<size_t>(c) * experts + e] = running;
             running += h;
         }
-        counts[e] = running;
     }
-    scan[e] = e < experts ? running : 0;
+    // scan over experts (threads 0 .. experts-1 hold the totals)
+    const uint32_t t = threadIdx.x;
+    const bool owner = t < experts;  // part == 0, e == t
+    if (owner) counts[t] = total;
+    scan[t] = owner ? total : 0;
     __syncthreads();
     for (uint32_t o = 1; o < 1024; o <<= 1) {  // Hillis-Steele inclusive scan
-        const uint32_t add = e >= o ? scan[e - o] : 0;
+        const uint32_t add = t >= o ? scan[t - o] : 0;
         __syncthreads();
-        scan[e] += add;
+        scan[t] += add;
         __syncthreads();
     }
-    if (e < experts) {
-        const uint32_t excl = scan[e] - running;
-        offsets[e] = excl;
-        cursors[e] = excl + running;  // where the reference's atomic cursor ends up (non_gemm.cu:2511)
+    if (owner) {
+        const uint32_t excl = scan[t] - total;
+        offsets[t] = excl;
+        cursors[t] = excl + total;  // where the reference's atomic cursor ends up (non_gemm.cu:2511)
     }
-    if (e == experts - 1) offsets[experts] = scan[e];
+    if (t == experts - 1) offsets[experts] = scan[t];
 }
 
 // stable scatter: routes of one expert keep ascending route order
@@ -185,17 +227,22 @@ __device__ __forceinline__ size_t moe_scale_base(uint32_t expert, const uint32_t
     return ((static_cast<size_t>(offsets[expert]) + 127) / 128 + expert) * tile_bytes;
 }
 
-// Scatter already quantized token rows into expert-major order (second half of non_gemm.cu:2899-2998): packed bytes
-// are copied 16 at a time, scale bytes move from the token-tiled layout to the expert's tile range.
-__global__ void __launch_bounds__(128) moe_scatter_rows_kernel(const uint8_t* __restrict__ src_packed,
-                                                               const uint8_t* __restrict__ src_scales,
-                                                               const uint32_t* __restrict__ sorted_routes,
-                                                               const uint32_t* __restrict__ sorted_experts,
-                                                               const uint32_t* __restrict__ offsets,
-                                                               uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                               uint32_t routes_per_row, uint32_t k, uint32_t tile_bytes,
-                                                               int gather_rows) {
-    const uint32_t sorted = blockIdx.x;
+// Scatter already quantized token rows into expert-major order (second half of non_gemm.cu:2899-2998).  One warp per
+// sorted route: packed bytes move 16 at a time, the row's scale bytes move as the 4-byte words they form in the 128 x 4
+// tile layout (four consecutive blocks of a row are adjacent in both the token-tiled source and the expert's tiles).
+constexpr uint32_t kScatterWarps = 8;
+__global__ void __launch_bounds__(kScatterWarps * 32) moe_scatter_rows_kernel(const uint8_t* __restrict__ src_packed,
+                                                                              const uint8_t* __restrict__ src_scales,
+                                                                              const uint32_t* __restrict__ sorted_routes,
+                                                                              const uint32_t* __restrict__ sorted_experts,
+                                                                              const uint32_t* __restrict__ offsets,
+                                                                              uint8_t* __restrict__ packed,
+                                                                              uint8_t* __restrict__ scales, uint32_t routes,
+                                                                              uint32_t routes_per_row, uint32_t k,
+                                                                              uint32_t tile_bytes, int gather_rows) {
+    const uint32_t sorted = blockIdx.x * kScatterWarps + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (sorted >= routes) return;
     const uint32_t src_row = gather_rows ? sorted_routes[sorted] / routes_per_row : sorted;
     const uint32_t expert = sorted_experts[sorted];
     const uint32_t col = sorted - offsets[expert];
@@ -205,67 +252,71 @@ __global__ void __launch_bounds__(128) moe_scatter_rows_kernel(const uint8_t* __
     if (row_bytes % 16 == 0 && ((reinterpret_cast<uintptr_t>(src_packed) | reinterpret_cast<uintptr_t>(packed)) & 15) == 0) {
         const uint4* s4 = reinterpret_cast<const uint4*>(s1);
         uint4* d4 = reinterpret_cast<uint4*>(d1);
-        for (uint32_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) d4[i] = __ldg(s4 + i);
+        for (uint32_t i = lane; i < row_bytes / 16; i += 32) d4[i] = __ldg(s4 + i);
     } else {  // rows that do not start on 16-byte boundaries (K % 32 != 0): 8-byte words, K % 16 == 0 guarantees those
         const uint2* s2 = reinterpret_cast<const uint2*>(s1);
         uint2* d2 = reinterpret_cast<uint2*>(d1);
-        for (uint32_t i = threadIdx.x; i < row_bytes / 8; i += blockDim.x) d2[i] = __ldg(s2 + i);
+        for (uint32_t i = lane; i < row_bytes / 8; i += 32) d2[i] = __ldg(s2 + i);
     }
     const size_t base = moe_scale_base(expert, offsets, tile_bytes);
-    for (uint32_t b = threadIdx.x; b < k / 16; b += blockDim.x)
+    const uint32_t blocks = k / 16;
+    const bool aligned4 = ((reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(src_scales)) & 3) == 0;
+    const uint32_t words = aligned4 ? blocks / 4 : 0;  // whole groups of four blocks
+    for (uint32_t w = lane; w < words; w += 32)
+        *reinterpret_cast<uint32_t*>(scales + base + tiled_scale_offset(col, w * 4, k)) =
+            __ldg(reinterpret_cast<const uint32_t*>(src_scales + tiled_scale_offset(src_row, w * 4, k)));
+    for (uint32_t b = words * 4 + lane; b < blocks; b += 32)
         scales[base + tiled_scale_offset(col, b, k)] = __ldg(src_scales + tiled_scale_offset(src_row, b, k));
 }
 
 // silu(gate) * up on bf16 halves, then NVFP4 with unit global scale into the expert's scale tiles
-// (non_gemm.cu:2805-2875).  One CTA per sorted route, one thread per 8 products.
-__global__ void __launch_bounds__(1024) moe_silu_mul_quantize_kernel(const uint16_t* __restrict__ gate_up,
-                                                                     const uint32_t* __restrict__ sorted_experts,
-                                                                     const uint32_t* __restrict__ offsets,
-                                                                     uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                                     uint32_t k, uint32_t tile_bytes) {
-    const uint32_t sorted = blockIdx.x;
-    const uint32_t expert = sorted_experts[sorted];
-    const uint32_t col = sorted - offsets[expert];
-    const uint16_t* gate = gate_up + static_cast<size_t>(sorted) * k * 2;
-    const uint16_t* up = gate + k;
-    const size_t base = moe_scale_base(expert, offsets, tile_bytes);
-    uint8_t* prow = packed + static_cast<size_t>(sorted) * (k / 2);
+// (non_gemm.cu:2805-2875).  One thread per 8 products, two neighbouring threads share a 16-element block; the grid is
+// flat over all routes so that a CTA is full whatever the row length.
+__global__ void __launch_bounds__(256) moe_silu_mul_quantize_kernel(const uint16_t* __restrict__ gate_up,
+                                                                    const uint32_t* __restrict__ sorted_experts,
+                                                                    const uint32_t* __restrict__ offsets,
+                                                                    uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                                                                    uint32_t routes, uint32_t k, uint32_t tile_bytes) {
     const uint32_t halves = k / 8;
-    for (uint32_t h0 = 0; h0 < halves; h0 += blockDim.x) {
-        const uint32_t h = h0 + threadIdx.x;
-        float v[8];
-        float amax = 0.0f;
-        if (h < halves) {
-            const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gate + h * 8));
-            const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(up + h * 8));
-            const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+    const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const bool live = unit < static_cast<uint64_t>(routes) * halves;
+    const uint32_t sorted = live ? static_cast<uint32_t>(unit / halves) : 0;
+    const uint32_t h = live ? static_cast<uint32_t>(unit % halves) : 0;
+    float v[8];
+    float amax = 0.0f;
+    if (live) {
+        const uint16_t* gate = gate_up + static_cast<size_t>(sorted) * k * 2;
+        const uint16_t* up = gate + k;
+        const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gate + h * 8));
+        const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(up + h * 8));
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
-                const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
-                v[2 * j] = __fdiv_rn(g0, 1.0f + expf(-g0)) * u0;
-                v[2 * j + 1] = __fdiv_rn(g1, 1.0f + expf(-g1)) * u1;
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(v[i]));
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        for (int j = 0; j < 4; ++j) {
+            const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
+            v[2 * j] = __fdiv_rn(g0, 1.0f + expf(-g0)) * u0;
+            v[2 * j + 1] = __fdiv_rn(g1, 1.0f + expf(-g1)) * u1;
         }
-        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
-        if (h >= halves) continue;
-        const uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(div6_rn(amax));
-        const float sv = e4m3_value(sc);
-        const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
-        uint32_t w = 0;
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
-            const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
-            w |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << (i * 4);
-        }
-        *reinterpret_cast<uint32_t*>(prow + h * 4) = w;
-        if ((h & 1) == 0) scales[base + tiled_scale_offset(col, h >> 1, k)] = sc;
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(v[i]));
+    }
+    // k / 8 is even, so the two halves of a block are lanes 2i and 2i + 1 of one warp and belong to one route
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+    if (!live) return;
+    const uint8_t sc = amax == 0.0f ? 0 : ue4m3_code(div6_rn(amax));
+    const float sv = e4m3_value(sc);
+    const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
+        const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
+        w |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << (i * 4);
+    }
+    *reinterpret_cast<uint32_t*>(packed + static_cast<size_t>(sorted) * (k / 2) + h * 4) = w;
+    if ((h & 1) == 0) {
+        const uint32_t expert = sorted_experts[sorted];
+        scales[moe_scale_base(expert, offsets, tile_bytes) + tiled_scale_offset(sorted - offsets[expert], h >> 1, k)] = sc;
     }
 }
 
@@ -458,9 +509,9 @@ cudaError_t infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream(const float*
     cudaError_t st = infer_quantize_nvfp4_col_major_f32_on_stream(input, source_packed, source_scales, in_features, rows, 1.0f,
                                                                   stream);
     if (st != cudaSuccess) return st;
-    moe_scatter_rows_kernel<<<routes, 128, 0, stream>>>(source_packed, source_scales, sorted_routes, sorted_experts,
-                                                        expert_offsets, packed, scales, routes_per_row, in_features,
-                                                        scale_tile_bytes, 1);
+    moe_scatter_rows_kernel<<<(routes + kScatterWarps - 1) / kScatterWarps, kScatterWarps * 32, 0, stream>>>(
+        source_packed, source_scales, sorted_routes, sorted_experts, expert_offsets, packed, scales, routes, routes_per_row,
+        in_features, scale_tile_bytes, 1);
     return cudaGetLastError();
 }
 
@@ -474,9 +525,9 @@ cudaError_t eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream(
         return cudaErrorInvalidValue;
     cudaError_t st = eider_b200_quantize_nvfp4_bf16_on_stream(input, source_packed, source_scales, in_features, rows, 1.0f, stream);
     if (st != cudaSuccess) return st;
-    moe_scatter_rows_kernel<<<routes, 128, 0, stream>>>(source_packed, source_scales, sorted_routes, sorted_experts,
-                                                        expert_offsets, packed, scales, routes_per_row, in_features,
-                                                        scale_tile_bytes, 1);
+    moe_scatter_rows_kernel<<<(routes + kScatterWarps - 1) / kScatterWarps, kScatterWarps * 32, 0, stream>>>(
+        source_packed, source_scales, sorted_routes, sorted_experts, expert_offsets, packed, scales, routes, routes_per_row,
+        in_features, scale_tile_bytes, 1);
     return cudaGetLastError();
 }
 
@@ -489,10 +540,9 @@ cudaError_t infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(con
     if (!gate_up || !sorted_experts || !expert_offsets || !packed || !scales || routes == 0 || in_features == 0 ||
         in_features % 16 != 0 || scale_tile_bytes == 0 || (reinterpret_cast<uintptr_t>(gate_up) & 15) != 0)
         return cudaErrorInvalidValue;
-    uint32_t threads = (in_features / 8 + 31) / 32 * 32;
-    if (threads > 1024) threads = 1024;
-    moe_silu_mul_quantize_kernel<<<routes, threads, 0, stream>>>(gate_up, sorted_experts, expert_offsets, packed, scales,
-                                                                 in_features, scale_tile_bytes);
+    const uint64_t units = static_cast<uint64_t>(routes) * (in_features / 8);
+    moe_silu_mul_quantize_kernel<<<static_cast<uint32_t>((units + 255) / 256), 256, 0, stream>>>(
+        gate_up, sorted_experts, expert_offsets, packed, scales, routes, in_features, scale_tile_bytes);
     return cudaGetLastError();
 }
 
