@@ -39,8 +39,8 @@ constexpr uint32_t kTmemCols = 64;       // 2 x 16 accumulator columns + 16 + 16
 #ifdef EIDER_GEMM_TRACE
 // bring-up instrumentation: [cta][0] entry, [1] after setup sync, [2] expansion done, [3] first weight stage landed,
 // [4] last MMA committed, [5] epilogue done, [6] producer done
-__device__ long long g_dtrace[256][8];
-#define DTRACE(slot) g_dtrace[blockIdx.x][slot] = clock64()
+__device__ long long g_dtrace[512][8];
+#define DTRACE(slot) g_dtrace[blockIdx.x & 511][slot] = clock64()
 #else
 #define DTRACE(slot) ((void)0)
 #endif
@@ -122,14 +122,13 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
     const uint32_t stage1 = min(p.k_stages, stage0 + p.per);
     const uint32_t k_bytes = p.k / 2;
 
-    // The expansion warps start on their slice of x (and clear their operand tiles) before the CTA-wide setup barrier,
-    // so the global-load latency hides behind barrier initialisation and the tensor-memory allocation.
+    // The expansion warps clear their operand tiles before the CTA-wide setup barrier.  Under a programmatic dependent
+    // launch everything up to griddepcontrol.wait (setup, the first weight stages) overlaps the tail of the kernel that
+    // ran before; x, the split-K scratch and the output are only touched after the wait.
     const uint32_t k_begin = stage0 * 256, k_end = min(p.k, stage1 * 256);
     const uint32_t nhalf = k_end > k_begin ? (k_end - k_begin) / 8 : 0;  // 8-element half blocks, one per expansion thread
-    float pre[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     if (warp >= 2) {
         const uint32_t te = threadIdx.x - 64;
-        if (te < nhalf) load8<XT>(static_cast<const XT*>(p.x) + k_begin + te * 8, pre);
         uint4* z = reinterpret_cast<uint4*>(act);
         for (uint32_t i = te; i < p.per * kActTile / 16; i += p.expand_threads) z[i] = make_uint4(0, 0, 0, 0);
         z = reinterpret_cast<uint4*>(act_sf);
@@ -151,6 +150,19 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
         umma::fence_barrier_init();
         umma::prefetch_tensormap(&map_w);
     }
+    auto load_stage = [&](uint32_t rt, uint32_t s, uint32_t slot) {
+        const uint8_t* sf_base = p.sf_w + static_cast<size_t>(rt) * p.sf_tile_stride;
+        const uint32_t kb = min(4u, (k_bytes - s * kStageK + 31) / 32);
+        umma::mbar_arrive_expect_tx(&full[slot], kWeightTile + kb * 512);
+        umma::tma_load_2d(ring_w + slot * kWeightTile, &map_w, &full[slot], static_cast<int32_t>(s * kStageK), static_cast<int32_t>(rt * kRows));
+        umma::bulk_load_1d(ring_sf + slot * kSfTile, sf_base + static_cast<size_t>(s) * kSfTile, kb * 512, &full[slot]);
+    };
+    // The first ring of weight stages of the first row tile is requested by the thread that initialised the barriers,
+    // before the setup barrier: weights depend on nothing, and every slot is free.
+    uint32_t early = 0;
+    if (group < p.row_tiles) early = min(kRing, stage1 > stage0 ? stage1 - stage0 : 0u);
+    if (threadIdx.x == 0)
+        for (uint32_t i = 0; i < early; ++i) load_stage(group, stage0 + i, i);
     if (warp == 1) {
         umma::tmem_alloc(tmem_slot, kTmemCols);
         umma::tmem_relinquish();
@@ -159,7 +171,10 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
     __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) DTRACE(1);
+    if (threadIdx.x == 0) {
+        DTRACE(1);
+        umma::griddep_launch_dependents();  // the next kernel in the stream may start its own setup and weight requests
+    }
 
     if (warp == 0) {
         // ---------------------------------------------------------------- weight producer
@@ -167,16 +182,12 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t rt = group; ok && rt < p.row_tiles; rt += groups) {
-            const uint8_t* sf_base = p.sf_w + static_cast<size_t>(rt) * p.sf_tile_stride;
             for (uint32_t s = stage0; s < stage1; ++s, ++it) {
+                if (it < early) continue;  // requested before the setup barrier (by lane 0, the same thread order as here)
                 const uint32_t slot = it % kRing, phase = (it / kRing) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&empty[slot], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
                 if (leader) {
-                    const uint32_t kb = min(4u, (k_bytes - s * kStageK + 31) / 32);
-                    umma::mbar_arrive_expect_tx(&full[slot], kWeightTile + kb * 512);
-                    umma::tma_load_2d(ring_w + slot * kWeightTile, &map_w, &full[slot], static_cast<int32_t>(s * kStageK),
-                                      static_cast<int32_t>(rt * kRows));
-                    umma::bulk_load_1d(ring_sf + slot * kSfTile, sf_base + static_cast<size_t>(s) * kSfTile, kb * 512, &full[slot]);
+                    load_stage(rt, s, slot);
                 }
                 __syncwarp();
             }
@@ -243,17 +254,13 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
         // ---------------------------------------------------------------- activation expansion, then epilogue
         const uint32_t te = threadIdx.x - 64;  // 0 .. expand_threads - 1; the first 128 go on to be the epilogue
         const uint32_t quad = warp & 3;
+        umma::griddep_wait();  // x may be the previous kernel's output; scratch, counters and the output are shared with it
         // (operand tiles were cleared before the setup barrier: rows past tokens * TERMS and the K tail stay zero)
         for (uint32_t m = 0; m < p.tokens; ++m) {
             float r[8];
             float amax = 0.0f;
             if (te < nhalf) {
-                if (m == 0) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) r[i] = pre[i];
-                } else {
-                    load8<XT>(static_cast<const XT*>(p.x) + static_cast<size_t>(m) * p.k + k_begin + te * 8, r);
-                }
+                load8<XT>(static_cast<const XT*>(p.x) + static_cast<size_t>(m) * p.k + k_begin + te * 8, r);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     if (!(fabsf(r[i]) < __int_as_float(0x7f800000))) r[i] = 0.0f;

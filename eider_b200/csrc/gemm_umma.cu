@@ -5,6 +5,7 @@
 #include "gemm_umma.cuh"
 #include "decode_umma.cuh"
 #include "gemm_pair_umma.cuh"
+#include "gemv_stream.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -141,6 +142,8 @@ struct DensePlan {
     uint32_t* status;       // device status word
 };
 
+enum DecodePath : uint32_t { kDecodeAuto = 0, kDecodeStream = 1, kDecodeFused = 2, kDecodeSplit = 3, kDecodeFusedMany = 4 };
+
 struct DecodePlan {
     int kind;
     uint32_t max_tokens, n, k, terms;
@@ -149,10 +152,12 @@ struct DecodePlan {
     uint32_t* counters;
     uint32_t* status;
     uint32_t fused_splits, fused_per;  // single-launch path for one or two tokens (0 = not available)
+    uint32_t many_splits, many_per, many_ring;  // the same kernel as one work item per CTA, three CTAs per SM (0 = not available)
     // activation expansion buffers (NVFP4 W4A16 path)
     uint8_t* act_packed;
     uint8_t* act_scales;
     float* act_col_scale;
+    uint32_t path;  // DecodePath: which kernel family serves one or two tokens
 };
 
 struct GroupedPlan {
@@ -385,7 +390,7 @@ using namespace eider::gemm;
 
 #ifdef EIDER_GEMM_TRACE
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_dtrace(long long* host) {
-    return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 256 * 8);
+    return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 512 * 8);
 }
 extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
     cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
@@ -509,9 +514,34 @@ void pick_fused_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_o
     *per_out = best_per;
 }
 
+// Shared memory the single-launch decode kernel needs for `ring` weight stages beside `per` resident activation stages.
+uint32_t fused_smem_bytes(uint32_t per, uint32_t ring) {
+    return decode::kFixedBytes + ring * (decode::kWeightTile + decode::kSfTile) + per * (decode::kActTile + decode::kActSfStage);
+}
+
+// One (row tile, K split) item per CTA with three CTAs resident per SM: splits chosen so that the items just fill
+// 3 x SMs slots; every SM then interleaves the MMAs, activation expansion and epilogues of three independent items.
+void pick_many_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_out, uint32_t* per_out, uint32_t* ring_out) {
+    *splits_out = *per_out = *ring_out = 0;
+    const uint32_t slots = 3 * static_cast<uint32_t>(sm_count());
+    uint32_t s = slots / row_tiles;
+    if (s < 2) return;
+    if (s > 32) s = 32;
+    if (s > k_stages) s = k_stages;
+    uint32_t per = (k_stages + s - 1) / s;
+    s = (k_stages + per - 1) / per;  // no empty split
+    if (s < 2 || per > decode::kMaxLocalStages) return;
+    uint32_t ring = per < 4 ? per : 4;
+    while (ring > 2 && fused_smem_bytes(per, ring) > 74 * 1024) --ring;
+    if (fused_smem_bytes(per, ring) > 74 * 1024) return;
+    *splits_out = s;
+    *per_out = per;
+    *ring_out = ring;
+}
+
 extern "C++" {
 template <int TERMS, typename XT>
-cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, cudaStream_t stream) {
+cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, bool many, cudaStream_t stream) {
     auto kernel = decode::nvfp4_decode_fused_kernel<TERMS, XT>;
     static bool configured = false;
     if (!configured) {
@@ -519,9 +549,24 @@ cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& 
         if (st != cudaSuccess) return st;
         configured = true;
     }
-    const uint32_t grid = (static_cast<uint32_t>(sm_count()) / p.splits) * p.splits;
-    kernel<<<grid, 64 + p.expand_threads, decode::kSmemBytes, stream>>>(map_w, p);
-    return cudaGetLastError();
+    // Programmatic dependent launch: setup and the first weight requests of this kernel overlap the tail of the kernel
+    // before it; the kernel waits (griddepcontrol.wait) before it reads x or touches scratch, counters and output.
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(64 + p.expand_threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (many) {  // one item per CTA, small carve-out so that three CTAs share an SM
+        cfg.gridDim = dim3(p.row_tiles * p.splits);
+        cfg.dynamicSmemBytes = fused_smem_bytes(p.per, p.ring);
+    } else {
+        cfg.gridDim = dim3((static_cast<uint32_t>(sm_count()) / p.splits) * p.splits);
+        cfg.dynamicSmemBytes = decode::kSmemBytes;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, map_w, p);
 }
 }  // extern "C++"
 
@@ -539,7 +584,10 @@ DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t
     plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK);
     const uint32_t row_tiles = (n + kTileRows - 1) / kTileRows;
     if (kind == kNvf4) pick_fused_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->fused_splits, &plan->fused_per);
-    const uint32_t ws_splits = plan->splits > plan->fused_splits ? plan->splits : plan->fused_splits;
+    if (kind == kNvf4)
+        pick_many_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->many_splits, &plan->many_per, &plan->many_ring);
+    uint32_t ws_splits = plan->splits > plan->fused_splits ? plan->splits : plan->fused_splits;
+    if (plan->many_splits > ws_splits) ws_splits = plan->many_splits;
     const size_t ws = static_cast<size_t>(ws_splits) * row_tiles * kTileRows * max_tokens * sizeof(float);
     const uint32_t rows = max_tokens * plan->terms;
     bool ok = cudaMalloc(reinterpret_cast<void**>(&plan->workspace), ws) == cudaSuccess &&
@@ -584,6 +632,13 @@ void eider_b200_decode_destroy(void* raw) {
     delete plan;
 }
 
+int eider_b200_decode_plan_set_path(void* raw, uint32_t path) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan || path > kDecodeFusedMany) return 0;
+    plan->path = path;
+    return 1;
+}
+
 cudaError_t eider_b200_decode_plan_status(void* raw, uint32_t* host_status) {
     auto* plan = static_cast<DecodePlan*>(raw);
     if (!plan || !host_status) return cudaErrorInvalidValue;
@@ -598,7 +653,28 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
     if (!plan || plan->kind != kNvf4 || !input || !w_values || !w_scales_tiled || !d || tokens == 0 ||
         tokens > plan->max_tokens)
         return cudaErrorInvalidValue;
-    if (tokens <= 2 && plan->fused_splits != 0 && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
+    if (beta != 0.0f && !c) return cudaErrorInvalidValue;
+    if (tokens <= 2 && plan->path == kDecodeStream) {
+        // one or two tokens: CUDA-core streaming GEMV (weights read once at HBM speed, exact products)
+        gemv_stream::Params g{};
+        g.x = input;
+        g.tokens = tokens;
+        g.n = plan->n;
+        g.k = plan->k;
+        g.w = w_values;
+        g.sf = w_scales_tiled;
+        g.sf_tile_stride = ((plan->k / 16 + 3) / 4 * 4) * 128;
+        g.out = d;
+        g.c_in = c;
+        g.ld_out = plan->n;
+        g.out_is_bf16 = out_is_bf16;
+        g.alpha = weight_scale_2;
+        g.beta = beta;
+        if (gemv_stream::supported(g)) return gemv_stream::launch(g, input_is_bf16, stream);
+        if (plan->path == kDecodeStream) return cudaErrorInvalidValue;
+    }
+    const bool many = plan->many_splits != 0 && (plan->path == kDecodeFusedMany || plan->path == kDecodeAuto);
+    if (tokens <= 2 && plan->path != kDecodeSplit && (many || plan->fused_splits != 0) && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
         // one launch: the activation is expanded inside the GEMV CTAs
         CUtensorMap map_w;
         cudaError_t fst = make_map(&map_w, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);
@@ -609,9 +685,9 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         p.n = plan->n;
         p.k = plan->k;
         p.k_stages = (plan->k / 2 + kStageBytesK - 1) / kStageBytesK;
-        p.splits = plan->fused_splits;
-        p.per = plan->fused_per;
-        p.ring = decode::ring_depth(p.per);
+        p.splits = many ? plan->many_splits : plan->fused_splits;
+        p.per = many ? plan->many_per : plan->fused_per;
+        p.ring = many ? plan->many_ring : decode::ring_depth(p.per);
         p.expand_threads = p.per * 32 < 128 ? 128 : p.per * 32;
         p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
         p.sf_w = w_scales_tiled;
@@ -627,7 +703,7 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         p.status = plan->status;
         if (beta != 0.0f && !c) return cudaErrorInvalidValue;
         // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 gets eight
-        return input_is_bf16 ? launch_fused_decode<4, uint16_t>(map_w, p, stream) : launch_fused_decode<8, float>(map_w, p, stream);
+        return input_is_bf16 ? launch_fused_decode<4, uint16_t>(map_w, p, many, stream) : launch_fused_decode<8, float>(map_w, p, many, stream);
     }
     cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
                                                              plan->act_col_scale, tokens, plan->k, plan->terms, stream);

@@ -388,6 +388,14 @@ class Nvfp4DecodePlan:
                                                               int(out.dtype == torch.bfloat16), _stream()))
         return out
 
+    PATHS = {"auto": 0, "stream": 1, "fused": 2, "split": 3, "fused_many": 4}
+
+    def set_path(self, path: str) -> None:
+        """Kernel family for one or two tokens: "auto" (the CUDA-core streaming GEMV), "stream", "fused" (single-launch
+        tcgen05 kernel) or "split" (expansion kernel + split-K tcgen05 GEMM)."""
+        if not self._lib.eider_b200_decode_plan_set_path(self._plan, self.PATHS[path]):
+            raise ShapeError(f"decode path {path!r} was refused")
+
     def status(self) -> int:
         v = C.c_uint32(0)
         check("eider_b200_decode_plan_status", self._lib.eider_b200_decode_plan_status(self._plan, C.byref(v)))

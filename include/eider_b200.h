@@ -164,6 +164,10 @@ EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_on_stream(void* plan, co
                                                                   int out_is_bf16, cudaStream_t stream);
 EIDER_B200_API void eider_b200_decode_destroy(void* plan);
 EIDER_B200_API cudaError_t eider_b200_decode_plan_status(void* plan, uint32_t* host_status);
+/* Kernel family for one or two tokens of an NVFP4 decode plan: 0 = automatic (the CUDA-core streaming GEMV),
+ * 1 = streaming GEMV only, 2 = single-launch tcgen05 kernel with in-kernel activation expansion, 3 = expansion kernel +
+ * split-K tcgen05 GEMM (what three or more tokens always use).  Returns 1 on success. */
+EIDER_B200_API int eider_b200_decode_plan_set_path(void* plan, uint32_t path);
 
 /* ---- routed MoE ----------------------------------------------------------------------------------- */
 
