@@ -256,14 +256,14 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
 
 // Decode orientation: weights are the row operand (128 output features per tile on the tensor-memory
 // lanes), the few tokens (x terms) are the column operand.
-cudaError_t run_decode(const DecodePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const float* x_col_scale,
-                       uint32_t tokens, const uint8_t* w_values, const uint8_t* w_scales, const float* channel_scale,
+cudaError_t run_decode(const DecodePlan& plan, uint32_t terms, const uint8_t* x_values, const uint8_t* x_scales,
+                       const float* x_col_scale, uint32_t tokens, const uint8_t* w_values, const uint8_t* w_scales, const float* channel_scale,
                        const void* c, void* d, float alpha, float beta, int out_is_bf16, cudaStream_t stream) {
     const bool nv = plan.kind == kNvf4;
     if (!x_values || !w_values || !d || tokens == 0 || tokens > plan.max_tokens) return cudaErrorInvalidValue;
     if (nv && (!x_scales || !w_scales)) return cudaErrorInvalidValue;
     const uint32_t k_bytes = nv ? plan.k / 2 : plan.k;
-    const uint32_t cols = tokens * plan.terms;
+    const uint32_t cols = tokens * terms;
     uint32_t block_n = 16;
     while (block_n < cols) block_n *= 2;
     if (block_n > 256) return cudaErrorInvalidValue;
@@ -298,7 +298,7 @@ cudaError_t run_decode(const DecodePlan& plan, const uint8_t* x_values, const ui
     const uint32_t items = p.row_tiles * p.splits;
 #define EIDER_DECODE(KIND, BN, TERMS) launch<KIND, BN, true, TERMS, false>(map_rows, map_cols, p, items, stream)
     if (nv) {
-        if (plan.terms == 8) {
+        if (terms == 8) {
             switch (block_n) {
                 case 16: return EIDER_DECODE(kNvf4, 16, 8);
                 case 32: return EIDER_DECODE(kNvf4, 32, 8);
@@ -307,7 +307,7 @@ cudaError_t run_decode(const DecodePlan& plan, const uint8_t* x_values, const ui
                 default: return EIDER_DECODE(kNvf4, 256, 8);
             }
         }
-        if (plan.terms == 4) {
+        if (terms == 4) {
             switch (block_n) {
                 case 16: return EIDER_DECODE(kNvf4, 16, 4);
                 case 32: return EIDER_DECODE(kNvf4, 32, 4);
@@ -316,7 +316,7 @@ cudaError_t run_decode(const DecodePlan& plan, const uint8_t* x_values, const ui
                 default: return EIDER_DECODE(kNvf4, 256, 4);
             }
         }
-        if (plan.terms == 1) {
+        if (terms == 1) {
             switch (block_n) {
                 case 16: return EIDER_DECODE(kNvf4, 16, 1);
                 case 32: return EIDER_DECODE(kNvf4, 32, 1);
@@ -480,13 +480,24 @@ cudaError_t eider_b200_fp8_gemm_tn_on_stream(void* raw, const uint8_t* x_values,
 // ---- decode (tokens <= 64): weights stream once, tokens ride on the MMA N dimension -----------------
 namespace {
 
-uint32_t pick_splits(uint32_t k_stages) {
-    // about five 128-byte K stages per work item keeps every persistent CTA within one item of the average load
-    uint32_t splits = (k_stages + 4) / 5;
-    if (splits < 1) splits = 1;
-    if (splits > 32) splits = 32;
-    while (splits > 1 && ((k_stages + splits - 1) / splits) * (splits - 1) >= k_stages) --splits;  // no empty split
-    return splits;
+uint32_t pick_splits(uint32_t k_stages, uint32_t row_tiles) {
+    // Persistent CTAs walk (row tile, K split) items.  Cost model in cycles: a stage of four MMAs retires in about 560
+    // cycles whatever its width, and meeting the other splits through global memory costs a few memory round trips per
+    // item, so K is only split when the row tiles alone leave most SMs idle.
+    const uint32_t sms = static_cast<uint32_t>(sm_count());
+    uint32_t best = 1;
+    float best_cost = 1e30f;
+    for (uint32_t s = 1; s <= k_stages && s <= 32; ++s) {
+        const uint32_t per = (k_stages + s - 1) / s;
+        if (s > 1 && per * (s - 1) >= k_stages) continue;  // last split would be empty
+        const uint32_t rounds = (row_tiles * s + sms - 1) / sms;
+        const float cost = static_cast<float>(rounds * per) * 560.0f + (s > 1 ? 6000.0f * rounds : 0.0f);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = s;
+        }
+    }
+    return best;
 }
 
 // K splits of the single-launch decode kernel: every CTA keeps one split for the whole launch and walks row tiles, so
@@ -581,8 +592,8 @@ DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t
     plan->k = k;
     plan->terms = kind == kNvf4 ? (max_tokens * 8 <= 256 ? 8u : 4u) : 1u;
     const uint32_t k_bytes = kind == kNvf4 ? k / 2 : k;
-    plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK);
     const uint32_t row_tiles = (n + kTileRows - 1) / kTileRows;
+    plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles);
     if (kind == kNvf4) pick_fused_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->fused_splits, &plan->fused_per);
     if (kind == kNvf4)
         pick_many_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->many_splits, &plan->many_per, &plan->many_ring);
@@ -705,10 +716,12 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 gets eight
         return input_is_bf16 ? launch_fused_decode<4, uint16_t>(map_w, p, many, stream) : launch_fused_decode<8, float>(map_w, p, many, stream);
     }
+    // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding
+    const uint32_t terms = (input_is_bf16 && plan->terms > 4) ? 4u : plan->terms;
     cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
-                                                             plan->act_col_scale, tokens, plan->k, plan->terms, stream);
+                                                             plan->act_col_scale, tokens, plan->k, terms, stream);
     if (st != cudaSuccess) return st;
-    return run_decode(*plan, plan->act_packed, plan->act_scales, plan->act_col_scale, tokens, w_values, w_scales_tiled,
+    return run_decode(*plan, terms, plan->act_packed, plan->act_scales, plan->act_col_scale, tokens, w_values, w_scales_tiled,
                       nullptr, c, d, weight_scale_2, beta, out_is_bf16, stream);
 }
 
@@ -728,7 +741,7 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
         st = infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(static_cast<const float*>(input), plan->act_packed,
                                                                  plan->act_col_scale, tokens, plan->k, stream);
     if (st != cudaSuccess) return st;
-    return run_decode(*plan, plan->act_packed, nullptr, plan->act_col_scale, tokens, weight, nullptr, channel_scale, nullptr,
+    return run_decode(*plan, 1, plan->act_packed, nullptr, plan->act_col_scale, tokens, weight, nullptr, channel_scale, nullptr,
                       d, weight_scale, 0.0f, out_is_bf16, stream);
 }
 

@@ -616,17 +616,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 if (*last_flag) {
                     __threadfence();
                     if (row_ok) {
-                        for (uint32_t ocol = 0; ocol < p.out_cols; ++ocol) {
-                            float sum = 0.0f;
-                            for (uint32_t s = 0; s < p.splits; ++s)
-                                sum += __ldcg(&p.workspace[(static_cast<size_t>(s) * p.out_cols + ocol) * (p.row_tiles * kTileRows) + row]);
-                            const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
-                            float x = sum * rs;
-                            if (p.beta != 0.0f && p.c_in)
-                                x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
-                                                               : static_cast<const float*>(p.c_in)[index], x);
-                            if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
-                            else static_cast<float*>(p.out)[index] = x;
+                        // four output columns at a time: their partials (up to 8 splits each per pass) are all requested
+                        // before any is used, so a pass costs one memory round trip; sums run in split order
+                        for (uint32_t ocol0 = 0; ocol0 < p.out_cols; ocol0 += 4) {
+                            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+                                float part[4][8];
+#pragma unroll
+                                for (uint32_t c = 0; c < 4; ++c)
+#pragma unroll
+                                    for (uint32_t u = 0; u < 8; ++u)
+                                        part[c][u] = (s0 + u < p.splits && ocol0 + c < p.out_cols)
+                                                         ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.out_cols + ocol0 + c) * (p.row_tiles * kTileRows) + row])
+                                                         : 0.0f;
+#pragma unroll
+                                for (uint32_t c = 0; c < 4; ++c)
+#pragma unroll
+                                    for (uint32_t u = 0; u < 8; ++u) sum[c] += part[c][u];
+                            }
+#pragma unroll
+                            for (uint32_t c = 0; c < 4; ++c) {
+                                if (ocol0 + c >= p.out_cols) break;
+                                const size_t index = static_cast<size_t>(ocol0 + c) * p.ld_out + row;
+                                float x = sum[c] * rs;
+                                if (p.beta != 0.0f && p.c_in)
+                                    x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
+                                                                   : static_cast<const float*>(p.c_in)[index], x);
+                                if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
+                                else static_cast<float*>(p.out)[index] = x;
+                            }
                         }
                     }
                 }

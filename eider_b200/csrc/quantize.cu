@@ -306,73 +306,89 @@ cudaError_t launch_quantize_nvfp4(const T* input, uint8_t* packed, uint8_t* scal
 // over the expanded rows reproduces the W4A16 product (the reference keeps up to two such residual terms for
 // its own W4A4 decode, crates/eider-cuda/native/sm12x_mma.cu:717-880).
 // Output rows are token-major: row = token * TERMS + j; scales are tiled with outer = that row.
-template <typename T, int PASSES>
-__global__ void __launch_bounds__(1024) expand_nvfp4_terms_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
-                                                                  uint8_t* __restrict__ scales, float* __restrict__ col_scale,
-                                                                  uint32_t k, uint32_t terms) {
-    __shared__ float red[32];
-    const uint32_t token = blockIdx.x;
+constexpr uint32_t kExpandThreads = 128;                     // one thread per 8 elements of the CTA's chunk
+constexpr uint32_t kExpandChunk = kExpandThreads * 8;        // elements per CTA
+
+__device__ __forceinline__ float decode_e4m3_fast(uint8_t code) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(code), __NV_E4M3);
+    return __half2float(__half(__half_raw{h.x}));
+}
+__device__ __forceinline__ float2 decode_e2m1x2_fast(uint32_t byte) {
+    const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+    return make_float2(__half2float(__half(__half_raw{h.x})), __half2float(__half(__half_raw{h.y})));
+}
+
+// grid = (chunks per row, tokens).  Every CTA finds the row maximum itself (the row is a few kilobytes and shared
+// through L2) and then expands only its 1024-element chunk, so a handful of tokens still spreads over many SMs; the
+// residual chain of a thread never leaves its registers.
+template <typename T>
+__global__ void __launch_bounds__(kExpandThreads) expand_nvfp4_terms_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
+                                                                            uint8_t* __restrict__ scales, float* __restrict__ col_scale,
+                                                                            uint32_t k, uint32_t terms) {
+    __shared__ float red[kExpandThreads / 32];
+    const uint32_t token = blockIdx.y;
     const T* src = input + static_cast<size_t>(token) * k;
     const uint32_t halves = k / 8;
-    float r[PASSES][8];
     float amax = 0.0f;
+    for (uint32_t h = threadIdx.x; h < halves; h += kExpandThreads) {
+        float t[8];
+        Half8<T>::load(src + h * 8, t);
 #pragma unroll
-    for (int j = 0; j < PASSES; ++j) {
-        const uint32_t h = threadIdx.x + j * blockDim.x;
-        if (h < halves) {
-            Half8<T>::load(src + h * 8, r[j]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) r[j][i] = 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (!isfinite(r[j][i])) r[j][i] = 0.0f;  // non-finite activations carry no information for a GEMV
-            amax = fmaxf(amax, fabsf(r[j][i]));
-        }
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(t[i]));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
     amax = red[0];
-    for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+#pragma unroll
+    for (uint32_t w = 1; w < kExpandThreads / 32; ++w) amax = fmaxf(amax, red[w]);
     float g = row_scale_pow2(amax);
+    float inv_g = pow2_reciprocal(g);
+
+    const uint32_t h = blockIdx.x * kExpandThreads + threadIdx.x;
+    float r[8];
+    if (h < halves) {
+        Half8<T>::load(src + h * 8, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (!isfinite(r[i])) r[i] = 0.0f;  // non-finite activations carry no information for a GEMV
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = 0.0f;
+    }
     for (uint32_t term = 0; term < terms; ++term) {
         const uint32_t row = token * terms + term;
-        if (threadIdx.x == 0) col_scale[row] = g;
-        const Divisor dg = make_divisor(g);
-        uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
+        if (blockIdx.x == 0 && threadIdx.x == 0) col_scale[row] = g;
+        float v[8];
+        float bmax = 0.0f;
 #pragma unroll
-        for (int j = 0; j < PASSES; ++j) {
-            const uint32_t h = threadIdx.x + j * blockDim.x;
-            float v[8];
-            float bmax = 0.0f;
+        for (int i = 0; i < 8; ++i) {
+            v[i] = r[i] * inv_g;  // exact: g is a power of two
+            bmax = fmaxf(bmax, fabsf(v[i]));
+        }
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));  // the other half of the 16-element block
+        const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(div6_rn(bmax));
+        const float sv = decode_e4m3_fast(sc);
+        const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
+        const float back = sv * g;
+        uint32_t w = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                v[i] = div_rn(r[j][i], dg);
-                bmax = fmaxf(bmax, fabsf(v[i]));
-            }
-            bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
-            if (h >= halves) continue;
-            const uint8_t sc = bmax == 0.0f ? 0 : ue4m3_code(div6_rn(bmax));
-            const float sv = e4m3_value(sc);
-            const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
-            uint32_t w = 0;
-#pragma unroll
-            for (int i = 0; i < 8; i += 2) {
-                const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
-                const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
-                const uint32_t byte = e2m1x2_code(lo, hi);
-                w |= byte << (i * 4);
-                // leftover for the next term
-                r[j][i] = fmaf(-e2m1_value(byte & 0xfu) * sv, g, r[j][i]);
-                r[j][i + 1] = fmaf(-e2m1_value(byte >> 4) * sv, g, r[j][i + 1]);
-            }
-            *reinterpret_cast<uint32_t*>(prow + h * 4) = w;
+        for (int i = 0; i < 8; i += 2) {
+            const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
+            const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
+            const uint32_t byte = e2m1x2_code(lo, hi);
+            w |= byte << (i * 4);
+            const float2 q = decode_e2m1x2_fast(byte);  // leftover for the next term
+            r[i] = fmaf(-q.x, back, r[i]);
+            r[i + 1] = fmaf(-q.y, back, r[i + 1]);
+        }
+        if (h < halves) {
+            *reinterpret_cast<uint32_t*>(packed + static_cast<size_t>(row) * (k / 2) + h * 4) = w;
             if ((h & 1) == 0) scales[tiled_scale_offset(row, h >> 1, k)] = sc;
         }
         g *= 0.25f;
+        inv_g *= 4.0f;
     }
 }
 
@@ -504,28 +520,13 @@ cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input
     if (!input || !packed || !scales || !col_scale || tokens == 0 || in_features == 0 || in_features % 16 != 0 ||
         terms == 0 || terms > 16 || in_features / 8 > 4096 || (reinterpret_cast<uintptr_t>(input) & 15) != 0)
         return cudaErrorInvalidValue;
-    const uint32_t halves = in_features / 8;
-    const uint32_t passes = (halves + 1023) / 1024;
-    const uint32_t threads = ((halves + passes - 1) / passes + 31) / 32 * 32;
-#define EIDER_EXPAND(TT, PP)                                                                                          \
-    expand_nvfp4_terms_kernel<TT, PP><<<tokens, threads, 0, stream>>>(static_cast<const TT*>(input), packed, scales, \
-                                                                      col_scale, in_features, terms)
-    if (input_is_bf16) {
-        switch (passes) {
-            case 1: EIDER_EXPAND(uint16_t, 1); break;
-            case 2: EIDER_EXPAND(uint16_t, 2); break;
-            case 3: EIDER_EXPAND(uint16_t, 3); break;
-            default: EIDER_EXPAND(uint16_t, 4); break;
-        }
-    } else {
-        switch (passes) {
-            case 1: EIDER_EXPAND(float, 1); break;
-            case 2: EIDER_EXPAND(float, 2); break;
-            case 3: EIDER_EXPAND(float, 3); break;
-            default: EIDER_EXPAND(float, 4); break;
-        }
-    }
-#undef EIDER_EXPAND
+    const dim3 grid((in_features + kExpandChunk - 1) / kExpandChunk, tokens);
+    if (input_is_bf16)
+        expand_nvfp4_terms_kernel<uint16_t><<<grid, kExpandThreads, 0, stream>>>(static_cast<const uint16_t*>(input), packed, scales,
+                                                                                 col_scale, in_features, terms);
+    else
+        expand_nvfp4_terms_kernel<float><<<grid, kExpandThreads, 0, stream>>>(static_cast<const float*>(input), packed, scales,
+                                                                              col_scale, in_features, terms);
     return cudaGetLastError();
 }
 

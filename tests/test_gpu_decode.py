@@ -58,8 +58,8 @@ def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
     # eight residual terms carry the activation essentially exactly; four terms keep ~1e-3 of the block maximum
     # and that is also what the single-launch path uses for one or two bf16 tokens (bf16 itself resolves 4e-3)
     tol = 1e-4 if tokens <= 32 else 1e-2
-    if dtype == "bf16" and tokens <= 2:
-        tol = 2e-3
+    if dtype == "bf16":
+        tol = max(tol, 2e-3)  # bf16 activations always take four terms
     ok, stats = gemm_close(to_np(y), ref, rel=tol, abs_frac=tol)
     assert ok, stats
     assert torch.equal(y, y2)
