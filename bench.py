@@ -291,6 +291,9 @@ def main():
     ap.add_argument("--impl", default="eider_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how the column blocks become [M, N] on every rank: GEMM epilogue stores into every "
+                         "rank's output (symmetric memory) or NCCL all-gather + re-assembly")
     ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe"],
                     help="prefill (default, the contract line), or the single-GPU decode / MoE configs")
     args = ap.parse_args()
@@ -350,6 +353,14 @@ def main():
         return plan.run(xq, current["w"], out=y_local)
 
     sharded = parallel.ColumnShardedLinear(N, local_linear)
+    gather = "none" if world == 1 else "nccl"
+    if world > 1 and args.gather == "fused":
+        try:
+            sharded.fuse_into(plan, M)
+            gather = "fused"
+        except Exception as exc:  # symmetric memory is not available on this box: keep the NCCL path
+            if rank == 0:
+                print(f"# fused all-gather unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
     result = {}
 
     def step(i, x):
@@ -440,7 +451,8 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "nvfp4(e2m1+ue4m3) x nvfp4, f32 accumulate, bf16 out", "data": "synthetic",
         "config": {"workload": WORKLOAD, "M": M, "K": K, "N": N, "partition": f"N column-sharded x{world}" +
-                   (" + NCCL all-gather of bf16 outputs" if world > 1 else ""),
+                   ({"nccl": " + NCCL all-gather of bf16 outputs", "none": "",
+                     "fused": " + all-gather fused into the GEMM epilogue (stores into every rank's output over NVLink)"}[gather]),
                    "l2": f"inputs larger than L2: {rotate} rotating weight copies of {n_local * K * 9 // 16 // 2**20} MiB each"},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "note": "weights stay resident in HBM (model state); X from and Y to pinned host memory"},

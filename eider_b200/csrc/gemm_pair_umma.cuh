@@ -305,9 +305,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 if (!row_ok) continue;
                 const uint32_t c = col_of(step);
                 if (wide) {
-                    uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + t.col0 + c;
-                    store_bf16x32_scaled(dst, &raw[step & 1][0], rs);
-                    store_bf16x32_scaled(dst + 32, &raw[step & 1][32], rs);
+                    store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs);
                 } else {
 #pragma unroll
                     for (uint32_t i = 0; i < 64; ++i) {  // fully unrolled: the accumulator stays in registers
@@ -319,8 +317,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                         if (p.beta != 0.0f && p.c_in)
                             x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index])
                                                            : static_cast<const float*>(p.c_in)[index], x);
-                        if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
-                        else static_cast<float*>(p.out)[index] = x;
+                        for_each_out(p, [&](void* base) {
+                            if (p.out_is_bf16) static_cast<uint16_t*>(base)[index] = float_to_bf16_bits(x);
+                            else static_cast<float*>(base)[index] = x;
+                        });
                     }
                 }
             }

@@ -4,6 +4,7 @@
 // (crates/eider-cuda/native/cutlass_grouped_gemm.cu) with one hand-written kernel family.
 #include "gemm_umma.cuh"
 #include "decode_umma.cuh"
+#include "decode_fp8_umma.cuh"
 #include "gemm_pair_umma.cuh"
 #include "gemv_stream.cuh"
 
@@ -140,6 +141,9 @@ struct DensePlan {
     uint32_t m, n, k;       // tokens, out features, in features
     uint32_t block_n;       // weight rows per tile
     uint32_t* status;       // device status word
+    void* peers[8];         // fused all-gather: this rank's column block inside every rank's output (all null = off)
+    uint32_t n_peers;
+    uint32_t peer_ld;       // row pitch (elements) of those outputs
 };
 
 enum DecodePath : uint32_t { kDecodeAuto = 0, kDecodeStream = 1, kDecodeFused = 2, kDecodeSplit = 3, kDecodeFusedMany = 4 };
@@ -232,6 +236,13 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
     p.out_cols = plan.n;
     p.splits = 1;
     p.status = plan.status;
+    if (plan.n_peers > 0) {
+        if (beta != 0.0f) return cudaErrorInvalidValue;  // C would have to be read from the gathered layout
+        for (uint32_t q = 0; q < plan.n_peers; ++q) p.out_peers[q] = plan.peers[q];
+        p.n_peers = plan.n_peers;
+        p.out = plan.peers[0];
+        p.ld_out = plan.peer_ld;
+    }
     if (plan.block_n == kPairBlockCode) {
         // 256 x 256 tiles on CTA pairs
         p.col_tiles = (plan.n + kPairN - 1) / kPairN;
@@ -442,6 +453,17 @@ int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     return 1;
 }
 
+cudaError_t eider_b200_gemm_plan_set_output_peers(void* raw, void* const* peers, uint32_t count, uint32_t ld_out) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || count > 8 || (count > 0 && (!peers || ld_out < plan->n || ld_out % 16 != 0))) return cudaErrorInvalidValue;
+    for (uint32_t q = 0; q < count; ++q)
+        if (!peers[q] || (reinterpret_cast<uintptr_t>(peers[q]) & 31) != 0) return cudaErrorInvalidValue;
+    for (uint32_t q = 0; q < 8; ++q) plan->peers[q] = q < count ? peers[q] : nullptr;
+    plan->n_peers = count;
+    plan->peer_ld = ld_out;
+    return cudaSuccess;
+}
+
 uint32_t eider_b200_gemm_plan_block_n(void* raw) {
     auto* plan = static_cast<DensePlan*>(raw);
     return plan ? plan->block_n : 0;
@@ -550,6 +572,49 @@ void pick_many_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_ou
     *ring_out = ring;
 }
 
+// FP8 single-launch decode: one (row tile, K split) item per CTA, three CTAs per SM.
+void pick_fp8_many_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_out, uint32_t* per_out, uint32_t* ring_out) {
+    *splits_out = *per_out = *ring_out = 0;
+    const uint32_t slots = 3 * static_cast<uint32_t>(sm_count());
+    uint32_t s = slots / row_tiles;
+    if (s < 1) s = 1;
+    if (s > 32) s = 32;
+    if (s > k_stages) s = k_stages;
+    uint32_t per = (k_stages + s - 1) / s;
+    if (per > decode_fp8::kMaxPer) return;
+    s = (k_stages + per - 1) / per;  // no empty split
+    uint32_t ring = per < 4 ? per : 4;
+    while (ring > 2 && decode_fp8::smem_bytes(per, ring) > 74 * 1024) --ring;
+    if (decode_fp8::smem_bytes(per, ring) > 74 * 1024) return;
+    *splits_out = s;
+    *per_out = per;
+    *ring_out = ring;
+}
+
+extern "C++" {
+template <typename XT>
+cudaError_t launch_fp8_fused_decode(const CUtensorMap& map_w, const decode_fp8::Params& p, cudaStream_t stream) {
+    auto kernel = decode_fp8::fp8_decode_fused_kernel<XT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 76 * 1024);
+        if (st != cudaSuccess) return st;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.row_tiles * p.splits);
+    cfg.blockDim = dim3(decode_fp8::kThreads);
+    cfg.dynamicSmemBytes = decode_fp8::smem_bytes(p.per, p.ring);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, map_w, p);
+}
+}  // extern "C++"
+
 extern "C++" {
 template <int TERMS, typename XT>
 cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, bool many, cudaStream_t stream) {
@@ -595,6 +660,7 @@ DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t
     const uint32_t row_tiles = (n + kTileRows - 1) / kTileRows;
     plan->splits = pick_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles);
     if (kind == kNvf4) pick_fused_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->fused_splits, &plan->fused_per);
+    if (kind == kFp8) pick_fp8_many_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->many_splits, &plan->many_per, &plan->many_ring);
     if (kind == kNvf4)
         pick_many_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->many_splits, &plan->many_per, &plan->many_ring);
     uint32_t ws_splits = plan->splits > plan->fused_splits ? plan->splits : plan->fused_splits;
@@ -733,6 +799,32 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
     auto* plan = static_cast<DecodePlan*>(raw);
     if (!plan || plan->kind != kFp8 || !input || !weight || !d || tokens == 0 || tokens > plan->max_tokens)
         return cudaErrorInvalidValue;
+    if (tokens <= decode_fp8::kMaxTokens && plan->many_splits != 0 && plan->path != kDecodeSplit &&
+        (reinterpret_cast<uintptr_t>(input) & 15) == 0 && plan->k % 16 == 0) {
+        // one launch: the per-token quantizer runs inside the GEMV CTAs
+        CUtensorMap map_w;
+        cudaError_t fst = make_map(&map_w, weight, plan->n, plan->k, plan->k, kTileRows);
+        if (fst != cudaSuccess) return fst;
+        decode_fp8::Params p{};
+        p.x = input;
+        p.tokens = tokens;
+        p.n = plan->n;
+        p.k = plan->k;
+        p.k_stages = (plan->k + kStageBytesK - 1) / kStageBytesK;
+        p.splits = plan->many_splits;
+        p.per = plan->many_per;
+        p.ring = plan->many_ring;
+        p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
+        p.channel_scale = channel_scale;
+        p.out = d;
+        p.ld_out = plan->n;
+        p.out_is_bf16 = out_is_bf16;
+        p.alpha = weight_scale;
+        p.workspace = plan->workspace;
+        p.counters = plan->counters;
+        p.status = plan->status;
+        return input_is_bf16 ? launch_fp8_fused_decode<uint16_t>(map_w, p, stream) : launch_fp8_fused_decode<float>(map_w, p, stream);
+    }
     cudaError_t st;
     if (input_is_bf16)
         st = eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(static_cast<const uint16_t*>(input), plan->act_packed,

@@ -60,7 +60,22 @@ struct Params {
     uint32_t group_cols;            // column-operand rows per group (weights per expert)
     const float* group_alpha;       // per-group alpha (null: use alpha)
     uint32_t* status;               // device status word, 0 = ok
+    // Fused all-gather (dense, row-major bf16/f32 output only): when n_peers > 0 every output element is written to
+    // each of out_peers[0 .. n_peers) instead of `out`; the pointers are this rank's column block inside every rank's
+    // full output (peer memory mapped into this process), so the slab travels over NVLink tile by tile while the GEMM
+    // is still running.  Plain stores only.
+    void* out_peers[8];
+    uint32_t n_peers;
 };
+
+// Calls f(base) for every output buffer of the launch.
+template <typename F> __device__ __forceinline__ void for_each_out(const Params& p, F f) {
+    if (p.n_peers == 0) {
+        f(p.out);
+        return;
+    }
+    for (uint32_t q = 0; q < p.n_peers; ++q) f(p.out_peers[q]);
+}
 
 template <int BLOCK_N> struct SmemLayout {
     static constexpr uint32_t kA = kTileRows * kStageBytesK;                 // 16 KB
@@ -206,19 +221,26 @@ template <> __device__ __forceinline__ void store_chunk32<false>(void* out, size
 
 // 32 fp32 accumulator columns -> 32 bf16 (scaled), written with two 32-byte stores.  A thread owns one output row, so
 // every store instruction of a warp touches 32 different lines; wider stores halve the number of such instructions.
-__device__ __forceinline__ void store_bf16x32_scaled(uint16_t* dst, const uint32_t* raw, float scale) {
-    uint32_t w[16];
+__device__ __forceinline__ void convert_bf16x64_scaled(const uint32_t* raw, float scale, uint32_t (&w)[32]) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 32; ++i) {
         __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[2 * i]) * scale, __uint_as_float(raw[2 * i + 1]) * scale);
         w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
+}
+__device__ __forceinline__ void store_bf16x64(uint16_t* dst, const uint32_t (&w)[32]) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 4; ++i)
         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 16 * i), "r"(w[8 * i]),
                      "r"(w[8 * i + 1]), "r"(w[8 * i + 2]), "r"(w[8 * i + 3]), "r"(w[8 * i + 4]), "r"(w[8 * i + 5]),
                      "r"(w[8 * i + 6]), "r"(w[8 * i + 7])
                      : "memory");
+}
+// 64 fp32 accumulator columns of one row -> 64 scaled bf16 at element offset `offset` of every output buffer
+__device__ __forceinline__ void store_row64_all(const Params& p, size_t offset, const uint32_t* raw, float scale) {
+    uint32_t w[32];
+    convert_bf16x64_scaled(raw, scale, w);
+    for_each_out(p, [&](void* base) { store_bf16x64(static_cast<uint16_t*>(base) + offset, w); });
 }
 
 // KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
@@ -472,7 +494,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             }
             if constexpr (kWide) if (wide) {
                 constexpr uint32_t kSteps = BLOCK_N / 64;
-                uint16_t* dst_row = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.ld_out + t.out_col0;
+                const size_t row_offset = static_cast<size_t>(row) * p.ld_out + t.out_col0;
                 uint32_t raw[2][64];
                 auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (BLOCK_N - 64 - step * 64) : step * 64; };
                 auto issue = [&](uint32_t step, uint32_t (&r)[64]) {
@@ -491,11 +513,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
                     }
-                    if (row_ok) {
-                        const uint32_t c = col_of(step);
-                        store_bf16x32_scaled(dst_row + c, &raw[step & 1][0], rs);
-                        store_bf16x32_scaled(dst_row + c + 32, &raw[step & 1][32], rs);
-                    }
+                    if (row_ok) store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs);
                 }
                 if (!T::kOverlap) {
                     umma::tmem_load_wait();
@@ -555,18 +573,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                                 }
                             }
                         }
-                        if (full_chunk && aligned) {
-                            if (p.out_is_bf16) store_chunk32<true>(p.out, index, v);
-                            else store_chunk32<false>(p.out, index, v);
-                        } else {
+                        for_each_out(p, [&](void* base) {
+                            if (full_chunk && aligned) {
+                                if (p.out_is_bf16) store_chunk32<true>(base, index, v);
+                                else store_chunk32<false>(base, index, v);
+                            } else {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                if (col0 + i < ncols && static_cast<uint32_t>(i) < kChunk) {
-                                    if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index + i] = float_to_bf16_bits(v[i]);
-                                    else static_cast<float*>(p.out)[index + i] = v[i];
+                                for (int i = 0; i < 32; ++i) {
+                                    if (col0 + i < ncols && static_cast<uint32_t>(i) < kChunk) {
+                                        if (p.out_is_bf16) static_cast<uint16_t*>(base)[index + i] = float_to_bf16_bits(v[i]);
+                                        else static_cast<float*>(base)[index + i] = v[i];
+                                    }
                                 }
                             }
-                        }
+                        });
                     }
                 } else {
                     // rows are output features, groups of TERMS columns are one token

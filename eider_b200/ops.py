@@ -172,6 +172,13 @@ class Fp4TnMatmulPlan:
         """Tile code in use: weight rows per tile, 512 = 256 x 256 tiles on CTA pairs."""
         return int(self._lib.eider_b200_gemm_plan_block_n(self._plan))
 
+    def set_output_peers(self, pointers, ld_out: int) -> None:
+        """Fused all-gather: `pointers[q]` = address of this rank's first output column inside rank q's full
+        [tokens, ld_out] output (peer memory mapped into this process).  An empty list switches it off."""
+        arr = (C.c_void_p * max(1, len(pointers)))(*[C.c_void_p(int(a)) for a in pointers])
+        check("eider_b200_gemm_plan_set_output_peers",
+              self._lib.eider_b200_gemm_plan_set_output_peers(self._plan, arr, len(pointers), ld_out))
+
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
             raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
@@ -229,6 +236,13 @@ class Fp8TnMatmulPlan:
     def block_n(self) -> int:
         """Tile code in use: weight rows per tile, 512 = 256 x 256 tiles on CTA pairs."""
         return int(self._lib.eider_b200_gemm_plan_block_n(self._plan))
+
+    def set_output_peers(self, pointers, ld_out: int) -> None:
+        """Fused all-gather: `pointers[q]` = address of this rank's first output column inside rank q's full
+        [tokens, ld_out] output (peer memory mapped into this process).  An empty list switches it off."""
+        arr = (C.c_void_p * max(1, len(pointers)))(*[C.c_void_p(int(a)) for a in pointers])
+        check("eider_b200_gemm_plan_set_output_peers",
+              self._lib.eider_b200_gemm_plan_set_output_peers(self._plan, arr, len(pointers), ld_out))
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):

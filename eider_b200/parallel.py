@@ -42,7 +42,14 @@ def gathered_to_row_major(gathered: torch.Tensor) -> torch.Tensor:
 
 
 class ColumnShardedLinear:
-    """y = x . W^T with W split over output features; `local_linear(x) -> [M, N/g]` is this rank's slab."""
+    """y = x . W^T with W split over output features; `local_linear(x) -> [M, N/g]` is this rank's slab.
+
+    Two ways to assemble [M, N] on every rank:
+      * NCCL: `all_gather_into_tensor` of the slabs and a re-assembly copy (the default);
+      * fused (`fuse_into(plan, tokens)`): every rank's full output lives in symmetric memory, the GEMM plan gets the
+        address of this rank's column block inside every rank's output and its epilogue writes each tile to all of them
+        while the GEMM is still running; the ranks meet at a device-side barrier before the result is used and before
+        it is overwritten again.  No collective library call and no re-assembly pass are left on the data path."""
 
     def __init__(self, out_features: int, local_linear: Callable[[torch.Tensor], torch.Tensor], group=None):
         self.group = group
@@ -54,8 +61,26 @@ class ColumnShardedLinear:
             raise ValueError("equal shards are required for all_gather_into_tensor")
         self.local_linear = local_linear
         self._gathered = None
+        self._fused = None
+
+    def fuse_into(self, plan, tokens: int, dtype=torch.bfloat16) -> None:
+        """Switches to the fused all-gather: `plan` must offer set_output_peers(pointers, ld_out)."""
+        if self.world == 1:
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+        full = symm_mem.empty(tokens, self.out_features, dtype=dtype, device="cuda")
+        handle = symm_mem.rendezvous(full, self.group if self.group is not None else dist.group.WORLD)
+        offset_bytes = self.begin * full.element_size()
+        plan.set_output_peers([int(ptr) + offset_bytes for ptr in handle.buffer_ptrs], self.out_features)
+        self._fused = (full, handle)
 
     def forward(self, x: torch.Tensor, assemble: bool = True) -> torch.Tensor:
+        if self._fused is not None:
+            full, handle = self._fused
+            handle.barrier(channel=0)   # nobody still reads the previous result out of this rank's buffer
+            self.local_linear(x)        # the epilogue writes this rank's columns into every rank's buffer
+            handle.barrier(channel=1)   # every rank's columns have arrived
+            return full
         y_local = self.local_linear(x)
         if self.world == 1:
             return y_local

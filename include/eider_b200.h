@@ -244,6 +244,14 @@ EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_st
  * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
 EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
 EIDER_B200_API uint32_t eider_b200_gemm_plan_block_n(void* plan); /* the tile code in use (0 for a null plan) */
+/* Fused all-gather for a column-sharded dense layer (no reference counterpart: the reference is single-GPU).  peers[q]
+ * points at this rank's first output column inside rank q's full [tokens][ld_out] output (its own buffer included),
+ * mapped into this process (CUDA IPC / symmetric memory), 32-byte aligned; count <= 8.  While set, the GEMM's epilogue
+ * writes every output tile to all of them with plain stores over NVLink and the `d` argument of the run call is ignored;
+ * beta must be 0.  The caller still has to synchronise the ranks before the outputs are read or overwritten.  count = 0
+ * switches it off. */
+EIDER_B200_API cudaError_t eider_b200_gemm_plan_set_output_peers(void* plan, void* const* peers, uint32_t count,
+                                                                 uint32_t ld_out);
 EIDER_B200_API cudaError_t eider_b200_gemm_plan_status(void* plan, uint32_t* host_status);
 
 #ifdef __cplusplus
