@@ -291,7 +291,7 @@ def main():
     ap.add_argument("--impl", default="eider_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--block-n", type=int, default=0)
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--gather", default="nccl", choices=["fused", "nccl"],
                     help="N > 1: how the column blocks become [M, N] on every rank: GEMM epilogue stores into every "
                          "rank's output (symmetric memory) or NCCL all-gather + re-assembly")
     ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe"],
