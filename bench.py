@@ -350,13 +350,19 @@ def main():
 
     def local_linear(x):
         ops.quantize_nvfp4_rowscale(x, out=xq)
-        return plan.run(xq, current["w"], out=y_local)
+        return (sharded.active_plan or plan).run(xq, current["w"], out=y_local)
 
     sharded = parallel.ColumnShardedLinear(N, local_linear)
     gather = "none" if world == 1 else "nccl"
     if world > 1 and args.gather == "fused":
         try:
-            sharded.fuse_into(plan, M)
+            plan_b = ops.Fp4TnMatmulPlan(M, n_local, K)  # second output buffer: one barrier per step is enough
+            for q in (plan, plan_b):
+                if args.block_n:
+                    q.set_block_n(args.block_n)
+                elif M > 128:
+                    q.set_block_n(512)  # the CTA-pair kernel writes peers through shared memory and TMA stores
+            sharded.fuse_into([plan, plan_b], M)
             gather = "fused"
         except Exception as exc:  # symmetric memory is not available on this box: keep the NCCL path
             if rank == 0:

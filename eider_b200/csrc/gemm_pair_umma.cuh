@@ -29,8 +29,11 @@ template <int KIND> struct PairSmem {
     static constexpr uint32_t kSfA = kNv ? 4 * kScaleTileBytes : 0;   // scales of this CTA's rows
     static constexpr uint32_t kSfB = kNv ? 8 * kScaleTileBytes : 0;   // scales of all 256 weight rows
     static constexpr uint32_t kStage = kA + kB + kSfA + kSfB;
-    static constexpr int kStages = (226u * 1024u) / kStage > 8 ? 8 : static_cast<int>((226u * 1024u) / kStage);
-    static constexpr uint32_t kBytes = kStage * kStages + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // epilogue staging for TMA stores: per epilogue warp two buffers of 32 rows x 128 bytes (64 bf16 columns)
+    static constexpr uint32_t kStoreBuf = 32 * 128;
+    static constexpr uint32_t kStore = 4 * 2 * kStoreBuf;
+    static constexpr int kStages = (226u * 1024u - kStore) / kStage > 8 ? 8 : static_cast<int>((226u * 1024u - kStore) / kStage);
+    static constexpr uint32_t kBytes = kStage * kStages + kStore + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 struct PairTile {
@@ -64,7 +67,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
     uint8_t* smem_b = smem_a + STAGES * L::kA;
     uint8_t* smem_sfa = smem_b + STAGES * L::kB;
     uint8_t* smem_sfb = smem_sfa + STAGES * L::kSfA;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::kStage);
+    uint8_t* smem_store = smem + STAGES * L::kStage;  // 1024-byte aligned: the stage size is a multiple of 1024
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_store + L::kStore);
     uint64_t* full = bars;                    // [STAGES]
     uint64_t* empty = bars + STAGES;          // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;   // [kAcc]
@@ -263,6 +267,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         const uint32_t quad = warp & 3;
         umma::griddep_wait();  // row scales written by the preceding kernel are read below
         const uint32_t accempty0_remote = umma::map_to_cta(umma::smem_u32(&acc_empty[0]), 0);
+        uint32_t store_count = 0;  // TMA stores issued by this warp (selects the staging buffer)
         uint32_t tile_count = 0;
         PairTile t;
         bool ok = true;
@@ -289,6 +294,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             };
             const bool wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
                               (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+            const bool staged = p.out_maps != nullptr;  // (the host sets the maps only for plain bf16 output)
             constexpr uint32_t kSteps = kPairN / 64;
             uint32_t raw[2][64];
             issue(0, raw[0]);
@@ -302,8 +308,36 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     __syncwarp();
                     if (lane == 0) umma::mbar_arrive_cluster(accempty0_remote + acc * 8);
                 }
-                if (!row_ok) continue;
                 const uint32_t c = col_of(step);
+                if (staged) {
+                    // this warp's 32 rows x 64 columns -> bf16 in a 128-byte-swizzled staging buffer -> one TMA store per
+                    // destination (the hardware clips rows and columns past the end of the output)
+                    uint8_t* sbuf = smem_store + (quad * 2 + (store_count & 1)) * L::kStoreBuf;
+                    if (store_count >= 2) {
+                        if (lane == 0) umma::tma_store_wait_read<1>();  // the stores that last read this buffer have finished reading
+                        __syncwarp();
+                    }
+                    ++store_count;
+                    uint32_t w[32];
+                    convert_bf16x64_scaled(&raw[step & 1][0], rs, w);
+                    const uint32_t row_base = umma::smem_u32(sbuf) + lane * 128;
+#pragma unroll
+                    for (uint32_t ch = 0; ch < 8; ++ch)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)), "r"(w[4 * ch]),
+                                     "r"(w[4 * ch + 1]), "r"(w[4 * ch + 2]), "r"(w[4 * ch + 3])
+                                     : "memory");
+                    umma::fence_proxy_async();
+                    __syncwarp();
+                    const uint32_t warp_row0 = t.row0 + quad * 32;
+                    if (lane == 0) {
+                        if (warp_row0 < p.rows && t.col0 + c < p.cols)
+                            for (uint32_t q = 0; q < p.n_peers; ++q)
+                                umma::tma_store_2d(&p.out_maps[q], sbuf, static_cast<int32_t>(t.col0 + c), static_cast<int32_t>(warp_row0));
+                        umma::tma_store_commit();  // one group per use of a staging buffer, empty or not
+                    }
+                    continue;
+                }
+                if (!row_ok) continue;
                 if (wide) {
                     store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs);
                 } else {
@@ -325,6 +359,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 }
             }
         }
+        if (lane == 0) umma::tma_store_wait_all();  // staging buffers are read (and the outputs written) before the CTA leaves
+        __syncwarp();
     }
 
     if (threadIdx.x == 64) TRACE_ADD(3, TRACE_NOW() - tr_start);

@@ -93,6 +93,20 @@ cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, con
     return cudaLaunchKernelEx(&cfg, kernel, map_rows, map_cols, p);
 }
 
+// bf16 output block [rows][cols] with row pitch ld (elements): box = 64 columns x 32 rows, 128-byte swizzle (what the
+// epilogue's staging buffers hold)
+cudaError_t make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint64_t ld) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // CTA-pair kernel: clusters of two along x, as many pairs as can be co-resident (one CTA per SM).
 template <int KIND>
 cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols, const Params& p, uint32_t pair_items,
@@ -144,6 +158,7 @@ struct DensePlan {
     void* peers[8];         // fused all-gather: this rank's column block inside every rank's output (all null = off)
     uint32_t n_peers;
     uint32_t peer_ld;       // row pitch (elements) of those outputs
+    CUtensorMap* peer_maps; // device array of n_peers bf16 tensor maps over the same column blocks (TMA-store epilogue)
 };
 
 enum DecodePath : uint32_t { kDecodeAuto = 0, kDecodeStream = 1, kDecodeFused = 2, kDecodeSplit = 3, kDecodeFusedMany = 4 };
@@ -242,6 +257,8 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
         p.n_peers = plan.n_peers;
         p.out = plan.peers[0];
         p.ld_out = plan.peer_ld;
+        // plain bf16 output on the CTA-pair kernel: whole tiles leave through shared memory and TMA stores
+        if (plan.peer_maps && out_is_bf16 && !channel_scale && plan.block_n == kPairBlockCode) p.out_maps = plan.peer_maps;
     }
     if (plan.block_n == kPairBlockCode) {
         // 256 x 256 tiles on CTA pairs
@@ -433,6 +450,7 @@ void eider_b200_nvfp4_gemm_tn_destroy(void* raw) {
     auto* plan = static_cast<DensePlan*>(raw);
     if (!plan) return;
     cudaFree(plan->status);
+    cudaFree(plan->peer_maps);
     delete plan;
 }
 
@@ -461,6 +479,18 @@ cudaError_t eider_b200_gemm_plan_set_output_peers(void* raw, void* const* peers,
     for (uint32_t q = 0; q < 8; ++q) plan->peers[q] = q < count ? peers[q] : nullptr;
     plan->n_peers = count;
     plan->peer_ld = ld_out;
+    if (count > 0) {
+        CUtensorMap maps[8];
+        for (uint32_t q = 0; q < count; ++q) {
+            cudaError_t st = make_out_map(&maps[q], peers[q], plan->m, plan->n, ld_out);
+            if (st != cudaSuccess) return st;
+        }
+        if (!plan->peer_maps) {
+            cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&plan->peer_maps), 8 * sizeof(CUtensorMap));
+            if (st != cudaSuccess) return st;
+        }
+        return cudaMemcpy(plan->peer_maps, maps, count * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    }
     return cudaSuccess;
 }
 

@@ -66,6 +66,10 @@ struct Params {
     // is still running.  Plain stores only.
     void* out_peers[8];
     uint32_t n_peers;
+    // The same destinations as 2-D bf16 tensor maps in global memory (box 64 columns x 32 rows, 128-byte swizzle),
+    // n_peers of them: the CTA-pair kernel stages each warp's 32 x 64 block in shared memory and lets the TMA write
+    // whole 128-byte lines, which is what makes stores over NVLink efficient.  Null: plain stores.
+    const CUtensorMap* out_maps;
 };
 
 // Calls f(base) for every output buffer of the launch.

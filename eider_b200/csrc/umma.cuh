@@ -128,6 +128,21 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
                  : "memory");
 }
 
+// 2-D tiled store from this CTA's shared memory (rows / columns outside the tensor are clipped); the tensor map may
+// live in global memory.  Stores are grouped per issuing thread: commit closes a group, wait_read<N> returns when all
+// but the newest N groups have finished READING shared memory (the staging buffer may be rewritten), wait_all when
+// they have completed.
+__device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_src, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending> __device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- tensor memory ----------------------------------------------------------------------------
 // Whole-warp calls.  `cols` is a power of two >= 32.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {

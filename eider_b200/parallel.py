@@ -62,24 +62,38 @@ class ColumnShardedLinear:
         self.local_linear = local_linear
         self._gathered = None
         self._fused = None
+        self.active_plan = None
 
-    def fuse_into(self, plan, tokens: int, dtype=torch.bfloat16) -> None:
-        """Switches to the fused all-gather: `plan` must offer set_output_peers(pointers, ld_out)."""
+    def fuse_into(self, plans, tokens: int, dtype=torch.bfloat16) -> None:
+        """Switches to the fused all-gather.  `plans` is one plan or a list of plans over the same weights, each offering
+        set_output_peers(pointers, ld_out); every plan gets its own symmetric output buffer and forward() rotates through
+        them (`active_plan` is the one the local linear has to run).  With two or more buffers a rank is never written
+        while it may still read the same buffer, and one barrier per step is enough."""
         if self.world == 1:
             return
         import torch.distributed._symmetric_memory as symm_mem
-        full = symm_mem.empty(tokens, self.out_features, dtype=dtype, device="cuda")
-        handle = symm_mem.rendezvous(full, self.group if self.group is not None else dist.group.WORLD)
-        offset_bytes = self.begin * full.element_size()
-        plan.set_output_peers([int(ptr) + offset_bytes for ptr in handle.buffer_ptrs], self.out_features)
-        self._fused = (full, handle)
+        plans = list(plans) if isinstance(plans, (list, tuple)) else [plans]
+        group = self.group if self.group is not None else dist.group.WORLD
+        slots = []
+        for plan in plans:
+            full = symm_mem.empty(tokens, self.out_features, dtype=dtype, device="cuda")
+            handle = symm_mem.rendezvous(full, group)
+            offset_bytes = self.begin * full.element_size()
+            plan.set_output_peers([int(ptr) + offset_bytes for ptr in handle.buffer_ptrs], self.out_features)
+            slots.append((plan, full, handle))
+        self._fused = slots
+        self._step = 0
+        self.active_plan = slots[0][0]
 
     def forward(self, x: torch.Tensor, assemble: bool = True) -> torch.Tensor:
         if self._fused is not None:
-            full, handle = self._fused
-            handle.barrier(channel=0)   # nobody still reads the previous result out of this rank's buffer
-            self.local_linear(x)        # the epilogue writes this rank's columns into every rank's buffer
-            handle.barrier(channel=1)   # every rank's columns have arrived
+            plan, full, handle = self._fused[self._step % len(self._fused)]
+            self._step += 1
+            self.active_plan = plan
+            if len(self._fused) == 1:
+                handle.barrier(channel=0)  # nobody still reads the previous result out of this rank's only buffer
+            self.local_linear(x)           # the epilogue writes this rank's columns into every rank's buffer
+            handle.barrier(channel=1)      # every rank's columns have arrived
             return full
         y_local = self.local_linear(x)
         if self.world == 1:

@@ -45,10 +45,13 @@ def _worker(rank, world, port, result):
         plan_fused = ops.Fp4TnMatmulPlan(m, e - b, k)
         lin_fused = parallel.ColumnShardedLinear(n, lambda t: plan_fused.run(ops.quantize_nvfp4_rowscale(t), shard))
         lin_fused.fuse_into(plan_fused, m)
-        for _ in range(3):  # repeated steps reuse the symmetric buffer
-            y_fused = lin_fused.forward(x)
-        torch.cuda.synchronize()
-        ok_dense = ok_dense and bool(torch.equal(y_fused, y_ref)) and plan_fused.status() == 0
+        for code in (0, 512):  # plain peer stores (tile shape chosen by the plan), then CTA pairs with TMA stores to the peers
+            if code:
+                plan_fused.set_block_n(code)
+            for _ in range(3):  # repeated steps reuse the symmetric buffer
+                y_fused = lin_fused.forward(x)
+            torch.cuda.synchronize()
+            ok_dense = ok_dense and bool(torch.equal(y_fused, y_ref)) and plan_fused.status() == 0
 
         # ---- MoE: expert parallel vs single GPU
         tokens, experts, top_k, hidden, inter = 64 * world, 8, 2, 256, 128
