@@ -781,7 +781,11 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         if (plan->path == kDecodeStream) return cudaErrorInvalidValue;
     }
     const bool many = plan->many_splits != 0 && (plan->path == kDecodeFusedMany || plan->path == kDecodeAuto);
-    if (tokens <= 2 && plan->path != kDecodeSplit && (many || plan->fused_splits != 0) && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
+    // the single-launch kernel holds 16 operand rows: up to four bf16 tokens (four terms each) or two f32 tokens (eight
+    // terms); every CTA expands its slice token after token, which is worth it up to three tokens (13.7 us against
+    // 15.5 us for the expansion kernel + GEMV at K = 5120, N = 13824)
+    const uint32_t fused_tokens = input_is_bf16 ? 3u : 2u;
+    if (tokens <= fused_tokens && plan->path != kDecodeSplit && (many || plan->fused_splits != 0) && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
         // one launch: the activation is expanded inside the GEMV CTAs
         CUtensorMap map_w;
         cudaError_t fst = make_map(&map_w, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);

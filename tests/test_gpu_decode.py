@@ -37,7 +37,8 @@ def test_expansion_reconstructs_activation(ops, oracle, terms):
         assert np.array_equal(col.cpu().numpy(), r0)
 
 
-@pytest.mark.parametrize("tokens,n,k", [(1, 128, 256), (1, 13824, 5120), (1, 5120, 13824), (3, 1000, 2048), (8, 7168, 5120),
+@pytest.mark.parametrize("tokens,n,k", [(1, 128, 256), (1, 13824, 5120), (1, 5120, 13824), (2, 640, 1056), (3, 1000, 2048),
+                                        (4, 5120, 13824), (8, 7168, 5120),
                                         (32, 520, 1024), (33, 512, 1024), (64, 2048, 5120)])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
