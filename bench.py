@@ -293,8 +293,7 @@ def main():
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: how the column blocks become [M, N] on every rank: GEMM epilogue stores into every "
-                         "rank's output (symmetric memory) or NCCL all-gather + re-assembly; auto = fused on the rank "
-                         "counts it has been measured on")
+                         "rank's output (symmetric memory) or NCCL all-gather + re-assembly; auto = fused on 2, 4 and 8 ranks")
     ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe"],
                     help="prefill (default, the contract line), or the single-GPU decode / MoE configs")
     args = ap.parse_args()
@@ -355,7 +354,7 @@ def main():
 
     sharded = parallel.ColumnShardedLinear(N, local_linear)
     gather = "none" if world == 1 else "nccl"
-    FUSED_MEASURED_ON = (2,)
+    FUSED_MEASURED_ON = (2, 4, 8)  # verified on 2 and 8 ranks of one box
     if world > 1 and (args.gather == "fused" or (args.gather == "auto" and world in FUSED_MEASURED_ON)):
         try:
             plan_b = ops.Fp4TnMatmulPlan(M, n_local, K)  # second output buffer: one barrier per step is enough
