@@ -11,7 +11,8 @@ scale, per-16 E4M3 scales) + the block-scaled tcgen05 GEMM with bf16 output.  In
 Prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`), the same through the public
 API with host buffers (`e2e`), the roofline of the dominant kernel, and the reference's CPU path timed on
 the host cores (`cpu_baseline`).  With --gpus N > 1 (launched by torchrun) the weight is sharded over N
-column-wise and the bf16 outputs are all-gathered over NCCL (strong scaling of the same workload).
+column-wise; the bf16 column blocks are written into every rank's output by the GEMM epilogue (symmetric memory, --gather
+fused) or all-gathered over NCCL (--gather nccl); strong scaling of the same workload.
 """
 from __future__ import annotations
 
