@@ -392,6 +392,36 @@ __global__ void __launch_bounds__(kExpandThreads) expand_nvfp4_terms_kernel(cons
     }
 }
 
+// Fused SiLU(gate) * up -> NVFP4 quantize (crates/eider-cuda/native/non_gemm.cu:559-629): the producer in front of the
+// down projection without the fp32 round trip.  gate = row[0..k), up = row[k..2k), sigmoid = 1 / (1 + expf(-g)),
+// value = (g * sigmoid * up) / input_scale in that order, then the block quantizer.  One thread per 16-element block,
+// grid = (blocks of 256 threads, tokens); k is a multiple of 16 and rows are 16-byte aligned on this path.
+__global__ void __launch_bounds__(256) silu_mul_quantize_nvfp4_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ packed,
+                                                                      uint8_t* __restrict__ scales, uint32_t k, float input_scale) {
+    const uint32_t token = blockIdx.y;
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= k / 16) return;
+    const float* gate = gate_up + static_cast<size_t>(token) * 2 * k + b * 16;
+    const float* up = gate + k;
+    const Divisor di = make_divisor(input_scale);
+    float v[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float4 g4 = __ldg(reinterpret_cast<const float4*>(gate) + q);
+        const float4 u4 = __ldg(reinterpret_cast<const float4*>(up) + q);
+        const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float sigmoid = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g[i])));
+            v[4 * q + i] = div_rn(__fmul_rn(__fmul_rn(g[i], sigmoid), u[i]), di);
+        }
+    }
+    uint2 bytes;
+    const uint8_t sc = quantize_block16(v, 16, &bytes);
+    *reinterpret_cast<uint2*>(packed + static_cast<size_t>(token) * (k / 2) + b * 8) = bytes;
+    scales[tiled_scale_offset(token, b, k)] = sc;
+}
+
 // Per-token dynamic FP8: s = amax / 448 (1 when 0), q = e4m3(x / s)
 // (crates/eider-cuda/native/non_gemm.cu:9952-9974, 10028-10066).
 template <typename T, bool DYNAMIC>
@@ -528,6 +558,22 @@ cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input
         expand_nvfp4_terms_kernel<float><<<grid, kExpandThreads, 0, stream>>>(static_cast<const float*>(input), packed, scales,
                                                                               col_scale, in_features, terms);
     return cudaGetLastError();
+}
+
+cudaError_t eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream(const float* gate_up, uint8_t* packed, uint8_t* scales,
+                                                                      uint32_t tokens, uint32_t rows, float input_scale,
+                                                                      cudaStream_t stream) {
+    if (!gate_up || !packed || !scales || tokens == 0 || rows == 0 || rows % 16 != 0 || bad_scale(input_scale) ||
+        (reinterpret_cast<uintptr_t>(gate_up) & 15) != 0 || (reinterpret_cast<uintptr_t>(packed) & 7) != 0)
+        return cudaErrorInvalidValue;
+    const dim3 grid((rows / 16 + 255) / 256, tokens);
+    silu_mul_quantize_nvfp4_kernel<<<grid, 256, 0, stream>>>(gate_up, packed, scales, rows, input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream(const float* gate_up, uint8_t* packed, uint8_t* scales,
+                                                                         uint32_t rows, float input_scale, cudaStream_t stream) {
+    return eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream(gate_up, packed, scales, 1, rows, input_scale, stream);
 }
 
 cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(const float* input, uint8_t* quantized_input,

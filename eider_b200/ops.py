@@ -475,6 +475,23 @@ class Fp8DecodePlan:
             pass
 
 
+def silu_mul_halves_quantize_nvfp4(gate_up: torch.Tensor, input_scale: float = 1.0) -> "Nvfp4Matrix":
+    """Fused SiLU(gate) * up -> NVFP4 of [tokens, 2K] f32 rows (gate half first): the activation of the down projection
+    without the fp32 round trip (the reference's infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream)."""
+    if gate_up.dim() == 1:
+        gate_up = gate_up.unsqueeze(0)
+    _need(gate_up, torch.float32, "gate_up")
+    tokens, two_k = gate_up.shape
+    k = two_k // 2
+    if two_k % 32 != 0:
+        raise ShapeError("the intermediate size must be a multiple of 16")
+    out = Nvfp4Matrix.zeros(tokens, k, gate_up.device)
+    check("eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream",
+          _lib.load().eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream(
+              gate_up.data_ptr(), out.packed.data_ptr(), out.scales.data_ptr(), tokens, k, input_scale, _stream()))
+    return out
+
+
 def expand_nvfp4_terms(x: torch.Tensor, terms: int):
     """Residual NVFP4 expansion (packed [tokens*terms, K/2], tiled scales, per-row f32 scales)."""
     lib = _lib.load()

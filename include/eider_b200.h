@@ -70,6 +70,18 @@ EIDER_B200_API cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* i
 /* ue4m3_scale_layout_len, crates/eider-cuda/src/format.rs:194-198. */
 EIDER_B200_API size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner);
 
+/* Fused producer SiLU(gate) * up -> NVFP4 (crates/eider-cuda/src/ffi.rs:2441;
+ * crates/eider-cuda/native/non_gemm.cu:559-629): gate_up holds `rows` gate values followed by `rows` up values of one
+ * token; packed [rows/2], scales tiled with outer = 0.  This implementation needs rows % 16 == 0 and a 16-byte aligned
+ * input.  The batch form takes [tokens][2 * rows] and tiles the scales with outer = token. */
+EIDER_B200_API cudaError_t infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream(const float* gate_up, uint8_t* packed,
+                                                                                        uint8_t* scales, uint32_t rows,
+                                                                                        float input_scale, cudaStream_t stream);
+EIDER_B200_API cudaError_t eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream(const float* gate_up, uint8_t* packed,
+                                                                                     uint8_t* scales, uint32_t tokens,
+                                                                                     uint32_t rows, float input_scale,
+                                                                                     cudaStream_t stream);
+
 /* ---- FP8 E4M3 quantizers -------------------------------------------------------------------- */
 
 /* crates/eider-cuda/src/ffi.rs:3198 and :3206 (kernels non_gemm.cu:9952-9974, 10028-10066). */

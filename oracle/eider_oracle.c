@@ -601,6 +601,30 @@ ORACLE_API void oracle_moe_silu_mul_quantize(const uint16_t* gate_up, const uint
     free(row);
 }
 
+/* Fused SiLU(gate) * up -> NVFP4 quantize of `tokens` activation rows (the producer in front of the down projection):
+ * crates/eider-cuda/native/non_gemm.cu:559-629 (one token: gate = gate_up[0..k), up = gate_up[k..2k),
+ * sigmoid = 1 / (1 + expf(-g)), value = g * sigmoid * up, then the activation quantizer with `input_scale`;
+ * scales tiled with outer = token).  `act_out` (may be NULL) receives the fp32 products. */
+ORACLE_API void oracle_silu_mul_halves_quantize_nvfp4(const float* gate_up, size_t tokens, size_t k, float input_scale,
+                                                      uint8_t* packed, uint8_t* scales, float* act_out) {
+    size_t blocks = (k + 15) / 16;
+    uint8_t* tmp = (uint8_t*)malloc(blocks);
+    float* row = (float*)malloc(k * sizeof(float));
+    for (size_t t = 0; t < tokens; ++t) {
+        const float* g = gate_up + t * 2 * k;
+        const float* u = g + k;
+        for (size_t i = 0; i < k; ++i) {
+            float sigmoid = 1.0f / (1.0f + expf(-g[i]));
+            row[i] = g[i] * sigmoid * u[i];
+        }
+        if (act_out) memcpy(act_out + t * k, row, k * sizeof(float));
+        quantize_row(row, k, input_scale, packed + t * ((k + 1) / 2), tmp);
+        for (size_t b = 0; b < blocks; ++b) scales[oracle_tiled_scale_offset(t, b, k)] = tmp[b];
+    }
+    free(tmp);
+    free(row);
+}
+
 /* Grouped W4A4 GEMM: per expert D_e[row][m] = alpha_e * sum_k X_e[row][k] * W_e[m][k], rounded to
  * bf16 (crates/eider-cuda/native/cutlass_grouped_gemm.cu:116-164; output [route][m],
  * non_gemm.cu:3080-3083).  Activations dequantised from the per-expert tiled scales. */

@@ -84,6 +84,7 @@ _gather_q = _sig("oracle_moe_gather_quantize", None, _f32p, _u32p, _u32p, _u32p,
                  C.c_int, _u8p, _u8p)
 _silu_q = _sig("oracle_moe_silu_mul_quantize", None, _u16p, _u32p, _u32p, _sz, _sz, _sz, _u8p, _u8p,
                C.c_void_p)
+_silu_dense = _sig("oracle_silu_mul_halves_quantize_nvfp4", None, _f32p, _sz, _sz, C.c_float, _u8p, _u8p, C.c_void_p)
 _grouped = _sig("oracle_moe_grouped_gemm", None, _u8p, _u8p, _u32p, _sz, _sz, _u8p, _u8p, _f32p, _sz,
                 _sz, _u16p)
 _combine = _sig("oracle_moe_combine", None, _u32p, _f32p, _u16p, _sz, _sz, _sz, _f32p)
@@ -344,6 +345,20 @@ def moe_silu_mul_quantize(gate_up_bits, sorted_experts, offsets, experts, want_a
     act = np.zeros((r, k), np.float32) if want_act else None
     _silu_q(gu, sorted_experts, offsets, r, k, tile, packed, scales,
             act.ctypes.data if act is not None else None)
+    return (packed, scales, act) if want_act else (packed, scales)
+
+
+def silu_mul_halves_quantize_nvfp4(gate_up, input_scale=1.0, want_act=False):
+    """gate_up [tokens, 2K] f32 -> (packed [tokens, K/2], tiled scales[, fp32 products]); non_gemm.cu:559-629."""
+    gu = _f32(gate_up)
+    if gu.ndim == 1:
+        gu = gu[None]
+    t, two_k = gu.shape
+    k = two_k // 2
+    packed = np.zeros((t, k // 2), np.uint8)
+    scales = np.zeros(scale_layout_len(t, k), np.uint8)
+    act = np.zeros((t, k), np.float32) if want_act else None
+    _silu_dense(np.ascontiguousarray(gu), t, k, float(input_scale), packed, scales, act.ctypes.data if act is not None else None)
     return (packed, scales, act) if want_act else (packed, scales)
 
 

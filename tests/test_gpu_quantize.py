@@ -150,3 +150,32 @@ def test_fp8_static_and_weight(ops, oracle):
     wqo, wso = oracle.quantize_fp8_weight(w)
     assert np.array_equal(ws.cpu().numpy(), wso)
     assert np.array_equal(wq.cpu().numpy(), wqo)
+
+
+@pytest.mark.parametrize("tokens,k,scale", [(1, 768, 1.0), (1, 13824, 0.03125), (5, 2048, 1.0), (130, 256, 0.5)])
+def test_fused_silu_mul_quantize_matches_oracle(ops, oracle, tokens, k, scale):
+    # non_gemm.cu:559-629: value = g * (1 / (1 + expf(-g))) * up / input_scale, then the block quantizer; the device's
+    # expf may differ from the host's in the last place, which can move a code across a rounding boundary now and then
+    import torch
+    rng = np.random.default_rng(tokens + k)
+    gu = (rng.standard_normal((tokens, 2 * k)) * 2.0).astype(np.float32)
+    gu[0, :16] = 0.0  # an all-zero block: scale byte 0, codes 0
+    q = ops.silu_mul_halves_quantize_nvfp4(torch.from_numpy(gu).cuda(), scale)
+    torch.cuda.synchronize()
+    p_ref, s_ref, act = oracle.silu_mul_halves_quantize_nvfp4(gu, scale, want_act=True)
+    got_p, got_s = q.packed.cpu().numpy(), q.scales.cpu().numpy()
+    assert np.count_nonzero(got_p != p_ref) / got_p.size < 2e-3
+    assert np.count_nonzero(got_s != s_ref) / got_s.size < 2e-3
+    deq = oracle.dequantize_tiled(got_p, got_s) * scale
+    bmax = np.abs(act).reshape(tokens, -1, 16).max(axis=2).repeat(16, axis=1)
+    assert np.all(np.abs(deq - act) <= 0.27 * bmax + 1e-12)
+    if tokens == 1:  # the reference's single-token entry point gives the same bytes
+        from eider_b200 import _lib
+        lib = _lib.load()
+        p1 = torch.zeros(k // 2, dtype=torch.uint8, device="cuda")
+        s1 = torch.zeros_like(q.scales)
+        assert lib.infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream(
+            torch.from_numpy(gu).cuda().data_ptr(), p1.data_ptr(), s1.data_ptr(), k, scale, None) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(p1.cpu().numpy(), got_p[0]) and np.array_equal(s1.cpu().numpy(), got_s)
+        assert lib.infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream(None, p1.data_ptr(), s1.data_ptr(), k, scale, None) == 1

@@ -215,3 +215,19 @@ def test_gemm_fixture_lcg(oracle):
     # the reference's host path (unpack, then f32 matmul) gives the same numbers
     y2 = oracle.nvfp4_linear_host(xd, wp, ws, 0.5)
     assert np.allclose(y2, y, rtol=1e-5, atol=1e-4)
+
+
+def test_fused_silu_mul_quantize_oracle_is_the_staged_path():
+    # non_gemm.cu:559-629 against the staged form: silu-mul in fp32 (same operation order), then the activation quantizer
+    from oracle import oracle as o
+    rng = np.random.default_rng(3)
+    k = 96
+    gu = (rng.standard_normal((3, 2 * k)) * 2.0).astype(np.float32)
+    packed, scales, act = o.silu_mul_halves_quantize_nvfp4(gu, 0.25, want_act=True)
+    g, u = gu[:, :k], gu[:, k:]
+    one = np.float32(1.0)
+    sig = one / (one + np.exp(-g).astype(np.float32))
+    staged = (g * sig).astype(np.float32) * u
+    assert np.allclose(act, staged, rtol=2e-6, atol=0)  # numpy's exp may differ from libm's expf in the last place
+    p2, s2 = o.quantize_nvfp4(act, 0.25)
+    assert np.array_equal(packed, p2) and np.array_equal(scales, s2)
