@@ -422,6 +422,55 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_nvfp4_kernel(const floa
     scales[tiled_scale_offset(token, b, k)] = sc;
 }
 
+// Fused RMSNorm -> NVFP4 quantize (crates/eider-cuda/native/non_gemm.cu:193-288): one CTA per row.  Pass one sums the
+// squares (per-thread strided partial sums, warp shuffles, then the warp sums in warp order: a fixed order for a given
+// launch shape), pass two gives every thread 16-element blocks: value = x * inverse_rms * weight / input_scale in that
+// order, then the block quantizer.  The row is read twice; the second read hits L1/L2.
+__global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const float* __restrict__ input, const float* __restrict__ weight,
+                                                                      uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                                                                      uint32_t cols, float eps, float input_scale) {
+    __shared__ float red[8];
+    __shared__ float inverse_rms;
+    const uint32_t row = blockIdx.x;
+    const float* x = input + static_cast<size_t>(row) * cols;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
+        inverse_rms = rsqrtf(__fdiv_rn(total, static_cast<float>(cols)) + eps);
+    }
+    __syncthreads();
+    const float inv = inverse_rms;
+    const Divisor di = make_divisor(input_scale);
+    for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+        float v[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 x4 = __ldg(reinterpret_cast<const float4*>(x + b * 16) + q);
+            const float4 w4 = __ldg(reinterpret_cast<const float4*>(weight + b * 16) + q);
+            v[4 * q + 0] = div_rn(__fmul_rn(__fmul_rn(x4.x, inv), w4.x), di);
+            v[4 * q + 1] = div_rn(__fmul_rn(__fmul_rn(x4.y, inv), w4.y), di);
+            v[4 * q + 2] = div_rn(__fmul_rn(__fmul_rn(x4.z, inv), w4.z), di);
+            v[4 * q + 3] = div_rn(__fmul_rn(__fmul_rn(x4.w, inv), w4.w), di);
+        }
+        uint2 bytes;
+        const uint8_t sc = quantize_block16(v, 16, &bytes);
+        *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (cols / 2) + b * 8) = bytes;
+        scales[tiled_scale_offset(row, b, cols)] = sc;
+    }
+}
+
 // Per-token dynamic FP8: s = amax / 448 (1 when 0), q = e4m3(x / s)
 // (crates/eider-cuda/native/non_gemm.cu:9952-9974, 10028-10066).
 template <typename T, bool DYNAMIC>
@@ -557,6 +606,17 @@ cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input
     else
         expand_nvfp4_terms_kernel<float><<<grid, kExpandThreads, 0, stream>>>(static_cast<const float*>(input), packed, scales,
                                                                               col_scale, in_features, terms);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(const float* input, const float* weight, uint8_t* packed,
+                                                                  uint8_t* scales, uint32_t rows, uint32_t cols, float eps,
+                                                                  float input_scale, cudaStream_t stream) {
+    if (!input || !weight || !packed || !scales || rows == 0 || cols == 0 || cols % 16 != 0 || bad_scale(input_scale) ||
+        ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(weight)) & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(packed) & 7) != 0)
+        return cudaErrorInvalidValue;
+    rms_norm_quantize_nvfp4_kernel<<<rows, 256, 0, stream>>>(input, weight, packed, scales, cols, eps, input_scale);
     return cudaGetLastError();
 }
 

@@ -475,6 +475,21 @@ class Fp8DecodePlan:
             pass
 
 
+def rms_norm_quantize_nvfp4(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, input_scale: float = 1.0) -> "Nvfp4Matrix":
+    """Fused RMSNorm -> NVFP4 of [rows, cols] f32 (the reference's infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream)."""
+    _need(x, torch.float32, "input")
+    _need(weight, torch.float32, "weight")
+    rows, cols = x.shape
+    if weight.numel() != cols:
+        raise ShapeError("weight length must equal the row length")
+    out = Nvfp4Matrix.zeros(rows, cols, x.device)
+    check("infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream",
+          _lib.load().infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(
+              x.data_ptr(), weight.data_ptr(), out.packed.data_ptr(), out.scales.data_ptr(), rows, cols, eps, input_scale,
+              _stream()))
+    return out
+
+
 def silu_mul_halves_quantize_nvfp4(gate_up: torch.Tensor, input_scale: float = 1.0) -> "Nvfp4Matrix":
     """Fused SiLU(gate) * up -> NVFP4 of [tokens, 2K] f32 rows (gate half first): the activation of the down projection
     without the fp32 round trip (the reference's infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream)."""

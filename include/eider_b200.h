@@ -70,6 +70,14 @@ EIDER_B200_API cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* i
 /* ue4m3_scale_layout_len, crates/eider-cuda/src/format.rs:194-198. */
 EIDER_B200_API size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner);
 
+/* Fused producer RMSNorm -> NVFP4 (crates/eider-cuda/native/non_gemm.cu:193-288): input [rows][cols] f32, weight [cols];
+ * value = x * rsqrt(mean(x^2) + eps) * weight / input_scale, then the activation quantizer; scales tiled with outer = row.
+ * This implementation needs cols % 16 == 0 and 16-byte aligned input and weight. */
+EIDER_B200_API cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(const float* input, const float* weight,
+                                                                                 uint8_t* packed, uint8_t* scales, uint32_t rows,
+                                                                                 uint32_t cols, float eps, float input_scale,
+                                                                                 cudaStream_t stream);
+
 /* Fused producer SiLU(gate) * up -> NVFP4 (crates/eider-cuda/src/ffi.rs:2441;
  * crates/eider-cuda/native/non_gemm.cu:559-629): gate_up holds `rows` gate values followed by `rows` up values of one
  * token; packed [rows/2], scales tiled with outer = 0.  This implementation needs rows % 16 == 0 and a 16-byte aligned

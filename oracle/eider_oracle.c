@@ -625,6 +625,41 @@ ORACLE_API void oracle_silu_mul_halves_quantize_nvfp4(const float* gate_up, size
     free(row);
 }
 
+/* Fused RMSNorm -> NVFP4 quantize: crates/eider-cuda/native/non_gemm.cu:193-288
+ * (inverse_rms = rsqrtf(sum(x^2) / cols + eps); value = x * inverse_rms * weight / input_scale in that order; block
+ * maximum over |value| without a finiteness test; then scale byte and codes as in the activation quantizer).  The
+ * reference sums the squares in a thread-strided tree whose order depends on the launch shape; this restatement sums
+ * in double and rounds once, so a device result may differ from it by an ulp of inverse_rms.  `norm_out` may be NULL. */
+ORACLE_API void oracle_rms_norm_quantize_nvfp4(const float* input, const float* weight, size_t rows, size_t cols, float eps,
+                                               float input_scale, uint8_t* packed, uint8_t* scales, float* norm_out) {
+    size_t blocks = (cols + 15) / 16;
+    float* row = (float*)malloc(cols * sizeof(float));
+    for (size_t r = 0; r < rows; ++r) {
+        const float* x = input + r * cols;
+        double ss = 0.0;
+        for (size_t i = 0; i < cols; ++i) ss += (double)x[i] * (double)x[i];
+        float mean = (float)ss / (float)cols + eps;
+        float inv = 1.0f / sqrtf(mean);
+        for (size_t i = 0; i < cols; ++i) row[i] = x[i] * inv * weight[i] / input_scale;
+        if (norm_out) memcpy(norm_out + r * cols, row, cols * sizeof(float));
+        uint8_t* prow = packed + r * ((cols + 1) / 2);
+        for (size_t b = 0; b < blocks; ++b) {
+            size_t start = b * 16, end = start + 16 < cols ? start + 16 : cols;
+            float amax = 0.0f;
+            for (size_t i = start; i < end; ++i) amax = fmaxf(amax, fabsf(row[i]));
+            uint8_t sc = amax == 0.0f ? 0 : oracle_ue4m3_code(amax / 6.0f);
+            float sv = oracle_e4m3_value(sc);
+            scales[oracle_tiled_scale_offset(r, b, cols)] = sc;
+            for (size_t i = start; i < end; ++i) {
+                uint8_t code = oracle_e2m1_code(sv == 0.0f ? 0.0f : row[i] / sv);
+                if ((i & 1) == 0) prow[i / 2] = code;
+                else prow[i / 2] |= (uint8_t)(code << 4);
+            }
+        }
+    }
+    free(row);
+}
+
 /* Grouped W4A4 GEMM: per expert D_e[row][m] = alpha_e * sum_k X_e[row][k] * W_e[m][k], rounded to
  * bf16 (crates/eider-cuda/native/cutlass_grouped_gemm.cu:116-164; output [route][m],
  * non_gemm.cu:3080-3083).  Activations dequantised from the per-expert tiled scales. */

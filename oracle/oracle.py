@@ -85,6 +85,7 @@ _gather_q = _sig("oracle_moe_gather_quantize", None, _f32p, _u32p, _u32p, _u32p,
 _silu_q = _sig("oracle_moe_silu_mul_quantize", None, _u16p, _u32p, _u32p, _sz, _sz, _sz, _u8p, _u8p,
                C.c_void_p)
 _silu_dense = _sig("oracle_silu_mul_halves_quantize_nvfp4", None, _f32p, _sz, _sz, C.c_float, _u8p, _u8p, C.c_void_p)
+_rms_q = _sig("oracle_rms_norm_quantize_nvfp4", None, _f32p, _f32p, _sz, _sz, C.c_float, C.c_float, _u8p, _u8p, C.c_void_p)
 _grouped = _sig("oracle_moe_grouped_gemm", None, _u8p, _u8p, _u32p, _sz, _sz, _u8p, _u8p, _f32p, _sz,
                 _sz, _u16p)
 _combine = _sig("oracle_moe_combine", None, _u32p, _f32p, _u16p, _sz, _sz, _sz, _f32p)
@@ -360,6 +361,18 @@ def silu_mul_halves_quantize_nvfp4(gate_up, input_scale=1.0, want_act=False):
     act = np.zeros((t, k), np.float32) if want_act else None
     _silu_dense(np.ascontiguousarray(gu), t, k, float(input_scale), packed, scales, act.ctypes.data if act is not None else None)
     return (packed, scales, act) if want_act else (packed, scales)
+
+
+def rms_norm_quantize_nvfp4(x, weight, eps=1e-6, input_scale=1.0, want_norm=False):
+    """x [rows, cols] f32, weight [cols] -> (packed, tiled scales[, normalised fp32 values]); non_gemm.cu:193-288."""
+    x = _f32(x)
+    rows, cols = x.shape
+    packed = np.zeros((rows, (cols + 1) // 2), np.uint8)
+    scales = np.zeros(scale_layout_len(rows, cols), np.uint8)
+    norm = np.zeros((rows, cols), np.float32) if want_norm else None
+    _rms_q(np.ascontiguousarray(x), _f32(weight), rows, cols, float(eps), float(input_scale), packed, scales,
+           norm.ctypes.data if norm is not None else None)
+    return (packed, scales, norm) if want_norm else (packed, scales)
 
 
 def moe_grouped_gemm(act_packed, act_scales, offsets, w_packed, w_scales, alpha):

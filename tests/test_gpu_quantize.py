@@ -179,3 +179,25 @@ def test_fused_silu_mul_quantize_matches_oracle(ops, oracle, tokens, k, scale):
         torch.cuda.synchronize()
         assert np.array_equal(p1.cpu().numpy(), got_p[0]) and np.array_equal(s1.cpu().numpy(), got_s)
         assert lib.infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream(None, p1.data_ptr(), s1.data_ptr(), k, scale, None) == 1
+
+
+@pytest.mark.parametrize("rows,cols,scale", [(1, 5120, 1.0), (7, 2048, 0.25), (300, 256, 1.0)])
+def test_fused_rms_norm_quantize_matches_oracle(ops, oracle, rows, cols, scale):
+    # non_gemm.cu:193-288: x * rsqrt(mean(x^2) + eps) * weight / input_scale, then the block quantizer.  The sum of
+    # squares has no canonical order (and the device uses rsqrtf), so inverse_rms may differ from the oracle's by an
+    # ulp or two, which moves a code across a rounding boundary now and then.
+    import torch
+    rng = np.random.default_rng(rows + cols)
+    x = (rng.standard_normal((rows, cols)) * np.exp(rng.uniform(-1, 1, (rows, 1)))).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    q = ops.rms_norm_quantize_nvfp4(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-6, scale)
+    torch.cuda.synchronize()
+    p_ref, s_ref, norm = oracle.rms_norm_quantize_nvfp4(x, w, 1e-6, scale, want_norm=True)
+    got_p, got_s = q.packed.cpu().numpy(), q.scales.cpu().numpy()
+    assert np.count_nonzero(got_p != p_ref) / got_p.size < 5e-3
+    assert np.count_nonzero(got_s != s_ref) / got_s.size < 5e-3
+    deq = oracle.dequantize_tiled(got_p, got_s)
+    bmax = np.abs(norm).reshape(rows, -1, 16).max(axis=2).repeat(16, axis=1)
+    assert np.all(np.abs(deq - norm) <= 0.27 * bmax + 1e-12)
+    from eider_b200 import _lib
+    assert _lib.load().infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(None, None, None, None, rows, cols, 1e-6, scale, None) == 1
