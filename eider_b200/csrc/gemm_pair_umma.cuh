@@ -292,7 +292,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
                 umma::tmem_load_32x32(taddr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
             };
-            const bool wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
+            const bool wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
                               (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             const bool staged = p.out_maps != nullptr;  // (the host sets the maps only for plain bf16 output)
             constexpr uint32_t kSteps = kPairN / 64;
@@ -319,7 +319,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     }
                     ++store_count;
                     uint32_t w[32];
-                    convert_bf16x64_scaled(&raw[step & 1][0], rs, w);
+                    convert_bf16x64_scaled(&raw[step & 1][0], rs, nullptr, w);  // (no column scales on this path: the host checks)
                     const uint32_t row_base = umma::smem_u32(sbuf) + lane * 128;
 #pragma unroll
                     for (uint32_t ch = 0; ch < 8; ++ch)
@@ -339,7 +339,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 }
                 if (!row_ok) continue;
                 if (wide) {
-                    store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs);
+                    store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs,
+                                    p.col_scale ? p.col_scale + t.col0 + c : nullptr);
                 } else {
 #pragma unroll
                     for (uint32_t i = 0; i < 64; ++i) {  // fully unrolled: the accumulator stays in registers

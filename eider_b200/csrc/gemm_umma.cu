@@ -199,20 +199,28 @@ bool dense_shape_ok(int kind, uint32_t m, uint32_t n, uint32_t k) {
 }
 
 uint32_t pick_block_n(uint32_t m, uint32_t n) {
-    // Fill the machine: prefer 256-wide weight tiles, fall back to narrower ones when the tile count is small.
+    // Cost model in MMA-cycles per K step: the slowest SM runs `waves` tiles, and an MMA retires in about 128 cycles at
+    // N = 256 but never under about 103 however narrow it is, so narrower tiles only pay when they save a whole wave.
     const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
     const uint32_t sms = static_cast<uint32_t>(sm_count());
-    // Two or more row tiles and enough 256 x 256 tiles for every pair of SMs: CTA pairs (half the weight-tile fill
-    // per CTA).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
+    uint32_t best = 64;
+    float best_cost = 1e30f;
+    for (uint32_t bn : {256u, 128u, 64u}) {
+        const uint32_t tiles = row_tiles * ((n + bn - 1) / bn);
+        const float cost = static_cast<float>((tiles + sms - 1) / sms) * (bn == 256u ? 128.0f : 103.0f);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    // Two or more row tiles: 256 x 256 tiles on CTA pairs (each CTA fills only half of the weight tile, measured about 7 %
+    // faster than one-CTA 256-wide tiles).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
     if (row_tiles >= 2 && (row_tiles % 2 == 0 || row_tiles >= 9)) {
         const uint32_t pair_items = ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN);
-        if (pair_items >= sms / 2) return kPairBlockCode;
+        const float cost = static_cast<float>((pair_items + sms / 2 - 1) / (sms / 2)) * 128.0f * 0.93f;
+        if (cost <= best_cost) return kPairBlockCode;
     }
-    for (uint32_t bn : {256u, 128u, 64u}) {
-        uint32_t tiles = row_tiles * ((n + bn - 1) / bn);
-        if (tiles >= sms || bn == 64u) return bn;
-    }
-    return 64u;
+    return best;
 }
 
 }  // namespace

@@ -225,7 +225,20 @@ template <> __device__ __forceinline__ void store_chunk32<false>(void* out, size
 
 // 32 fp32 accumulator columns -> 32 bf16 (scaled), written with two 32-byte stores.  A thread owns one output row, so
 // every store instruction of a warp touches 32 different lines; wider stores halve the number of such instructions.
-__device__ __forceinline__ void convert_bf16x64_scaled(const uint32_t* raw, float scale, uint32_t (&w)[32]) {
+// `col_scale` (may be null) points at the per-column scales of these 64 columns, 16-byte aligned; every lane reads the
+// same addresses, so the loads are broadcasts out of L1.
+__device__ __forceinline__ void convert_bf16x64_scaled(const uint32_t* raw, float scale, const float* col_scale, uint32_t (&w)[32]) {
+    if (col_scale) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(col_scale) + q);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(raw[4 * q]) * scale * c.x, __uint_as_float(raw[4 * q + 1]) * scale * c.y);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(raw[4 * q + 2]) * scale * c.z, __uint_as_float(raw[4 * q + 3]) * scale * c.w);
+            w[2 * q] = *reinterpret_cast<uint32_t*>(&h0);
+            w[2 * q + 1] = *reinterpret_cast<uint32_t*>(&h1);
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(raw[2 * i]) * scale, __uint_as_float(raw[2 * i + 1]) * scale);
@@ -241,9 +254,10 @@ __device__ __forceinline__ void store_bf16x64(uint16_t* dst, const uint32_t (&w)
                      : "memory");
 }
 // 64 fp32 accumulator columns of one row -> 64 scaled bf16 at element offset `offset` of every output buffer
-__device__ __forceinline__ void store_row64_all(const Params& p, size_t offset, const uint32_t* raw, float scale) {
+__device__ __forceinline__ void store_row64_all(const Params& p, size_t offset, const uint32_t* raw, float scale,
+                                                const float* col_scale) {
     uint32_t w[32];
-    convert_bf16x64_scaled(raw, scale, w);
+    convert_bf16x64_scaled(raw, scale, col_scale, w);
     for_each_out(p, [&](void* base) { store_bf16x64(static_cast<uint16_t*>(base) + offset, w); });
 }
 
@@ -493,7 +507,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             bool wide = false;
             if constexpr (kWide) {
                 const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
-                wide = p.out_is_bf16 && !p.col_scale && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
+                wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
                        t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             }
             if constexpr (kWide) if (wide) {
@@ -517,7 +531,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
                     }
-                    if (row_ok) store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs);
+                    if (row_ok)
+                        store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs,
+                                        p.col_scale ? p.col_scale + (GROUPED ? t.group * p.group_cols : 0) + t.out_col0 + col_of(step) : nullptr);
                 }
                 if (!T::kOverlap) {
                     umma::tmem_load_wait();
