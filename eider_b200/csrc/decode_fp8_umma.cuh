@@ -1,4 +1,4 @@
-// Single-launch FP8 W8A8 decode for one to four tokens (tcgen05 kind::f8f6f4).
+// Single-launch FP8 W8A8 decode for one to eight tokens (tcgen05 kind::f8f6f4).
 //
 // y[t][n] = alpha * s_x[t] * s_w[n] * sum_k e4m3(xq[t][k]) * e4m3(W[n][k]),   xq[t] = e4m3(x[t] / s_x[t]),
 // s_x[t] = amax(x[t]) / 448 (1 when the row is all zero): the reference's per-token dynamic activation quantizer
@@ -22,7 +22,7 @@ namespace decode_fp8 {
 
 constexpr uint32_t kRows = 128;
 constexpr uint32_t kCols = 16;
-constexpr uint32_t kMaxTokens = 4;
+constexpr uint32_t kMaxTokens = 8;
 constexpr uint32_t kStageK = 128;                  // bytes (= elements) of K per stage
 constexpr uint32_t kWeightTile = kRows * kStageK;  // 16 KB
 constexpr uint32_t kActTile = kCols * kStageK;     // 2 KB
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kThreads, 3) fp8_decode_fused_kernel(const __g
     volatile uint32_t* abort_flag = tmem_slot + 1;
     uint32_t* last_flag = tmem_slot + 2;
     float* red = reinterpret_cast<float*>(tmem_slot + 4);  // [4 warps][kMaxTokens]
-    float* x_scale = red + 16;                             // [kMaxTokens]
+    float* x_scale = red + 4 * kMaxTokens;                 // [kMaxTokens]
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t split = blockIdx.x % p.splits, rt = blockIdx.x / p.splits;
@@ -160,7 +160,9 @@ __global__ void __launch_bounds__(kThreads, 3) fp8_decode_fused_kernel(const __g
         umma::griddep_wait();  // x may be the previous kernel's output; scratch, counters and the output are shared with it
         const XT* x = static_cast<const XT*>(p.x);
         // row maxima over the whole K (the scale is per token, not per slice)
-        float amax[kMaxTokens] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float amax[kMaxTokens];
+#pragma unroll
+        for (uint32_t m = 0; m < kMaxTokens; ++m) amax[m] = 0.0f;
         for (uint32_t h = te; h < p.k / 8; h += 128) {
 #pragma unroll
             for (uint32_t m = 0; m < kMaxTokens; ++m) {

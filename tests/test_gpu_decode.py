@@ -119,10 +119,10 @@ def test_fp8_decode_small_and_scalar_scale(ops, oracle):
     assert ok, stats
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 3, 4])
+@pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8])
 @pytest.mark.parametrize("n,k", [(200, 528), (1000, 2048), (5120, 13824)])
 def test_fp8_decode_single_launch(ops, oracle, tokens, n, k):
-    # one to four tokens take the single-launch kernel (quantizer inside the GEMV CTAs, K splits met in scratch):
+    # one to eight tokens take the single-launch kernel (quantizer inside the GEMV CTAs, K splits met in scratch):
     # same codes and scales as the stand-alone quantizer, partial row tiles, a K that is not a multiple of the stage
     import torch
     rng = np.random.default_rng(tokens * 31 + n)
@@ -130,7 +130,7 @@ def test_fp8_decode_single_launch(ops, oracle, tokens, n, k):
     ws = (rng.uniform(0.5, 2.0, n) * 0.01).astype(np.float32)
     x = rng.standard_normal((tokens, k)).astype(np.float32) * np.exp(rng.uniform(-2, 2, (tokens, 1))).astype(np.float32)
     xq, xs = oracle.quantize_fp8_dynamic(x)
-    plan = ops.Fp8DecodePlan(4, n, k)
+    plan = ops.Fp8DecodePlan(8, n, k)
     y = plan.run(_dev(x), _dev(wq), _dev(ws), out_dtype=torch.float32)
     y2 = plan.run(_dev(x), _dev(wq), _dev(ws), out_dtype=torch.float32)  # counters self-reset, fixed summation order
     torch.cuda.synchronize()
