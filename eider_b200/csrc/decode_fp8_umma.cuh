@@ -1,4 +1,4 @@
-// Single-launch FP8 W8A8 decode for one to eight tokens (tcgen05 kind::f8f6f4).
+// Single-launch FP8 W8A8 decode for one to four tokens (tcgen05 kind::f8f6f4).
 //
 // y[t][n] = alpha * s_x[t] * s_w[n] * sum_k e4m3(xq[t][k]) * e4m3(W[n][k]),   xq[t] = e4m3(x[t] / s_x[t]),
 // s_x[t] = amax(x[t]) / 448 (1 when the row is all zero): the reference's per-token dynamic activation quantizer
@@ -22,7 +22,7 @@ namespace decode_fp8 {
 
 constexpr uint32_t kRows = 128;
 constexpr uint32_t kCols = 16;
-constexpr uint32_t kMaxTokens = 8;
+constexpr uint32_t kMaxTokens = 4;
 constexpr uint32_t kStageK = 128;                  // bytes (= elements) of K per stage
 constexpr uint32_t kWeightTile = kRows * kStageK;  // 16 KB
 constexpr uint32_t kActTile = kCols * kStageK;     // 2 KB

@@ -841,9 +841,9 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
     auto* plan = static_cast<DecodePlan*>(raw);
     if (!plan || plan->kind != kFp8 || !input || !weight || !d || tokens == 0 || tokens > plan->max_tokens)
         return cudaErrorInvalidValue;
-    // (the kernel takes up to eight tokens, but every CTA quantizes all of them: beyond four the quantize kernel + GEMV pair
-    // is faster: 19.8 us against 23.9 us at eight tokens, K = 5120, N = 7168)
-    if (tokens <= 4 && plan->many_splits != 0 && plan->path != kDecodeSplit &&
+    // (every CTA quantizes all tokens: beyond four the quantize kernel + GEMV pair is faster, 19.8 us against 23.9 us at
+    // eight tokens, K = 5120, N = 7168)
+    if (tokens <= decode_fp8::kMaxTokens && plan->many_splits != 0 && plan->path != kDecodeSplit &&
         (reinterpret_cast<uintptr_t>(input) & 15) == 0 && plan->k % 16 == 0) {
         // one launch: the per-token quantizer runs inside the GEMV CTAs
         CUtensorMap map_w;

@@ -122,7 +122,7 @@ def test_fp8_decode_small_and_scalar_scale(ops, oracle):
 @pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8])
 @pytest.mark.parametrize("n,k", [(200, 528), (1000, 2048), (5120, 13824)])
 def test_fp8_decode_single_launch(ops, oracle, tokens, n, k):
-    # one to eight tokens take the single-launch kernel (quantizer inside the GEMV CTAs, K splits met in scratch):
+    # one to four tokens take the single-launch kernel (more go through the quantize kernel + GEMV pair) (quantizer inside the GEMV CTAs, K splits met in scratch):
     # same codes and scales as the stand-alone quantizer, partial row tiles, a K that is not a multiple of the stage
     import torch
     rng = np.random.default_rng(tokens * 31 + n)
