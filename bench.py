@@ -241,6 +241,40 @@ def config_decode(args):
     print(json.dumps(out), flush=True)
 
 
+def config_fp8_gemm(args):
+    """FP8 W8A8 prefill GEMM (per-token x per-channel scales in the epilogue) at a few shapes, one GPU."""
+    import torch
+    from eider_b200 import ops
+    peaks = load_peaks()
+    cases = []
+    for (m, k, n) in [(512, 5120, 7168), (512, 5120, 27648), (2048, 5120, 7168), (4096, 5120, 27648)]:
+        ws = [torch.randint(0, 120, (n, k), dtype=torch.uint8, device="cuda") for _ in range(3)]
+        wsc = torch.rand(n, device="cuda") * 0.01
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        xq, xs = ops.quantize_fp8_dynamic(x)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        plan = ops.Fp8TnMatmulPlan(m, n, k)
+        if args.block_n:
+            plan.set_block_n(args.block_n)
+        for i in range(args.warmup):
+            plan.run(xq, ws[i % 3], xs, wsc, out=y)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            plan.run(xq, ws[i % 3], xs, wsc, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        tf = 2.0 * m * n * k / us / 1e6
+        assert plan.status() == 0
+        cases.append({"M": m, "K": k, "N": n, "tile_code": plan.block_n, "us": us, "tflops": tf,
+                      "frac_of_2x_bf16_peak": tf / (2.0 * peaks["bf16_tflops"])})
+    print(json.dumps({"metric": "fp8_gemm_tflops", "unit": "TFLOP/s", "n_gpus": 1, "data": "synthetic",
+                      "peak": 2.0 * peaks["bf16_tflops"], "peak_source": f"2 x {peaks['source']} dense bf16 burst",
+                      "timing": f"CUDA events over {args.steps} launches, 3 rotating weight copies", "cases": cases}))
+
+
 def config_moe(args):
     """Routed-MoE prefill: 4096 tokens, 128 experts, top-8, hidden 2048, intermediate 768, one GPU."""
     import torch
@@ -295,14 +329,16 @@ def main():
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: how the column blocks become [M, N] on every rank: GEMM epilogue stores into every "
                          "rank's output (symmetric memory) or NCCL all-gather + re-assembly; auto = fused on 2, 4 and 8 ranks")
-    ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe"],
-                    help="prefill (default, the contract line), or the single-GPU decode / MoE configs")
+    ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe", "fp8"],
+                    help="prefill (default, the contract line), or the single-GPU decode / MoE / FP8 GEMM configs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl != "reference" and args.config == "decode":
         return config_decode(args)
     if args.impl != "reference" and args.config == "moe":
         return config_moe(args)
+    if args.impl != "reference" and args.config == "fp8":
+        return config_fp8_gemm(args)
 
     if args.impl == "reference":
         reference_arm(args)
