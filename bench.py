@@ -331,8 +331,14 @@ def main():
                          "rank's output (symmetric memory) or NCCL all-gather + re-assembly; auto = fused on 2, 4 and 8 ranks")
     ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe", "fp8"],
                     help="prefill (default, the contract line), or the single-GPU decode / MoE / FP8 GEMM configs")
+    ap.add_argument("--tokens", type=int, default=0, help="prefill only: M instead of 512 (the larger-chunk configs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.tokens:
+        global M, WORKLOAD, FLOPS_PER_STEP
+        M = args.tokens
+        WORKLOAD = f"nvfp4_w4a4_prefill_gemm_M{M}_K{K}_N{N}"
+        FLOPS_PER_STEP = 2.0 * M * N * K
     if args.impl != "reference" and args.config == "decode":
         return config_decode(args)
     if args.impl != "reference" and args.config == "moe":
