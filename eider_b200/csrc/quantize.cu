@@ -471,6 +471,67 @@ __global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const floa
     }
 }
 
+// Post-norm residual add + quantizing pre-norm in one kernel (crates/eider-cuda/native/non_gemm.cu:746-870): one CTA per
+// row; h = input * inverse_rms0 * input_weight + residual is written to `output`, kept in shared memory and squared for
+// the second norm, then the RMSNorm quantizer runs on the staged row.  Sums run in the same fixed order as above.
+__global__ void __launch_bounds__(256) rms_norm_add_rms_norm_quantize_nvfp4_kernel(
+    const float* __restrict__ input, const float* __restrict__ input_weight, const float* __restrict__ residual,
+    float* __restrict__ output, const float* __restrict__ quant_weight, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+    uint32_t cols, float input_eps, float quant_eps, float input_scale) {
+    extern __shared__ __align__(16) float staged[];
+    __shared__ float red[8];
+    const uint32_t row = blockIdx.x;
+    const size_t off = static_cast<size_t>(row) * cols;
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float total = 0.0f;
+        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
+        __syncthreads();
+        return total;
+    };
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(input + off) + i);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    const float inv0 = rsqrtf(__fdiv_rn(block_sum(ss), static_cast<float>(cols)) + input_eps);
+    float ss2 = 0.0f;
+    for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(input + off) + i);
+        const float4 w = __ldg(reinterpret_cast<const float4*>(input_weight) + i);
+        const float4 r = __ldg(reinterpret_cast<const float4*>(residual + off) + i);
+        float4 h;
+        h.x = fmaf(__fmul_rn(v.x, inv0), w.x, r.x);
+        h.y = fmaf(__fmul_rn(v.y, inv0), w.y, r.y);
+        h.z = fmaf(__fmul_rn(v.z, inv0), w.z, r.z);
+        h.w = fmaf(__fmul_rn(v.w, inv0), w.w, r.w);
+        reinterpret_cast<float4*>(output + off)[i] = h;
+        reinterpret_cast<float4*>(staged)[i] = h;
+        ss2 = fmaf(h.x, h.x, ss2); ss2 = fmaf(h.y, h.y, ss2); ss2 = fmaf(h.z, h.z, ss2); ss2 = fmaf(h.w, h.w, ss2);
+    }
+    const float inv1 = rsqrtf(__fdiv_rn(block_sum(ss2), static_cast<float>(cols)) + quant_eps);  // (block_sum's barriers order the staging)
+    const Divisor di = make_divisor(input_scale);
+    for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+        float v[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 h4 = reinterpret_cast<const float4*>(staged + b * 16)[q];
+            const float4 w4 = __ldg(reinterpret_cast<const float4*>(quant_weight + b * 16) + q);
+            v[4 * q + 0] = div_rn(__fmul_rn(__fmul_rn(h4.x, inv1), w4.x), di);
+            v[4 * q + 1] = div_rn(__fmul_rn(__fmul_rn(h4.y, inv1), w4.y), di);
+            v[4 * q + 2] = div_rn(__fmul_rn(__fmul_rn(h4.z, inv1), w4.z), di);
+            v[4 * q + 3] = div_rn(__fmul_rn(__fmul_rn(h4.w, inv1), w4.w), di);
+        }
+        uint2 bytes;
+        const uint8_t sc = quantize_block16(v, 16, &bytes);
+        *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (cols / 2) + b * 8) = bytes;
+        scales[tiled_scale_offset(row, b, cols)] = sc;
+    }
+}
+
 // Per-token dynamic FP8: s = amax / 448 (1 when 0), q = e4m3(x / s)
 // (crates/eider-cuda/native/non_gemm.cu:9952-9974, 10028-10066).
 template <typename T, bool DYNAMIC>
@@ -617,6 +678,23 @@ cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(const float* i
         (reinterpret_cast<uintptr_t>(packed) & 7) != 0)
         return cudaErrorInvalidValue;
     rms_norm_quantize_nvfp4_kernel<<<rows, 256, 0, stream>>>(input, weight, packed, scales, cols, eps, input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream(const float* input, const float* input_weight,
+                                                                          const float* residual, float* output,
+                                                                          const float* quant_weight, uint8_t* packed,
+                                                                          uint8_t* scales, uint32_t rows, uint32_t cols,
+                                                                          float input_eps, float quant_eps, float input_scale,
+                                                                          cudaStream_t stream) {
+    if (!input || !input_weight || !residual || !output || !quant_weight || !packed || !scales || rows == 0 || cols == 0 ||
+        cols % 16 != 0 || cols > 48 * 1024 / 4 || !(input_eps >= 0.0f) || !isfinite(input_eps) || !(quant_eps >= 0.0f) ||
+        !isfinite(quant_eps) || bad_scale(input_scale) || (reinterpret_cast<uintptr_t>(packed) & 7) != 0 ||
+        ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(input_weight) | reinterpret_cast<uintptr_t>(residual) |
+          reinterpret_cast<uintptr_t>(output) | reinterpret_cast<uintptr_t>(quant_weight)) & 15) != 0)
+        return cudaErrorInvalidValue;
+    rms_norm_add_rms_norm_quantize_nvfp4_kernel<<<rows, 256, cols * sizeof(float), stream>>>(
+        input, input_weight, residual, output, quant_weight, packed, scales, cols, input_eps, quant_eps, input_scale);
     return cudaGetLastError();
 }
 

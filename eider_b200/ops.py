@@ -490,6 +490,25 @@ def rms_norm_quantize_nvfp4(x: torch.Tensor, weight: torch.Tensor, eps: float = 
     return out
 
 
+def rms_norm_add_then_rms_norm_quantize_nvfp4(x: torch.Tensor, input_weight: torch.Tensor, residual: torch.Tensor,
+                                              quant_weight: torch.Tensor, input_eps: float = 1e-6, quant_eps: float = 1e-6,
+                                              input_scale: float = 1.0):
+    """h = rmsnorm(x; input_weight) + residual (returned, f32) and NVFP4 of rmsnorm(h; quant_weight) / input_scale
+    (the reference's infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream)."""
+    for t, name in ((x, "input"), (input_weight, "input_weight"), (residual, "residual"), (quant_weight, "quant_weight")):
+        _need(t, torch.float32, name)
+    rows, cols = x.shape
+    if residual.shape != x.shape or input_weight.numel() != cols or quant_weight.numel() != cols:
+        raise ShapeError("operand shapes do not match")
+    h = torch.empty_like(x)
+    out = Nvfp4Matrix.zeros(rows, cols, x.device)
+    check("infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream",
+          _lib.load().infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream(
+              x.data_ptr(), input_weight.data_ptr(), residual.data_ptr(), h.data_ptr(), quant_weight.data_ptr(),
+              out.packed.data_ptr(), out.scales.data_ptr(), rows, cols, input_eps, quant_eps, input_scale, _stream()))
+    return h, out
+
+
 def silu_mul_halves_quantize_nvfp4(gate_up: torch.Tensor, input_scale: float = 1.0) -> "Nvfp4Matrix":
     """Fused SiLU(gate) * up -> NVFP4 of [tokens, 2K] f32 rows (gate half first): the activation of the down projection
     without the fp32 round trip (the reference's infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream)."""

@@ -78,6 +78,15 @@ EIDER_B200_API cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream
                                                                                  uint32_t cols, float eps, float input_scale,
                                                                                  cudaStream_t stream);
 
+/* Fused producer: post-norm residual add, then the quantizing pre-norm of the next block
+ * (crates/eider-cuda/native/non_gemm.cu:746-870).  output = input * rsqrt(mean(input^2) + input_eps) * input_weight +
+ * residual (f32, [rows][cols]); packed / scales = NVFP4 of output * rsqrt(mean(output^2) + quant_eps) * quant_weight /
+ * input_scale.  This implementation needs cols % 16 == 0, cols <= 12288 and 16-byte aligned f32 operands. */
+EIDER_B200_API cudaError_t infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream(
+    const float* input, const float* input_weight, const float* residual, float* output, const float* quant_weight,
+    uint8_t* packed, uint8_t* scales, uint32_t rows, uint32_t cols, float input_eps, float quant_eps, float input_scale,
+    cudaStream_t stream);
+
 /* Fused producer SiLU(gate) * up -> NVFP4 (crates/eider-cuda/src/ffi.rs:2441;
  * crates/eider-cuda/native/non_gemm.cu:559-629): gate_up holds `rows` gate values followed by `rows` up values of one
  * token; packed [rows/2], scales tiled with outer = 0.  This implementation needs rows % 16 == 0 and a 16-byte aligned

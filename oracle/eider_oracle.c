@@ -660,6 +660,25 @@ ORACLE_API void oracle_rms_norm_quantize_nvfp4(const float* input, const float* 
     free(row);
 }
 
+/* Post-norm residual add followed by the quantizing pre-norm of the next block:
+ * crates/eider-cuda/native/non_gemm.cu:746-870.  h = input * rsqrt(mean(input^2) + input_eps) * input_weight + residual
+ * (the last multiply and the add contract to one FMA in the reference's build), written to `output`; then the RMSNorm
+ * quantizer above on h with quant_weight / quant_eps / input_scale.  Sums of squares in double (see above). */
+ORACLE_API void oracle_rms_norm_add_then_rms_norm_quantize_nvfp4(const float* input, const float* input_weight, const float* residual,
+                                                                 float* output, const float* quant_weight, size_t rows, size_t cols,
+                                                                 float input_eps, float quant_eps, float input_scale,
+                                                                 uint8_t* packed, uint8_t* scales, float* norm_out) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float* x = input + r * cols;
+        double ss = 0.0;
+        for (size_t i = 0; i < cols; ++i) ss += (double)x[i] * (double)x[i];
+        float inv = 1.0f / sqrtf((float)ss / (float)cols + input_eps);
+        for (size_t i = 0; i < cols; ++i) output[r * cols + i] = fmaf(x[i] * inv, input_weight[i], residual[r * cols + i]);
+    }
+    /* the quantizing norm tiles its scales with outer = row, exactly like the stand-alone producer */
+    oracle_rms_norm_quantize_nvfp4(output, quant_weight, rows, cols, quant_eps, input_scale, packed, scales, norm_out);
+}
+
 /* Grouped W4A4 GEMM: per expert D_e[row][m] = alpha_e * sum_k X_e[row][k] * W_e[m][k], rounded to
  * bf16 (crates/eider-cuda/native/cutlass_grouped_gemm.cu:116-164; output [route][m],
  * non_gemm.cu:3080-3083).  Activations dequantised from the per-expert tiled scales. */

@@ -201,3 +201,25 @@ def test_fused_rms_norm_quantize_matches_oracle(ops, oracle, rows, cols, scale):
     assert np.all(np.abs(deq - norm) <= 0.27 * bmax + 1e-12)
     from eider_b200 import _lib
     assert _lib.load().infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(None, None, None, None, rows, cols, 1e-6, scale, None) == 1
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 5120), (9, 2048), (200, 256)])
+def test_fused_add_then_norm_quantize_matches_oracle(ops, oracle, rows, cols):
+    # non_gemm.cu:746-870: h = rmsnorm(x) * w0 + residual (stored), then the quantizing RMSNorm of h
+    import torch
+    rng = np.random.default_rng(rows * 3 + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    res = rng.standard_normal((rows, cols)).astype(np.float32)
+    w0 = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    w1 = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    h, q = ops.rms_norm_add_then_rms_norm_quantize_nvfp4(dev(x), dev(w0), dev(res), dev(w1), 1e-6, 1e-5, 0.5)
+    torch.cuda.synchronize()
+    h_ref, p_ref, s_ref, norm = oracle.rms_norm_add_then_rms_norm_quantize_nvfp4(x, w0, res, w1, 1e-6, 1e-5, 0.5)
+    assert np.allclose(h.cpu().numpy(), h_ref, rtol=2e-6, atol=2e-6)
+    got_p, got_s = q.packed.cpu().numpy(), q.scales.cpu().numpy()
+    assert np.count_nonzero(got_p != p_ref) / got_p.size < 5e-3
+    assert np.count_nonzero(got_s != s_ref) / got_s.size < 5e-3
+    deq = oracle.dequantize_tiled(got_p, got_s)
+    bmax = np.abs(norm).reshape(rows, -1, 16).max(axis=2).repeat(16, axis=1)
+    assert np.all(np.abs(deq - norm) <= 0.27 * bmax + 1e-12)
