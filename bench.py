@@ -397,7 +397,7 @@ def main():
 
     sharded = parallel.ColumnShardedLinear(N, local_linear)
     gather = "none" if world == 1 else "nccl"
-    FUSED_MEASURED_ON = (2, 4, 8)  # verified on 2 and 8 ranks of one box
+    FUSED_MEASURED_ON = (2, 4, 8)  # verified on 2, 4 and 8 ranks of one box
     if world > 1 and (args.gather == "fused" or (args.gather == "auto" and world in FUSED_MEASURED_ON)):
         try:
             plan_b = ops.Fp4TnMatmulPlan(M, n_local, K)  # second output buffer: one barrier per step is enough
