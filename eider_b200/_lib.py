@@ -25,6 +25,7 @@ SIGNATURES = {
     "eider_b200_nvfp4_scales_to_tiled_on_stream": (_I, [_P, _P, _U32, _U32, _P]),
     "eider_b200_nvfp4_scale_layout_len": (_SZ, [_SZ, _SZ]),
     "infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _F, _P]),
+    "infer_rms_norm_quantize_nvfp4_pair_col_major_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _F, _F, _P]),
     "infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _F, _F, _F, _P]),
     "infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _U32, _F, _P]),
     "eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _P]),

@@ -426,9 +426,14 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_nvfp4_kernel(const floa
 // squares (per-thread strided partial sums, warp shuffles, then the warp sums in warp order: a fixed order for a given
 // launch shape), pass two gives every thread 16-element blocks: value = x * inverse_rms * weight / input_scale in that
 // order, then the block quantizer.  The row is read twice; the second read hits L1/L2.
+// PAIR (non_gemm.cu:290-419): a second NVFP4 term holds what the first left, residual = value - e2m1(code) * scale (one
+// FMA), quantized per block with its own scale byte.
+template <bool PAIR>
 __global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const float* __restrict__ input, const float* __restrict__ weight,
                                                                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                                      uint32_t cols, float eps, float input_scale) {
+                                                                      uint8_t* __restrict__ residual_packed,
+                                                                      uint8_t* __restrict__ residual_scales, uint32_t cols, float eps,
+                                                                      float input_scale) {
     __shared__ float red[8];
     __shared__ float inverse_rms;
     const uint32_t row = blockIdx.x;
@@ -468,6 +473,15 @@ __global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const floa
         const uint8_t sc = quantize_block16(v, 16, &bytes);
         *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (cols / 2) + b * 8) = bytes;
         scales[tiled_scale_offset(row, b, cols)] = sc;
+        if (PAIR) {
+            const float sv = e4m3_value(sc);
+            const uint32_t w[2] = {bytes.x, bytes.y};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = fmaf(-e2m1_value((w[i / 8] >> ((i % 8) * 4)) & 0xfu), sv, v[i]);
+            const uint8_t rsc = quantize_block16(v, 16, &bytes);
+            *reinterpret_cast<uint2*>(residual_packed + static_cast<size_t>(row) * (cols / 2) + b * 8) = bytes;
+            residual_scales[tiled_scale_offset(row, b, cols)] = rsc;
+        }
     }
 }
 
@@ -677,7 +691,21 @@ cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(const float* i
         ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(weight)) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(packed) & 7) != 0)
         return cudaErrorInvalidValue;
-    rms_norm_quantize_nvfp4_kernel<<<rows, 256, 0, stream>>>(input, weight, packed, scales, cols, eps, input_scale);
+    rms_norm_quantize_nvfp4_kernel<false><<<rows, 256, 0, stream>>>(input, weight, packed, scales, nullptr, nullptr, cols, eps, input_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_rms_norm_quantize_nvfp4_pair_col_major_f32_on_stream(const float* input, const float* weight, uint8_t* packed,
+                                                                       uint8_t* scales, uint8_t* residual_packed,
+                                                                       uint8_t* residual_scales, uint32_t rows, uint32_t cols,
+                                                                       float eps, float input_scale, cudaStream_t stream) {
+    if (!input || !weight || !packed || !scales || !residual_packed || !residual_scales || rows == 0 || cols == 0 ||
+        cols % 16 != 0 || bad_scale(input_scale) ||
+        ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(weight)) & 15) != 0 ||
+        ((reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(residual_packed)) & 7) != 0)
+        return cudaErrorInvalidValue;
+    rms_norm_quantize_nvfp4_kernel<true><<<rows, 256, 0, stream>>>(input, weight, packed, scales, residual_packed, residual_scales,
+                                                                   cols, eps, input_scale);
     return cudaGetLastError();
 }
 

@@ -78,6 +78,12 @@ EIDER_B200_API cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream
                                                                                  uint32_t cols, float eps, float input_scale,
                                                                                  cudaStream_t stream);
 
+/* The same with a second, residual NVFP4 term (crates/eider-cuda/native/non_gemm.cu:290-419): residual_packed /
+ * residual_scales quantize value - dequantized first term, block by block. */
+EIDER_B200_API cudaError_t infer_rms_norm_quantize_nvfp4_pair_col_major_f32_on_stream(
+    const float* input, const float* weight, uint8_t* packed, uint8_t* scales, uint8_t* residual_packed, uint8_t* residual_scales,
+    uint32_t rows, uint32_t cols, float eps, float input_scale, cudaStream_t stream);
+
 /* Fused producer: post-norm residual add, then the quantizing pre-norm of the next block
  * (crates/eider-cuda/native/non_gemm.cu:746-870).  output = input * rsqrt(mean(input^2) + input_eps) * input_weight +
  * residual (f32, [rows][cols]); packed / scales = NVFP4 of output * rsqrt(mean(output^2) + quant_eps) * quant_weight /

@@ -660,6 +660,41 @@ ORACLE_API void oracle_rms_norm_quantize_nvfp4(const float* input, const float* 
     free(row);
 }
 
+/* RMSNorm -> NVFP4 with a second, residual NVFP4 term: crates/eider-cuda/native/non_gemm.cu:290-419.  The primary term
+ * is oracle_rms_norm_quantize_nvfp4; residual_i = value_i - e2m1(code_i) * scale (one FMA in the reference's build) is
+ * quantized per block with its own scale byte (block maximum over |residual|, no finiteness test). */
+ORACLE_API void oracle_rms_norm_quantize_nvfp4_pair(const float* input, const float* weight, size_t rows, size_t cols, float eps,
+                                                    float input_scale, uint8_t* packed, uint8_t* scales,
+                                                    uint8_t* residual_packed, uint8_t* residual_scales) {
+    size_t blocks = (cols + 15) / 16;
+    float* norm = (float*)malloc(rows * cols * sizeof(float));
+    oracle_rms_norm_quantize_nvfp4(input, weight, rows, cols, eps, input_scale, packed, scales, norm);
+    for (size_t r = 0; r < rows; ++r) {
+        const uint8_t* prow = packed + r * ((cols + 1) / 2);
+        uint8_t* rrow = residual_packed + r * ((cols + 1) / 2);
+        for (size_t b = 0; b < blocks; ++b) {
+            size_t start = b * 16, end = start + 16 < cols ? start + 16 : cols;
+            float sv = oracle_e4m3_value(scales[oracle_tiled_scale_offset(r, b, cols)]);
+            float res[16];
+            float amax = 0.0f;
+            for (size_t i = start; i < end; ++i) {
+                uint8_t code = (i & 1) ? (uint8_t)(prow[i / 2] >> 4) : (uint8_t)(prow[i / 2] & 0x0f);
+                res[i - start] = fmaf(-oracle_e2m1_value(code), sv, norm[r * cols + i]);
+                amax = fmaxf(amax, fabsf(res[i - start]));
+            }
+            uint8_t sc = amax == 0.0f ? 0 : oracle_ue4m3_code(amax / 6.0f);
+            float rs = oracle_e4m3_value(sc);
+            residual_scales[oracle_tiled_scale_offset(r, b, cols)] = sc;
+            for (size_t i = start; i < end; ++i) {
+                uint8_t code = oracle_e2m1_code(rs == 0.0f ? 0.0f : res[i - start] / rs);
+                if ((i & 1) == 0) rrow[i / 2] = code;
+                else rrow[i / 2] |= (uint8_t)(code << 4);
+            }
+        }
+    }
+    free(norm);
+}
+
 /* Post-norm residual add followed by the quantizing pre-norm of the next block:
  * crates/eider-cuda/native/non_gemm.cu:746-870.  h = input * rsqrt(mean(input^2) + input_eps) * input_weight + residual
  * (the last multiply and the add contract to one FMA in the reference's build), written to `output`; then the RMSNorm

@@ -88,6 +88,7 @@ _silu_dense = _sig("oracle_silu_mul_halves_quantize_nvfp4", None, _f32p, _sz, _s
 _rms_q = _sig("oracle_rms_norm_quantize_nvfp4", None, _f32p, _f32p, _sz, _sz, C.c_float, C.c_float, _u8p, _u8p, C.c_void_p)
 _rms_add_q = _sig("oracle_rms_norm_add_then_rms_norm_quantize_nvfp4", None, _f32p, _f32p, _f32p, _f32p, _f32p, _sz, _sz,
                   C.c_float, C.c_float, C.c_float, _u8p, _u8p, C.c_void_p)
+_rms_pair = _sig("oracle_rms_norm_quantize_nvfp4_pair", None, _f32p, _f32p, _sz, _sz, C.c_float, C.c_float, _u8p, _u8p, _u8p, _u8p)
 _grouped = _sig("oracle_moe_grouped_gemm", None, _u8p, _u8p, _u32p, _sz, _sz, _u8p, _u8p, _f32p, _sz,
                 _sz, _u16p)
 _combine = _sig("oracle_moe_combine", None, _u32p, _f32p, _u16p, _sz, _sz, _sz, _f32p)
@@ -375,6 +376,18 @@ def rms_norm_quantize_nvfp4(x, weight, eps=1e-6, input_scale=1.0, want_norm=Fals
     _rms_q(np.ascontiguousarray(x), _f32(weight), rows, cols, float(eps), float(input_scale), packed, scales,
            norm.ctypes.data if norm is not None else None)
     return (packed, scales, norm) if want_norm else (packed, scales)
+
+
+def rms_norm_quantize_nvfp4_pair(x, weight, eps=1e-6, input_scale=1.0):
+    """non_gemm.cu:290-419 -> (packed, scales, residual_packed, residual_scales)."""
+    x = _f32(x)
+    rows, cols = x.shape
+    packed = np.zeros((rows, cols // 2), np.uint8)
+    rpacked = np.zeros((rows, cols // 2), np.uint8)
+    scales = np.zeros(scale_layout_len(rows, cols), np.uint8)
+    rscales = np.zeros(scale_layout_len(rows, cols), np.uint8)
+    _rms_pair(np.ascontiguousarray(x), _f32(weight), rows, cols, float(eps), float(input_scale), packed, scales, rpacked, rscales)
+    return packed, scales, rpacked, rscales
 
 
 def rms_norm_add_then_rms_norm_quantize_nvfp4(x, input_weight, residual, quant_weight, input_eps=1e-6, quant_eps=1e-6,

@@ -223,3 +223,34 @@ def test_fused_add_then_norm_quantize_matches_oracle(ops, oracle, rows, cols):
     deq = oracle.dequantize_tiled(got_p, got_s)
     bmax = np.abs(norm).reshape(rows, -1, 16).max(axis=2).repeat(16, axis=1)
     assert np.all(np.abs(deq - norm) <= 0.27 * bmax + 1e-12)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 5120), (33, 1024)])
+def test_fused_rms_norm_quantize_pair_matches_oracle(ops, oracle, rows, cols):
+    # non_gemm.cu:290-419: the second term quantizes what the first left, block by block
+    import torch
+    from eider_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(rows + cols + 1)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    n_sf = oracle.scale_layout_len(rows, cols)
+    p = torch.zeros(rows, cols // 2, dtype=torch.uint8, device="cuda")
+    rp = torch.zeros_like(p)
+    s_ = torch.zeros(n_sf, dtype=torch.uint8, device="cuda")
+    rs = torch.zeros_like(s_)
+    assert lib.infer_rms_norm_quantize_nvfp4_pair_col_major_f32_on_stream(xd.data_ptr(), wd.data_ptr(), p.data_ptr(), s_.data_ptr(),
+                                                                          rp.data_ptr(), rs.data_ptr(), rows, cols, 1e-6, 1.0, None) == 0
+    torch.cuda.synchronize()
+    p0, s0, rp0, rs0 = oracle.rms_norm_quantize_nvfp4_pair(x, w, 1e-6, 1.0)
+    _, _, norm = oracle.rms_norm_quantize_nvfp4(x, w, 1e-6, 1.0, want_norm=True)
+    got = [t.cpu().numpy() for t in (p, s_, rp, rs)]
+    for a, b in zip(got, (p0, s0, rp0, rs0)):
+        assert np.count_nonzero(a != b) / a.size < 1e-2
+    # the first term alone equals the single-term producer bit for bit
+    q1 = ops.rms_norm_quantize_nvfp4(xd, wd, 1e-6, 1.0)
+    assert torch.equal(q1.packed, p) and torch.equal(q1.scales, s_)
+    two = oracle.dequantize_tiled(got[0], got[1]) + oracle.dequantize_tiled(got[2], got[3])
+    bmax = np.abs(norm).reshape(rows, -1, 16).max(axis=2).repeat(16, axis=1)
+    assert np.all(np.abs(two - norm) <= 0.08 * bmax + 1e-12)
