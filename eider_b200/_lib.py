@@ -29,6 +29,30 @@ SIGNATURES = {
     "infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _F, _F, _F, _P]),
     "infer_silu_mul_halves_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _U32, _F, _P]),
     "eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_rms_norm_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_rms_norm_add_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_gated_rms_norm_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_silu_mul_halves_f32_on_stream": (_I, [_P, _P, _U32, _P]),
+    "infer_silu_mul_halves_f32_batch_on_stream": (_I, [_P, _P, _U32, _U32, _P]),
+    "infer_gelu_tanh_mul_f32_on_stream": (_I, [_P, _P, _P, _U32, _P]),
+    "infer_unpack_heads_f32_on_stream": (_I, [_P, _P, _U32, _U32, _U32, _U32, _P]),
+    "infer_gelu_tanh_mul_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_unpack_heads_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _U32, _F, _P]),
+    "infer_unpack_heads_quantize_nvfp4_col_major_bf16_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _U32, _F, _P]),
+    "infer_gated_rms_norm_quantize_nvfp4_col_major_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _F, _F, _P]),
+    "infer_quantize_nvfp4_vector_simple_scales_f32_on_stream": (_I, [_P, _P, _P, _U32, _F, _P]),
+    "infer_scale_channel_f32_device_scalar_on_stream": (_I, [_P, _P, _P, _U32, _P]),
+    "infer_scale_channel_f32_device_row_scalar_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),
+    "infer_cutlass_fp4_gemv_f32_supported": (_I, [_U32, _U32]),
+    "infer_cutlass_fp4_gemv_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _F, _P]),
+    "infer_fp8_linear_channel_scaled_dynamic_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_fp8_linear_w8a8_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _F, _P]),
+    "infer_moe_sort_routes_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_moe_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _I, _P]),
+    "infer_moe_calibrated_quantize_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _I, _P]),
+    "infer_moe_gelu_tanh_mul_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_moe_gather_rms_norm_quantize_sorted_routes_nvfp4_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _F, _P]),
     "infer_quantize_fp8_e4m3_dynamic_f32_on_stream": (_I, [_P, _P, _P, _U32, _P]),
     "infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),
     "eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),

@@ -36,15 +36,6 @@ __host__ __device__ inline uint32_t ring_depth(uint32_t per) {
 }
 constexpr uint32_t kTmemCols = 64;       // 2 x 16 accumulator columns + 16 + 16 scale columns
 
-#ifdef EIDER_GEMM_TRACE
-// bring-up instrumentation: [cta][0] entry, [1] after setup sync, [2] expansion done, [3] first weight stage landed,
-// [4] last MMA committed, [5] epilogue done, [6] producer done
-__device__ long long g_dtrace[512][8];
-#define DTRACE(slot) g_dtrace[blockIdx.x & 511][slot] = clock64()
-#else
-#define DTRACE(slot) ((void)0)
-#endif
-
 struct Params {
     const void* x;            // [tokens][k] bf16 or f32
     uint32_t tokens, n, k;
@@ -114,7 +105,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
     float* red = reinterpret_cast<float*>(tmem_slot + 4);   // [32]
     float* col_scale = red + 32;                              // [kCols]
 
-    if (threadIdx.x == 0) DTRACE(0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t split = blockIdx.x % p.splits;
     const uint32_t group = blockIdx.x / p.splits, groups = gridDim.x / p.splits;
@@ -172,7 +162,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) {
-        DTRACE(1);
         umma::griddep_launch_dependents();  // the next kernel in the stream may start its own setup and weight requests
     }
 
@@ -192,7 +181,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
                 __syncwarp();
             }
         }
-        if (leader) DTRACE(6);
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         const bool leader = umma::elect_one();
@@ -215,7 +203,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
                 const uint32_t slot = it % kRing, phase = (it / kRing) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[slot], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
                 umma::tc_fence_after();
-                if (leader && it == 0) DTRACE(3);
                 if (leader) {
                     const uint32_t ls = s - stage0;
                     const uint32_t w_lo = w_lo0 + slot * (kWeightTile >> 4), a_lo = a_lo0 + ls * (kActTile >> 4);
@@ -249,7 +236,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
             if (ok && leader) umma::tc_commit(&acc_full[acc]);
             __syncwarp();
         }
-        if (leader) DTRACE(4);
     } else {
         // ---------------------------------------------------------------- activation expansion, then epilogue
         const uint32_t te = threadIdx.x - 64;  // 0 .. expand_threads - 1; the first 128 go on to be the epilogue
@@ -321,7 +307,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
         umma::fence_proxy_async();
         asm volatile("bar.sync 1, %0;" ::"r"(p.expand_threads) : "memory");
         if (te == 0) umma::mbar_arrive(act_ready);
-        if (te == 0) DTRACE(2);
         if (te >= 128) goto teardown;  // the extra expansion warps are done
 
         uint32_t tile = 0;
@@ -401,7 +386,6 @@ __global__ void __launch_bounds__(64 + kMaxExpandThreads, 1) nvfp4_decode_fused_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
         }
-        if (threadIdx.x == 64) DTRACE(5);
     }
 teardown:
     umma::tc_fence_before();

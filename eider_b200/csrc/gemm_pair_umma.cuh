@@ -105,8 +105,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
     umma::cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const long long tr_start = TRACE_NOW();
-    (void)tr_start;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -116,8 +114,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         PairTile t;
         bool ok = true;
         bool dep_waited = false;
-        const long long tr_p0 = TRACE_NOW();
-        (void)tr_p0;
         for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
             const bool row_sf = kNv && t.row_tile < p.row_tiles;
             const uint32_t sf_col_tile0 = t.col0 / kTileRows;
@@ -125,11 +121,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
-                const long long tr_w = TRACE_NOW();
-                (void)tr_w;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
                 if (!leader) continue;
-                TRACE_ADD(5, TRACE_NOW() - tr_w);
                 const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
                 uint32_t bytes = L::kA + L::kB;
                 if (kNv) bytes += kb * kScaleTileBytes * ((row_sf ? 1 : 0) + 1 + (second_sf ? 1 : 0));
@@ -157,7 +150,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                                        kb * kScaleTileBytes, &full[stage]);
             }
         }
-        if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
     } else if (warp == 1 && rank != 0) {
         // ------------------------------------------------------------------ odd CTA: forward stage arrivals
         const bool leader = umma::elect_one();
@@ -169,10 +161,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
-                const long long tr_f = TRACE_NOW();
-                (void)tr_f;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
-                if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
                 if (leader) umma::mbar_arrive_cluster(full0_remote + stage * 8);
                 __syncwarp();
             }
@@ -193,24 +182,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         uint32_t it = 0, tile_count = 0;
         PairTile t;
         bool ok = true;
-        const long long tr_m0 = TRACE_NOW();
-        (void)tr_m0;
         for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
-            const long long tr_a = TRACE_NOW();
-            (void)tr_a;
             if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
-            if (leader) { TRACE_ADD(2, TRACE_NOW() - tr_a); TRACE_ADD(7, 1); }
             umma::tc_fence_after();
             const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
             for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
-                const long long tr_f = TRACE_NOW();
-                (void)tr_f;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
-                if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
                 umma::tc_fence_after();
                 if (leader) {
                     const uint32_t a_lo = a_lo0 + stage * (L::kA >> 4);
@@ -261,7 +242,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             }
             __syncwarp();
         }
-        if (leader) TRACE_ADD(0, TRACE_NOW() - tr_m0);
     } else {
         // ------------------------------------------------------------------ epilogue warps (both CTAs)
         const uint32_t quad = warp & 3;
@@ -274,10 +254,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
-            const long long tr_w = TRACE_NOW();
-            (void)tr_w;
             if (!umma::mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
-            if (threadIdx.x == 64) TRACE_ADD(4, TRACE_NOW() - tr_w);
             umma::tc_fence_after();
             const uint32_t row = t.row0 + quad * 32 + lane;
             const bool row_ok = row < p.rows;
@@ -364,7 +341,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         __syncwarp();
     }
 
-    if (threadIdx.x == 64) TRACE_ADD(3, TRACE_NOW() - tr_start);
     // ---------------------------------------------------------------------- teardown
     // Neither CTA may leave (or free tensor memory) while the other can still reach its shared or tensor memory.
     umma::tc_fence_before();

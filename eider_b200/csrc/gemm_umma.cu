@@ -8,9 +8,11 @@
 #include "gemm_pair_umma.cuh"
 #include "gemv_stream.cuh"
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "eider_b200.h"
 
@@ -52,15 +54,73 @@ cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-int sm_count() {
-    static int count = 0;
-    if (count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
-        if (count <= 0) count = 148;
+// Tensor maps a plan has already encoded, keyed by what went into them: encoding costs a driver call of a microsecond or
+// two, which is a visible part of a 9 us decode launch.  A plan is driven by one host thread (the reference's contract),
+// so the cache is not locked.
+struct MapCache {
+    static constexpr int kEntries = 8;
+    struct Entry {
+        const void* base;
+        uint64_t rows, row_bytes, pitch;
+        uint32_t box_rows;
+        CUtensorMap map;
+    };
+    Entry entries[kEntries];
+    uint32_t next;
+
+    cudaError_t get(const CUtensorMap** out, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch, uint32_t box_rows) {
+        for (int i = 0; i < kEntries; ++i) {
+            Entry& e = entries[i];
+            if (e.base == base && e.rows == rows && e.row_bytes == row_bytes && e.pitch == pitch && e.box_rows == box_rows) {
+                *out = &e.map;
+                return cudaSuccess;
+            }
+        }
+        Entry& e = entries[next % kEntries];
+        e.base = nullptr;
+        cudaError_t st = make_map(&e.map, base, rows, row_bytes, pitch, box_rows);
+        if (st != cudaSuccess) return st;
+        e.base = base;
+        e.rows = rows;
+        e.row_bytes = row_bytes;
+        e.pitch = pitch;
+        e.box_rows = box_rows;
+        ++next;
+        *out = &e.map;
+        return cudaSuccess;
     }
-    return count;
+};
+
+// Per-device caches: one host process may drive several GPUs, and the shared-memory opt-in, the SM count and the
+// cluster occupancy all belong to the device that is current at the call.
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
+}
+
+int sm_count() {
+    static std::atomic<int> count[kMaxDevices];
+    const int dev = current_device();
+    int c = count[dev].load(std::memory_order_relaxed);
+    if (c == 0) {
+        cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev);
+        if (c <= 0) c = 148;
+        count[dev].store(c, std::memory_order_relaxed);
+    }
+    return c;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute: opt in once on every device that launches.
+template <typename Kernel>
+cudaError_t opt_in_smem(std::atomic<uint8_t> (&done)[kMaxDevices], Kernel kernel, uint32_t bytes) {
+    const int dev = current_device();
+    if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (st == cudaSuccess) done[dev].store(1, std::memory_order_release);
+    return st;
 }
 
 template <int KIND, int BLOCK_N, bool TRANSPOSED, int TERMS, bool GROUPED>
@@ -69,12 +129,8 @@ cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, con
     constexpr int kStages = default_stages<KIND, BLOCK_N>();
     constexpr uint32_t kSmem = smem_bytes<KIND, BLOCK_N, kStages>();
     auto kernel = gemm_kernel<KIND, BLOCK_N, kStages, TRANSPOSED, TERMS, GROUPED>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem));
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    static std::atomic<uint8_t> configured[kMaxDevices];
+    if (cudaError_t st = opt_in_smem(configured, kernel, kSmem); st != cudaSuccess) return st;
     uint32_t grid = static_cast<uint32_t>(sm_count());
     if (work_items < grid) grid = work_items;
     if (grid == 0) return cudaSuccess;
@@ -113,7 +169,9 @@ cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols
                         cudaStream_t stream) {
     using L = PairSmem<KIND>;
     auto kernel = gemm_pair_kernel<KIND>;
-    static int max_pairs = 0;
+    static std::atomic<int> max_pairs_of[kMaxDevices];
+    const int dev = current_device();
+    int max_pairs = max_pairs_of[dev].load(std::memory_order_acquire);
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kNumThreads);
     cfg.dynamicSmemBytes = L::kBytes;
@@ -136,6 +194,7 @@ cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols
         if (st != cudaSuccess) return st;
         if (clusters <= 0) return cudaErrorLaunchOutOfResources;
         max_pairs = clusters;
+        max_pairs_of[dev].store(clusters, std::memory_order_release);
     }
     uint32_t grid_pairs = static_cast<uint32_t>(max_pairs);
     if (pair_items < grid_pairs) grid_pairs = pair_items;
@@ -159,6 +218,7 @@ struct DensePlan {
     uint32_t n_peers;
     uint32_t peer_ld;       // row pitch (elements) of those outputs
     CUtensorMap* peer_maps; // device array of n_peers bf16 tensor maps over the same column blocks (TMA-store epilogue)
+    MapCache maps_x, maps_w;
 };
 
 enum DecodePath : uint32_t { kDecodeAuto = 0, kDecodeStream = 1, kDecodeFused = 2, kDecodeSplit = 3, kDecodeFusedMany = 4 };
@@ -177,11 +237,13 @@ struct DecodePlan {
     uint8_t* act_scales;
     float* act_col_scale;
     uint32_t path;  // DecodePath: which kernel family serves one or two tokens
+    MapCache maps_x, maps_w;
 };
 
 struct GroupedPlan {
     uint32_t m, max_n, k, groups;  // reference naming: m = out features per expert, max_n = max tokens per expert
     uint32_t* status;
+    MapCache maps_a, maps_w;
 };
 
 namespace {
@@ -225,19 +287,21 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
 
 }  // namespace
 
-cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const uint8_t* w_values,
+cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const uint8_t* w_values,
                       const uint8_t* w_scales, const void* c, void* d, float alpha, float beta, const float* token_scale,
                       const float* channel_scale, int out_is_bf16, cudaStream_t stream) {
     const bool nv = plan.kind == kNvf4;
     if (!x_values || !w_values || !d || (nv && (!x_scales || !w_scales))) return cudaErrorInvalidValue;
     if (beta != 0.0f && !c) return cudaErrorInvalidValue;
     const uint32_t k_bytes = nv ? plan.k / 2 : plan.k;
-    CUtensorMap map_rows, map_cols;
-    cudaError_t st = make_map(&map_rows, x_values, plan.m, k_bytes, k_bytes, kTileRows);
+    const CUtensorMap *map_rows_p, *map_cols_p;
+    cudaError_t st = plan.maps_x.get(&map_rows_p, x_values, plan.m, k_bytes, k_bytes, kTileRows);
     if (st != cudaSuccess) return st;
     // (the CTA-pair kernel loads the weight tile in two 128-row halves)
-    st = make_map(&map_cols, w_values, plan.n, k_bytes, k_bytes, plan.block_n == kPairBlockCode ? kPairHalfN : plan.block_n);
+    st = plan.maps_w.get(&map_cols_p, w_values, plan.n, k_bytes, k_bytes, plan.block_n == kPairBlockCode ? kPairHalfN : plan.block_n);
     if (st != cudaSuccess) return st;
+    const CUtensorMap& map_rows = *map_rows_p;
+    const CUtensorMap& map_cols = *map_cols_p;
     Params p{};
     p.rows = plan.m;
     p.cols = plan.n;
@@ -292,7 +356,7 @@ cudaError_t run_dense(const DensePlan& plan, const uint8_t* x_values, const uint
 
 // Decode orientation: weights are the row operand (128 output features per tile on the tensor-memory
 // lanes), the few tokens (x terms) are the column operand.
-cudaError_t run_decode(const DecodePlan& plan, uint32_t terms, const uint8_t* x_values, const uint8_t* x_scales,
+cudaError_t run_decode(DecodePlan& plan, uint32_t terms, const uint8_t* x_values, const uint8_t* x_scales,
                        const float* x_col_scale, uint32_t tokens, const uint8_t* w_values, const uint8_t* w_scales, const float* channel_scale,
                        const void* c, void* d, float alpha, float beta, int out_is_bf16, cudaStream_t stream) {
     const bool nv = plan.kind == kNvf4;
@@ -303,11 +367,13 @@ cudaError_t run_decode(const DecodePlan& plan, uint32_t terms, const uint8_t* x_
     uint32_t block_n = 16;
     while (block_n < cols) block_n *= 2;
     if (block_n > 256) return cudaErrorInvalidValue;
-    CUtensorMap map_rows, map_cols;
-    cudaError_t st = make_map(&map_rows, w_values, plan.n, k_bytes, k_bytes, kTileRows);
+    const CUtensorMap *map_rows_p, *map_cols_p;
+    cudaError_t st = plan.maps_w.get(&map_rows_p, w_values, plan.n, k_bytes, k_bytes, kTileRows);
     if (st != cudaSuccess) return st;
-    st = make_map(&map_cols, x_values, cols, k_bytes, k_bytes, block_n);
+    st = plan.maps_x.get(&map_cols_p, x_values, cols, k_bytes, k_bytes, block_n);
     if (st != cudaSuccess) return st;
+    const CUtensorMap& map_rows = *map_rows_p;
+    const CUtensorMap& map_cols = *map_cols_p;
     Params p{};
     p.rows = plan.n;
     p.cols = cols;
@@ -373,19 +439,20 @@ cudaError_t run_decode(const DecodePlan& plan, uint32_t terms, const uint8_t* x_
 #undef EIDER_DECODE
 }
 
-cudaError_t run_grouped(const GroupedPlan& plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
+cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
                         const uint8_t* w_scales, uint16_t* output, const float* alpha, const uint32_t* expert_offsets,
                         uint32_t total_routes, cudaStream_t stream) {
     if (!a_values || !a_scales || !w_values || !w_scales || !output || !alpha || !expert_offsets || total_routes == 0)
         return cudaErrorInvalidValue;
     const uint32_t k_bytes = plan.k / 2;
-    constexpr uint32_t kBlockN = 256;
-    CUtensorMap map_rows, map_cols;
-    cudaError_t st = make_map(&map_rows, a_values, total_routes, k_bytes, k_bytes, kTileRows);
+    const CUtensorMap *map_rows_p, *map_cols_p;
+    cudaError_t st = plan.maps_a.get(&map_rows_p, a_values, total_routes, k_bytes, k_bytes, kTileRows);
     if (st != cudaSuccess) return st;
-    st = make_map(&map_cols, w_values, static_cast<uint64_t>(plan.groups) * plan.m, k_bytes, k_bytes,
-                  plan.m % 256 == 0 ? 256 : 128);
+    st = plan.maps_w.get(&map_cols_p, w_values, static_cast<uint64_t>(plan.groups) * plan.m, k_bytes, k_bytes,
+                         plan.m % 256 == 0 ? 256 : 128);
     if (st != cudaSuccess) return st;
+    const CUtensorMap& map_rows = *map_rows_p;
+    const CUtensorMap& map_cols = *map_cols_p;
     Params p{};
     p.rows = total_routes;
     p.cols = plan.groups * plan.m;
@@ -415,7 +482,6 @@ cudaError_t run_grouped(const GroupedPlan& plan, const uint8_t* a_values, const 
     }
     p.col_tiles = plan.m / 128;
     return launch<kNvf4, 128, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
-    (void)kBlockN;
 }
 
 }  // namespace gemm
@@ -423,21 +489,6 @@ cudaError_t run_grouped(const GroupedPlan& plan, const uint8_t* a_values, const 
 
 using namespace eider;
 using namespace eider::gemm;
-
-#ifdef EIDER_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_dtrace(long long* host) {
-    return cudaMemcpyFromSymbol(host, eider::decode::g_dtrace, sizeof(long long) * 512 * 8);
-}
-extern "C" __attribute__((visibility("default"))) cudaError_t eider_b200_debug_read_trace(long long* host, int reset) {
-    cudaError_t st = cudaMemcpyFromSymbol(host, eider::gemm::g_trace, sizeof(long long) * 256 * 8);
-    if (st != cudaSuccess) return st;
-    if (reset) {
-        static long long zeros[256 * 8] = {0};
-        st = cudaMemcpyToSymbol(eider::gemm::g_trace, zeros, sizeof(zeros));
-    }
-    return st;
-}
-#endif
 
 extern "C" {
 
@@ -484,21 +535,28 @@ cudaError_t eider_b200_gemm_plan_set_output_peers(void* raw, void* const* peers,
     if (!plan || count > 8 || (count > 0 && (!peers || ld_out < plan->n || ld_out % 16 != 0))) return cudaErrorInvalidValue;
     for (uint32_t q = 0; q < count; ++q)
         if (!peers[q] || (reinterpret_cast<uintptr_t>(peers[q]) & 31) != 0) return cudaErrorInvalidValue;
-    for (uint32_t q = 0; q < 8; ++q) plan->peers[q] = q < count ? peers[q] : nullptr;
-    plan->n_peers = count;
-    plan->peer_ld = ld_out;
+    // Everything that can fail happens before the plan changes, so a failed call leaves the previous setting in force.
     if (count > 0) {
         CUtensorMap maps[8];
         for (uint32_t q = 0; q < count; ++q) {
             cudaError_t st = make_out_map(&maps[q], peers[q], plan->m, plan->n, ld_out);
             if (st != cudaSuccess) return st;
         }
-        if (!plan->peer_maps) {
-            cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&plan->peer_maps), 8 * sizeof(CUtensorMap));
+        CUtensorMap* device_maps = plan->peer_maps;
+        if (!device_maps) {
+            cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&device_maps), 8 * sizeof(CUtensorMap));
             if (st != cudaSuccess) return st;
         }
-        return cudaMemcpy(plan->peer_maps, maps, count * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+        cudaError_t st = cudaMemcpy(device_maps, maps, count * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+        if (st != cudaSuccess) {
+            if (!plan->peer_maps) cudaFree(device_maps);
+            return st;
+        }
+        plan->peer_maps = device_maps;
     }
+    for (uint32_t q = 0; q < 8; ++q) plan->peers[q] = q < count ? peers[q] : nullptr;
+    plan->n_peers = count;
+    plan->peer_ld = ld_out;
     return cudaSuccess;
 }
 
@@ -633,12 +691,8 @@ extern "C++" {
 template <typename XT>
 cudaError_t launch_fp8_fused_decode(const CUtensorMap& map_w, const decode_fp8::Params& p, cudaStream_t stream) {
     auto kernel = decode_fp8::fp8_decode_fused_kernel<XT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 76 * 1024);
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    static std::atomic<uint8_t> configured[kMaxDevices];
+    if (cudaError_t st = opt_in_smem(configured, kernel, 76 * 1024); st != cudaSuccess) return st;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.row_tiles * p.splits);
     cfg.blockDim = dim3(decode_fp8::kThreads);
@@ -657,12 +711,8 @@ extern "C++" {
 template <int TERMS, typename XT>
 cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, bool many, cudaStream_t stream) {
     auto kernel = decode::nvfp4_decode_fused_kernel<TERMS, XT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(decode::kSmemBytes));
-        if (st != cudaSuccess) return st;
-        configured = true;
-    }
+    static std::atomic<uint8_t> configured[kMaxDevices];
+    if (cudaError_t st = opt_in_smem(configured, kernel, decode::kSmemBytes); st != cudaSuccess) return st;
     // Programmatic dependent launch: setup and the first weight requests of this kernel overlap the tail of the kernel
     // before it; the kernel waits (griddepcontrol.wait) before it reads x or touches scratch, counters and output.
     cudaLaunchConfig_t cfg = {};
@@ -795,9 +845,10 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
     const uint32_t fused_tokens = input_is_bf16 ? 3u : 2u;
     if (tokens <= fused_tokens && plan->path != kDecodeSplit && (many || plan->fused_splits != 0) && (reinterpret_cast<uintptr_t>(input) & 15) == 0) {
         // one launch: the activation is expanded inside the GEMV CTAs
-        CUtensorMap map_w;
-        cudaError_t fst = make_map(&map_w, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);
+        const CUtensorMap* map_w_p;
+        cudaError_t fst = plan->maps_w.get(&map_w_p, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);
         if (fst != cudaSuccess) return fst;
+        const CUtensorMap& map_w = *map_w_p;
         decode::Params p{};
         p.x = input;
         p.tokens = tokens;
@@ -824,8 +875,9 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
         // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 gets eight
         return input_is_bf16 ? launch_fused_decode<4, uint16_t>(map_w, p, many, stream) : launch_fused_decode<8, float>(map_w, p, many, stream);
     }
-    // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding
-    const uint32_t terms = (input_is_bf16 && plan->terms > 4) ? 4u : plan->terms;
+    // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 activations get
+    // eight terms whenever the call's tokens fit the 256 operand rows, whatever the plan's capacity is
+    const uint32_t terms = input_is_bf16 ? 4u : (tokens * 8 <= plan->max_tokens * plan->terms ? 8u : 4u);
     cudaError_t st = eider_b200_expand_nvfp4_terms_on_stream(input, input_is_bf16, plan->act_packed, plan->act_scales,
                                                              plan->act_col_scale, tokens, plan->k, terms, stream);
     if (st != cudaSuccess) return st;
@@ -846,9 +898,10 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
     if (tokens <= decode_fp8::kMaxTokens && plan->many_splits != 0 && plan->path != kDecodeSplit &&
         (reinterpret_cast<uintptr_t>(input) & 15) == 0 && plan->k % 16 == 0) {
         // one launch: the per-token quantizer runs inside the GEMV CTAs
-        CUtensorMap map_w;
-        cudaError_t fst = make_map(&map_w, weight, plan->n, plan->k, plan->k, kTileRows);
+        const CUtensorMap* map_w_p;
+        cudaError_t fst = plan->maps_w.get(&map_w_p, weight, plan->n, plan->k, plan->k, kTileRows);
         if (fst != cudaSuccess) return fst;
+        const CUtensorMap& map_w = *map_w_p;
         decode_fp8::Params p{};
         p.x = input;
         p.tokens = tokens;
@@ -881,6 +934,95 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
                       d, weight_scale, 0.0f, out_is_bf16, stream);
 }
 
+
+// ---- stateless entry points of the reference, served by cached plans --------------------------------------------
+namespace {
+
+// The reference's GEMV / FP8-linear calls carry no plan.  The kernels here need one (split-K scratch, counters, a status
+// word), so these entry points keep one decode plan per (device, kind, out features, in features), created by the first
+// call with that shape.  That first call allocates and must therefore come before any stream capture; later calls only
+// launch.  Calls with the same shape share the plan's scratch and must not overlap on the GPU.
+struct ShimPlans {
+    struct Entry {
+        int dev, kind;
+        uint32_t max_tokens, n, k;
+        DecodePlan* plan;
+    };
+    std::mutex mutex;
+    std::vector<Entry> entries;
+
+    DecodePlan* get(int kind, uint32_t max_tokens, uint32_t n, uint32_t k) {
+        const int dev = current_device();
+        std::lock_guard<std::mutex> lock(mutex);
+        for (const Entry& e : entries)
+            if (e.dev == dev && e.kind == kind && e.max_tokens >= max_tokens && e.n == n && e.k == k) return e.plan;
+        DecodePlan* plan = make_decode_plan(kind, max_tokens, n, k);
+        if (plan) entries.push_back({dev, kind, max_tokens, n, k, plan});
+        return plan;
+    }
+};
+ShimPlans g_shim_plans;
+
+}  // namespace
+
+/* crates/eider-cuda/src/ffi.rs:576-588 (crates/eider-cuda/native/cutlass_gemv.cu:165-243): W4A4 GEMV, d[m] = alpha *
+ * sum_k a[m][k] * b[k]; a = weight rows with tiled scales (outer = output feature), b = one NVFP4 activation row with
+ * tiled scales (outer = 0); c must be non-null as in the reference and is not read (its beta is 0). */
+int infer_cutlass_fp4_gemv_f32_supported(uint32_t m, uint32_t k) { return (m > 0 && k > 0 && k % 32 == 0 && k <= 32768) ? 1 : 0; }
+
+cudaError_t infer_cutlass_fp4_gemv_f32_on_stream(const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* b_values,
+                                                 const uint8_t* b_scales, const float* c, float* d, uint32_t m, uint32_t k,
+                                                 float alpha, cudaStream_t stream) {
+    if (!a_values || !a_scales || !b_values || !b_scales || !c || !d || !infer_cutlass_fp4_gemv_f32_supported(m, k))
+        return cudaErrorInvalidValue;
+    DecodePlan* plan = g_shim_plans.get(kNvf4, 1, m, k);
+    if (!plan) return cudaErrorMemoryAllocation;
+    return run_decode(*plan, 1, b_values, b_scales, nullptr, 1, a_values, a_scales, nullptr, nullptr, d, alpha, 0.0f, 0, stream);
+}
+
+/* crates/eider-cuda/src/ffi.rs:3131 (kernels crates/eider-cuda/native/non_gemm.cu:9826-9863, 9952-10011): one token,
+ * per-token dynamic E4M3 activation, per-channel weight scales, f32 output [rows]. */
+cudaError_t infer_fp8_linear_channel_scaled_dynamic_f32_on_stream(const float* input, const uint8_t* weight,
+                                                                  const float* channel_weight_scale, float* output,
+                                                                  uint32_t rows, uint32_t cols, cudaStream_t stream) {
+    if (!input || !weight || !channel_weight_scale || !output || rows == 0 || cols == 0 || cols % 16 != 0)
+        return cudaErrorInvalidValue;
+    DecodePlan* plan = g_shim_plans.get(kFp8, 1, rows, cols);
+    if (!plan) return cudaErrorMemoryAllocation;
+    return eider_b200_fp8_linear_decode_on_stream(plan, input, 0, 1, weight, channel_weight_scale, 1.0f, output, 0, stream);
+}
+
+/* crates/eider-cuda/src/ffi.rs:3151: the same operator that also hands back the quantized activation and its scale
+ * (`threads` is the reference's launch width and has no meaning here). */
+cudaError_t infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream(
+    const float* input, uint8_t* quantized_input, const uint8_t* weight, const float* channel_weight_scale, float* input_scale,
+    float* output, uint32_t rows, uint32_t cols, uint32_t threads, cudaStream_t stream) {
+    (void)threads;
+    if (!input || !quantized_input || !weight || !channel_weight_scale || !input_scale || !output || rows == 0 || cols == 0 ||
+        cols % 16 != 0)
+        return cudaErrorInvalidValue;
+    DecodePlan* plan = g_shim_plans.get(kFp8, 1, rows, cols);
+    if (!plan) return cudaErrorMemoryAllocation;
+    cudaError_t st = infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(input, quantized_input, input_scale, 1, cols, stream);
+    if (st != cudaSuccess) return st;
+    return run_decode(*plan, 1, quantized_input, nullptr, input_scale, 1, weight, nullptr, channel_weight_scale, nullptr, output,
+                      1.0f, 0.0f, 0, stream);
+}
+
+/* crates/eider-cuda/src/ffi.rs:3239: static activation scale, per-tensor weight scale:
+ * y[n] = (sum_k e4m3(x / input_scale) * e4m3(w[n][k])) * weight_scale * input_scale. */
+cudaError_t infer_fp8_linear_w8a8_f32_on_stream(const float* input, const uint8_t* weight, float* output, uint32_t rows,
+                                                uint32_t cols, float weight_scale, float input_scale, cudaStream_t stream) {
+    if (!input || !weight || !output || rows == 0 || cols == 0 || cols % 16 != 0 || !(input_scale > 0.0f) || !isfinite(input_scale))
+        return cudaErrorInvalidValue;
+    DecodePlan* plan = g_shim_plans.get(kFp8, 1, rows, cols);
+    if (!plan) return cudaErrorMemoryAllocation;
+    cudaError_t st = infer_quantize_fp8_e4m3_f32_on_stream(input, plan->act_packed, cols, input_scale, stream);
+    if (st != cudaSuccess) return st;
+    return run_decode(*plan, 1, plan->act_packed, nullptr, nullptr, 1, weight, nullptr, nullptr, nullptr, output,
+                      weight_scale * input_scale, 0.0f, 0, stream);
+}
+
 // ---- routed-MoE grouped GEMM --------------------------------------------------------------------------
 /* Supersedes infer_cutlass_fp4_grouped_gemm_{supported,create,destroy,on_stream} (crates/eider-cuda/src/ffi.rs:643-667,
  * crates/eider-cuda/native/cutlass_grouped_gemm.cu).  m = out features per expert, max_n = most rows one expert may get,
@@ -893,7 +1035,7 @@ int eider_b200_nvfp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t
 
 void* eider_b200_nvfp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
     if (!eider_b200_nvfp4_grouped_gemm_supported(m, max_n, k, groups)) return nullptr;
-    auto* plan = new GroupedPlan{m, max_n, k, groups, nullptr};
+    auto* plan = new GroupedPlan{m, max_n, k, groups, nullptr, {}, {}};
     if (alloc_status(&plan->status) != cudaSuccess) {
         delete plan;
         return nullptr;

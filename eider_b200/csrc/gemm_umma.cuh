@@ -118,18 +118,6 @@ template <int KIND, int BLOCK_N> struct TmemPlan {
     static constexpr uint32_t kSfBOffset = kSfAOffset + kSfACols;
 };
 
-#ifdef EIDER_GEMM_TRACE
-// Bring-up instrumentation (never compiled into the shipped library): per-CTA cycle counters.
-// [cta][0] mma total, [1] mma wait full, [2] mma wait acc_empty, [3] epilogue total, [4] epilogue wait acc_full,
-// [5] producer wait empty, [6] producer total, [7] tiles
-__device__ long long g_trace[256][8];
-#define TRACE_ADD(slot, v) g_trace[blockIdx.x][slot] += (v)
-#define TRACE_NOW() clock64()
-#else
-#define TRACE_ADD(slot, v) ((void)0)
-#define TRACE_NOW() 0ll
-#endif
-
 struct TileCoord {
     uint32_t row0;        // first row-operand row of the tile
     uint32_t row_end;     // one past the last valid row (group end for grouped GEMM)
@@ -320,8 +308,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
 
     if (GROUPED) umma::griddep_wait();  // the expert offsets come from a preceding kernel
     GroupWalker walker{p.group_offsets, p.groups, p.col_tiles};
-    const long long tr_e0_outer = TRACE_NOW();
-    (void)tr_e0_outer;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -332,14 +318,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             TileCoord t;
             bool ok = true;
             bool dep_waited = false;
-            const long long tr_p0 = TRACE_NOW();
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x) {
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
                     const uint32_t stage = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
-                    const long long tr_w = TRACE_NOW();
                     if (!__all_sync(0xffffffffu, umma::mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
-                    if (leader) TRACE_ADD(5, TRACE_NOW() - tr_w);
                     if (!leader) continue;
                     const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
                     uint32_t bytes = L::kA + L::kB;
@@ -383,7 +366,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     if (TRANSPOSED) load_cols(); else load_rows();
                 }
             }
-            if (leader) TRACE_ADD(6, TRACE_NOW() - tr_p0);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -402,13 +384,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             uint32_t it = 0, tile_count = 0;
             TileCoord t;
             bool ok = true;
-            const long long tr_m0 = TRACE_NOW();
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x, ++tile_count) {
                 const uint32_t acc = tile_count % kAcc;
                 const uint32_t acc_phase = (tile_count / kAcc) & 1;
-                const long long tr_a = TRACE_NOW();
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
-                if (leader) { TRACE_ADD(2, TRACE_NOW() - tr_a); TRACE_ADD(7, 1); }
                 umma::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
                 // a column tile that does not start on a 128-row scale tile starts (col0 % 128) / 32 columns into it
@@ -417,9 +396,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
                     const uint32_t stage = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
-                    const long long tr_f = TRACE_NOW();
                     if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
-                    if (leader) TRACE_ADD(1, TRACE_NOW() - tr_f);
                     umma::tc_fence_after();
                     // descriptors differ from the per-CTA base only in the start-address field (16-byte units)
                     const uint32_t a_lo = a_lo0 + stage * (L::kA >> 4);
@@ -478,7 +455,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 if (ok && leader) umma::tc_commit(&acc_full[acc]);
                 __syncwarp();
             }
-            if (leader) TRACE_ADD(0, TRACE_NOW() - tr_m0);
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
@@ -491,9 +467,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
             const bool empty_tile = t.k_stage0 >= t.k_stage1;  // a K split with no stages contributes zeros
-            const long long tr_w = TRACE_NOW();
             if (!umma::mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
-            if (threadIdx.x == 64) TRACE_ADD(4, TRACE_NOW() - tr_w);
             umma::tc_fence_after();
             const uint32_t row = t.row0 + quad * 32 + lane;
             const bool row_ok = row < t.row_end;
@@ -693,7 +667,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
         }
     }
 
-    if (threadIdx.x == 64) TRACE_ADD(3, TRACE_NOW() - tr_e0_outer);
     // ---------------------------------------------------------------------- teardown
     umma::tc_fence_before();
     __syncthreads();

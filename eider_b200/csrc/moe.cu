@@ -5,6 +5,7 @@
 //
 // Semantics follow crates/eider-cuda/native/non_gemm.cu (lines cited per kernel).
 #include "common.cuh"
+#include "rowops.cuh"
 #include "eider_b200.h"
 
 namespace eider {
@@ -320,6 +321,57 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quantize_kernel(const uint16
     }
 }
 
+// Quantize sorted rows straight from their source, one thread per 16-element block, grid flat over routes x blocks.
+// The source row and the value formula depend on MODE:
+//   kPlain       f32 rows, row = gather ? sorted_routes[sorted] / routes_per_row : sorted          (non_gemm.cu:2621-2676)
+//   kCalibrated  the same rows times 1 / input_scales[expert]                                      (non_gemm.cu:2562-2600)
+//   kReluSquared sorted bf16 rows: max(x, 0)^2 times 1 / input_scales[expert]                      (same kernel)
+//   kGeluPair    sorted bf16 gate and up rows: GELU-tanh(gate) * up                                (non_gemm.cu:2705-2780)
+enum SortedQuantMode { kPlain = 0, kCalibrated = 1, kReluSquared = 2, kGeluPair = 3 };
+
+template <int MODE>
+__global__ void __launch_bounds__(256) moe_quantize_sorted_kernel(const void* __restrict__ input, const void* __restrict__ input2,
+                                                                  const float* __restrict__ input_scales,
+                                                                  const uint32_t* __restrict__ sorted_routes,
+                                                                  const uint32_t* __restrict__ sorted_experts,
+                                                                  const uint32_t* __restrict__ offsets, uint8_t* __restrict__ packed,
+                                                                  uint8_t* __restrict__ scales, uint32_t routes,
+                                                                  uint32_t routes_per_row, uint32_t k, uint32_t tile_bytes,
+                                                                  int gather_rows) {
+    const uint32_t blocks = k / 16;
+    const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (unit >= static_cast<uint64_t>(routes) * blocks) return;
+    const uint32_t sorted = static_cast<uint32_t>(unit / blocks), b = static_cast<uint32_t>(unit % blocks);
+    const uint32_t expert = __ldg(sorted_experts + sorted);
+    float v[16];
+    if (MODE == kPlain || MODE == kCalibrated) {
+        const uint32_t src_row = gather_rows ? __ldg(sorted_routes + sorted) / routes_per_row : sorted;
+        const float* src = static_cast<const float*>(input) + static_cast<size_t>(src_row) * k + b * 16;
+        const float inverse = MODE == kCalibrated ? __frcp_rn(__ldg(input_scales + expert)) : 1.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = MODE == kCalibrated ? __fmul_rn(__ldg(src + i), inverse) : __ldg(src + i);
+    } else {
+        const uint16_t* src = static_cast<const uint16_t*>(input) + static_cast<size_t>(sorted) * k + b * 16;
+        if (MODE == kReluSquared) {
+            const float inverse = __frcp_rn(__ldg(input_scales + expert));
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float x = fmaxf(bf16_bits_to_float(__ldg(src + i)), 0.0f);
+                v[i] = __fmul_rn(__fmul_rn(x, x), inverse);
+            }
+        } else {
+            const uint16_t* up = static_cast<const uint16_t*>(input2) + static_cast<size_t>(sorted) * k + b * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = rowops::gelu_tanh_mul(bf16_bits_to_float(__ldg(src + i)), bf16_bits_to_float(__ldg(up + i)));
+        }
+    }
+    uint2 bytes;
+    const uint8_t sc = quantize_block16(v, 16, &bytes);
+    uint8_t* dst = packed + static_cast<size_t>(sorted) * (k / 2) + b * 8;  // 8-byte aligned when `packed` is (k % 16 == 0)
+    *reinterpret_cast<uint2*>(dst) = bytes;
+    scales[moe_scale_base(expert, offsets, tile_bytes) + tiled_scale_offset(sorted - __ldg(offsets + expert), b, k)] = sc;
+}
+
 // non_gemm.cu:3066-3083
 __global__ void moe_pointer_tables_kernel(const uint32_t* __restrict__ offsets, const uint8_t* packed, const uint8_t* scales,
                                           uint16_t* output, const uint8_t** packed_table, const uint8_t** scale_table,
@@ -443,16 +495,12 @@ size_t eider_b200_moe_sort_scratch_bytes(uint32_t routes, uint32_t experts) {
     return static_cast<size_t>((routes + kSortChunk - 1) / kSortChunk) * experts * sizeof(uint32_t);
 }
 
-cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* indices, uint32_t* expert_counts, uint32_t* expert_offsets,
-                                                 uint32_t* expert_cursors, uint32_t* sorted_routes, uint32_t* sorted_experts,
-                                                 uint32_t* route_to_sorted, uint32_t routes, uint32_t experts, void* scratch,
-                                                 size_t scratch_bytes, cudaStream_t stream) {
-    if (!indices || !expert_counts || !expert_offsets || !expert_cursors || !sorted_routes || !sorted_experts ||
-        !route_to_sorted || !scratch || routes == 0 || experts == 0 || experts > 1024 ||
-        scratch_bytes < eider_b200_moe_sort_scratch_bytes(routes, experts))
-        return cudaErrorInvalidValue;
+// The three launches of the stable route sort over a chunk-histogram table of ceil(routes / 256) * experts words.
+static cudaError_t sort_routes_with(uint32_t* chunk_hist, const uint32_t* indices, uint32_t* expert_counts,
+                                    uint32_t* expert_offsets, uint32_t* expert_cursors, uint32_t* sorted_routes,
+                                    uint32_t* sorted_experts, uint32_t* route_to_sorted, uint32_t routes, uint32_t experts,
+                                    cudaStream_t stream) {
     const uint32_t chunks = (routes + kSortChunk - 1) / kSortChunk;
-    uint32_t* chunk_hist = static_cast<uint32_t*>(scratch);
     moe_chunk_hist_kernel<<<chunks, kSortChunk, experts * sizeof(uint32_t), stream>>>(indices, chunk_hist, routes, experts);
     cudaError_t st = cudaGetLastError();
     if (st != cudaSuccess) return st;
@@ -462,6 +510,18 @@ cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* indices, uint32
     moe_scatter_kernel<<<chunks, kSortChunk, (kSortChunk / 32) * experts * sizeof(uint32_t), stream>>>(
         indices, chunk_hist, expert_offsets, sorted_routes, sorted_experts, route_to_sorted, routes, experts);
     return cudaGetLastError();
+}
+
+cudaError_t eider_b200_moe_sort_routes_on_stream(const uint32_t* indices, uint32_t* expert_counts, uint32_t* expert_offsets,
+                                                 uint32_t* expert_cursors, uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                                 uint32_t* route_to_sorted, uint32_t routes, uint32_t experts, void* scratch,
+                                                 size_t scratch_bytes, cudaStream_t stream) {
+    if (!indices || !expert_counts || !expert_offsets || !expert_cursors || !sorted_routes || !sorted_experts ||
+        !route_to_sorted || !scratch || routes == 0 || experts == 0 || experts > 1024 ||
+        scratch_bytes < eider_b200_moe_sort_scratch_bytes(routes, experts))
+        return cudaErrorInvalidValue;
+    return sort_routes_with(static_cast<uint32_t*>(scratch), indices, expert_counts, expert_offsets, expert_cursors, sorted_routes,
+                            sorted_experts, route_to_sorted, routes, experts, stream);
 }
 
 // Route sort for callers that cannot hand over scratch memory and must not trigger an allocation: same outputs as
@@ -482,15 +542,17 @@ cudaError_t eider_b200_moe_sort_routes_noalloc_on_stream(const uint32_t* indices
     uint32_t* chunk_hist = nullptr;
     cudaError_t st = noalloc_sort_scratch(&chunk_hist);
     if (st != cudaSuccess) return st;
-    moe_chunk_hist_kernel<<<chunks, kSortChunk, experts * sizeof(uint32_t), stream>>>(indices, chunk_hist, routes, experts);
-    st = cudaGetLastError();
-    if (st != cudaSuccess) return st;
-    moe_prefix_kernel<<<1, 1024, 0, stream>>>(chunk_hist, expert_counts, expert_offsets, expert_cursors, chunks, experts);
-    st = cudaGetLastError();
-    if (st != cudaSuccess) return st;
-    moe_scatter_kernel<<<chunks, kSortChunk, (kSortChunk / 32) * experts * sizeof(uint32_t), stream>>>(
-        indices, chunk_hist, expert_offsets, sorted_routes, sorted_experts, route_to_sorted, routes, experts);
-    return cudaGetLastError();
+    return sort_routes_with(chunk_hist, indices, expert_counts, expert_offsets, expert_cursors, sorted_routes, sorted_experts,
+                            route_to_sorted, routes, experts, stream);
+}
+
+// crates/eider-cuda/src/ffi.rs:1701: the reference's sort call, which passes no scratch.  Same stable sort through the
+// table inside the library, hence the same size limit and the same rule about overlapping calls as the entry point above.
+cudaError_t infer_moe_sort_routes_on_stream(const uint32_t* indices, uint32_t* expert_counts, uint32_t* expert_offsets,
+                                            uint32_t* expert_cursors, uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                            uint32_t* route_to_sorted, uint32_t routes, uint32_t experts, cudaStream_t stream) {
+    return eider_b200_moe_sort_routes_noalloc_on_stream(indices, expert_counts, expert_offsets, expert_cursors, sorted_routes,
+                                                        sorted_experts, route_to_sorted, routes, experts, stream);
 }
 
 size_t eider_b200_moe_sort_noalloc_max_entries(void) { return kNoAllocSortEntries; }
@@ -543,6 +605,80 @@ cudaError_t infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(con
     const uint64_t units = static_cast<uint64_t>(routes) * (in_features / 8);
     moe_silu_mul_quantize_kernel<<<static_cast<uint32_t>((units + 255) / 256), 256, 0, stream>>>(
         gate_up, sorted_experts, expert_offsets, packed, scales, routes, in_features, scale_tile_bytes);
+    return cudaGetLastError();
+}
+
+static cudaError_t launch_sorted_quant(int mode, const void* input, const void* input2, const float* input_scales,
+                                       const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+                                       const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales, uint32_t routes,
+                                       uint32_t routes_per_row, uint32_t k, uint32_t tile_bytes, int gather_rows,
+                                       cudaStream_t stream) {
+    if (!input || !sorted_routes || !sorted_experts || !expert_offsets || !packed || !scales || routes == 0 ||
+        routes_per_row == 0 || k == 0 || k % 16 != 0 || tile_bytes == 0 || (reinterpret_cast<uintptr_t>(packed) & 7) != 0)
+        return cudaErrorInvalidValue;
+    const uint64_t units = static_cast<uint64_t>(routes) * (k / 16);
+    const uint32_t grid = static_cast<uint32_t>((units + 255) / 256);
+#define EIDER_SORTED_QUANT(M)                                                                                                  \
+    moe_quantize_sorted_kernel<M><<<grid, 256, 0, stream>>>(input, input2, input_scales, sorted_routes, sorted_experts,        \
+                                                            expert_offsets, packed, scales, routes, routes_per_row, k, tile_bytes, \
+                                                            gather_rows)
+    switch (mode) {
+        case kPlain: EIDER_SORTED_QUANT(kPlain); break;
+        case kCalibrated: EIDER_SORTED_QUANT(kCalibrated); break;
+        case kReluSquared: EIDER_SORTED_QUANT(kReluSquared); break;
+        default: EIDER_SORTED_QUANT(kGeluPair); break;
+    }
+#undef EIDER_SORTED_QUANT
+    return cudaGetLastError();
+}
+
+cudaError_t infer_moe_quantize_sorted_routes_nvfp4_on_stream(const float* input, const uint32_t* sorted_routes,
+                                                             const uint32_t* sorted_experts, const uint32_t* expert_offsets,
+                                                             uint8_t* packed, uint8_t* scales, uint32_t routes,
+                                                             uint32_t routes_per_row, uint32_t in_features,
+                                                             uint32_t scale_tile_bytes, int gather_rows, cudaStream_t stream) {
+    return launch_sorted_quant(kPlain, input, nullptr, nullptr, sorted_routes, sorted_experts, expert_offsets, packed, scales,
+                               routes, routes_per_row, in_features, scale_tile_bytes, gather_rows, stream);
+}
+
+cudaError_t infer_moe_calibrated_quantize_on_stream(const void* input, const float* input_scales, const uint32_t* sorted_routes,
+                                                    const uint32_t* sorted_experts, const uint32_t* expert_offsets,
+                                                    uint8_t* packed, uint8_t* scales, uint32_t routes, uint32_t routes_per_row,
+                                                    uint32_t features, uint32_t scale_tile_bytes, int relu_squared,
+                                                    cudaStream_t stream) {
+    if (!input_scales) return cudaErrorInvalidValue;
+    return launch_sorted_quant(relu_squared ? kReluSquared : kCalibrated, input, nullptr, input_scales, sorted_routes,
+                               sorted_experts, expert_offsets, packed, scales, routes, routes_per_row, features,
+                               scale_tile_bytes, 1, stream);
+}
+
+cudaError_t infer_moe_gelu_tanh_mul_quantize_sorted_routes_nvfp4_on_stream(const uint16_t* gate, const uint16_t* up,
+                                                                           const uint32_t* sorted_experts,
+                                                                           const uint32_t* expert_offsets, uint8_t* packed,
+                                                                           uint8_t* scales, uint32_t routes, uint32_t in_features,
+                                                                           uint32_t scale_tile_bytes, cudaStream_t stream) {
+    if (!up) return cudaErrorInvalidValue;
+    // (the kernel reads no route ids in this mode; the expert ids stand in for the non-null argument)
+    return launch_sorted_quant(kGeluPair, gate, up, nullptr, sorted_experts, sorted_experts, expert_offsets, packed, scales, routes,
+                               1, in_features, scale_tile_bytes, 0, stream);
+}
+
+cudaError_t infer_moe_gather_rms_norm_quantize_sorted_routes_nvfp4_on_stream(
+    const float* input, const float* weight, const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+    const uint32_t* expert_offsets, uint8_t* source_packed, uint8_t* source_scales, uint8_t* packed, uint8_t* scales,
+    uint32_t rows, uint32_t routes, uint32_t routes_per_row, uint32_t in_features, uint32_t scale_tile_bytes, float eps,
+    cudaStream_t stream) {
+    if (!input || !weight || !sorted_routes || !sorted_experts || !expert_offsets || !source_packed || !source_scales ||
+        !packed || !scales || rows == 0 || routes == 0 || routes_per_row == 0 || in_features == 0 || in_features % 16 != 0 ||
+        scale_tile_bytes == 0)
+        return cudaErrorInvalidValue;
+    // every token is normalised and quantized once (unit global scale), then its bytes are scattered to its routes
+    cudaError_t st = infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(input, weight, source_packed, source_scales, rows,
+                                                                           in_features, eps, 1.0f, stream);
+    if (st != cudaSuccess) return st;
+    moe_scatter_rows_kernel<<<(routes + kScatterWarps - 1) / kScatterWarps, kScatterWarps * 32, 0, stream>>>(
+        source_packed, source_scales, sorted_routes, sorted_experts, expert_offsets, packed, scales, routes, routes_per_row,
+        in_features, scale_tile_bytes, 1);
     return cudaGetLastError();
 }
 

@@ -7,6 +7,7 @@
 // Numerics restate crates/eider-cuda/native/non_gemm.cu:106-155 with IEEE divisions
 // (the reference's host twin, crates/eider-cuda/src/format.rs:242-292, is the arbiter).
 #include "common.cuh"
+#include "rowops.cuh"
 #include "eider_b200.h"
 
 namespace eider {
@@ -412,8 +413,7 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_nvfp4_kernel(const floa
         const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float sigmoid = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g[i])));
-            v[4 * q + i] = div_rn(__fmul_rn(__fmul_rn(g[i], sigmoid), u[i]), di);
+            v[4 * q + i] = div_rn(rowops::silu_sigmoid_mul(g[i], u[i]), di);
         }
     }
     uint2 bytes;
@@ -435,28 +435,9 @@ __global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const floa
                                                                       uint8_t* __restrict__ residual_scales, uint32_t cols, float eps,
                                                                       float input_scale) {
     __shared__ float red[8];
-    __shared__ float inverse_rms;
     const uint32_t row = blockIdx.x;
     const float* x = input + static_cast<size_t>(row) * cols;
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
-        ss = fmaf(v.x, v.x, ss);
-        ss = fmaf(v.y, v.y, ss);
-        ss = fmaf(v.z, v.z, ss);
-        ss = fmaf(v.w, v.w, ss);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float total = 0.0f;
-        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
-        inverse_rms = rsqrtf(__fdiv_rn(total, static_cast<float>(cols)) + eps);
-    }
-    __syncthreads();
-    const float inv = inverse_rms;
+    const float inv = rowops::inverse_rms(rowops::block_sum_ordered(rowops::thread_sum_squares_f4(x, cols), red), cols, eps);
     const Divisor di = make_divisor(input_scale);
     for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
         float v[16];
@@ -464,10 +445,10 @@ __global__ void __launch_bounds__(256) rms_norm_quantize_nvfp4_kernel(const floa
         for (int q = 0; q < 4; ++q) {
             const float4 x4 = __ldg(reinterpret_cast<const float4*>(x + b * 16) + q);
             const float4 w4 = __ldg(reinterpret_cast<const float4*>(weight + b * 16) + q);
-            v[4 * q + 0] = div_rn(__fmul_rn(__fmul_rn(x4.x, inv), w4.x), di);
-            v[4 * q + 1] = div_rn(__fmul_rn(__fmul_rn(x4.y, inv), w4.y), di);
-            v[4 * q + 2] = div_rn(__fmul_rn(__fmul_rn(x4.z, inv), w4.z), di);
-            v[4 * q + 3] = div_rn(__fmul_rn(__fmul_rn(x4.w, inv), w4.w), di);
+            v[4 * q + 0] = div_rn(rowops::normed(x4.x, inv, w4.x), di);
+            v[4 * q + 1] = div_rn(rowops::normed(x4.y, inv, w4.y), di);
+            v[4 * q + 2] = div_rn(rowops::normed(x4.z, inv, w4.z), di);
+            v[4 * q + 3] = div_rn(rowops::normed(x4.w, inv, w4.w), di);
         }
         uint2 bytes;
         const uint8_t sc = quantize_block16(v, 16, &bytes);
@@ -496,37 +477,22 @@ __global__ void __launch_bounds__(256) rms_norm_add_rms_norm_quantize_nvfp4_kern
     __shared__ float red[8];
     const uint32_t row = blockIdx.x;
     const size_t off = static_cast<size_t>(row) * cols;
-    auto block_sum = [&](float v) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-        __syncthreads();
-        float total = 0.0f;
-        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
-        __syncthreads();
-        return total;
-    };
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(input + off) + i);
-        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-    }
-    const float inv0 = rsqrtf(__fdiv_rn(block_sum(ss), static_cast<float>(cols)) + input_eps);
+    const float inv0 = rowops::inverse_rms(rowops::block_sum_ordered(rowops::thread_sum_squares_f4(input + off, cols), red), cols, input_eps);
     float ss2 = 0.0f;
     for (uint32_t i = threadIdx.x; i < cols / 4; i += blockDim.x) {
         const float4 v = __ldg(reinterpret_cast<const float4*>(input + off) + i);
         const float4 w = __ldg(reinterpret_cast<const float4*>(input_weight) + i);
         const float4 r = __ldg(reinterpret_cast<const float4*>(residual + off) + i);
         float4 h;
-        h.x = fmaf(__fmul_rn(v.x, inv0), w.x, r.x);
-        h.y = fmaf(__fmul_rn(v.y, inv0), w.y, r.y);
-        h.z = fmaf(__fmul_rn(v.z, inv0), w.z, r.z);
-        h.w = fmaf(__fmul_rn(v.w, inv0), w.w, r.w);
+        h.x = rowops::normed_add(v.x, inv0, w.x, r.x);
+        h.y = rowops::normed_add(v.y, inv0, w.y, r.y);
+        h.z = rowops::normed_add(v.z, inv0, w.z, r.z);
+        h.w = rowops::normed_add(v.w, inv0, w.w, r.w);
         reinterpret_cast<float4*>(output + off)[i] = h;
         reinterpret_cast<float4*>(staged)[i] = h;
         ss2 = fmaf(h.x, h.x, ss2); ss2 = fmaf(h.y, h.y, ss2); ss2 = fmaf(h.z, h.z, ss2); ss2 = fmaf(h.w, h.w, ss2);
     }
-    const float inv1 = rsqrtf(__fdiv_rn(block_sum(ss2), static_cast<float>(cols)) + quant_eps);  // (block_sum's barriers order the staging)
+    const float inv1 = rowops::inverse_rms(rowops::block_sum_ordered(ss2, red), cols, quant_eps);  // (its barriers order the staging)
     const Divisor di = make_divisor(input_scale);
     for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
         float v[16];
@@ -534,10 +500,10 @@ __global__ void __launch_bounds__(256) rms_norm_add_rms_norm_quantize_nvfp4_kern
         for (int q = 0; q < 4; ++q) {
             const float4 h4 = reinterpret_cast<const float4*>(staged + b * 16)[q];
             const float4 w4 = __ldg(reinterpret_cast<const float4*>(quant_weight + b * 16) + q);
-            v[4 * q + 0] = div_rn(__fmul_rn(__fmul_rn(h4.x, inv1), w4.x), di);
-            v[4 * q + 1] = div_rn(__fmul_rn(__fmul_rn(h4.y, inv1), w4.y), di);
-            v[4 * q + 2] = div_rn(__fmul_rn(__fmul_rn(h4.z, inv1), w4.z), di);
-            v[4 * q + 3] = div_rn(__fmul_rn(__fmul_rn(h4.w, inv1), w4.w), di);
+            v[4 * q + 0] = div_rn(rowops::normed(h4.x, inv1, w4.x), di);
+            v[4 * q + 1] = div_rn(rowops::normed(h4.y, inv1, w4.y), di);
+            v[4 * q + 2] = div_rn(rowops::normed(h4.z, inv1, w4.z), di);
+            v[4 * q + 3] = div_rn(rowops::normed(h4.w, inv1, w4.w), di);
         }
         uint2 bytes;
         const uint8_t sc = quantize_block16(v, 16, &bytes);
@@ -709,6 +675,10 @@ cudaError_t infer_rms_norm_quantize_nvfp4_pair_col_major_f32_on_stream(const flo
     return cudaGetLastError();
 }
 
+// The row is staged in dynamic shared memory beside the kernel's 32 bytes of static shared memory; both must fit the
+// 48 KB a kernel gets without opting in.
+constexpr uint32_t kAddNormMaxCols = (48 * 1024 - 64) / 4 / 16 * 16;  // 12272
+
 cudaError_t infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream(const float* input, const float* input_weight,
                                                                           const float* residual, float* output,
                                                                           const float* quant_weight, uint8_t* packed,
@@ -716,7 +686,7 @@ cudaError_t infer_rms_norm_add_then_rms_norm_quantize_nvfp4_f32_on_stream(const 
                                                                           float input_eps, float quant_eps, float input_scale,
                                                                           cudaStream_t stream) {
     if (!input || !input_weight || !residual || !output || !quant_weight || !packed || !scales || rows == 0 || cols == 0 ||
-        cols % 16 != 0 || cols > 48 * 1024 / 4 || !(input_eps >= 0.0f) || !isfinite(input_eps) || !(quant_eps >= 0.0f) ||
+        cols % 16 != 0 || cols > kAddNormMaxCols || !(input_eps >= 0.0f) || !isfinite(input_eps) || !(quant_eps >= 0.0f) ||
         !isfinite(quant_eps) || bad_scale(input_scale) || (reinterpret_cast<uintptr_t>(packed) & 7) != 0 ||
         ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(input_weight) | reinterpret_cast<uintptr_t>(residual) |
           reinterpret_cast<uintptr_t>(output) | reinterpret_cast<uintptr_t>(quant_weight)) & 15) != 0)

@@ -81,7 +81,8 @@ def quantize_nvfp4(x: torch.Tensor, input_scale: float = 1.0, out: Nvfp4Matrix |
 
 
 def quantize_nvfp4_rowscale(x: torch.Tensor, out: Nvfp4Matrix | None = None) -> Nvfp4Matrix:
-    """Per-token global scale g = amax/2688, then the reference quantizer with input_scale = g."""
+    """Per-token global scale g = the smallest power of two >= amax/2688 (1 for an all-zero row), then the reference
+    quantizer with input_scale = g; g lands in `row_scales`."""
     lib = _lib.load()
     tokens, k = x.shape
     if x.dtype not in (torch.float32, torch.bfloat16):
@@ -405,8 +406,9 @@ class Nvfp4DecodePlan:
     PATHS = {"auto": 0, "stream": 1, "fused": 2, "split": 3, "fused_many": 4}
 
     def set_path(self, path: str) -> None:
-        """Kernel family for one or two tokens: "auto" (the CUDA-core streaming GEMV), "stream", "fused" (single-launch
-        tcgen05 kernel) or "split" (expansion kernel + split-K tcgen05 GEMM)."""
+        """Kernel family for a few tokens: "auto" (single-launch tcgen05 kernel, one work item per CTA), "stream" (CUDA-core
+        streaming GEMV), "fused" (single-launch kernel, persistent CTAs), "split" (expansion kernel + split-K tcgen05 GEMM),
+        "fused_many" (what "auto" picks when the shape allows it)."""
         if not self._lib.eider_b200_decode_plan_set_path(self._plan, self.PATHS[path]):
             raise ShapeError(f"decode path {path!r} was refused")
 

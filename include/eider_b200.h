@@ -43,8 +43,9 @@ EIDER_B200_API cudaError_t infer_quantize_nvfp4_col_major_f32_on_stream(const fl
 EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_bf16_on_stream(const uint16_t* input, uint8_t* packed,
                                                                     uint8_t* scales, uint32_t rows, uint32_t cols,
                                                                     float input_scale, cudaStream_t stream);
-/* On-the-fly quantizer of the prefill GEMM: per token g = amax / 2688 (1 for an all-zero row), then the
- * operator above with input_scale = g; g is written to row_scales[cols].  Supersedes the static-scale
+/* On-the-fly quantizer of the prefill GEMM: per token g = the smallest power of two >= amax / 2688 (1 for an all-zero
+ * row; a power of two makes the division by g exact), then the operator above with input_scale = g; g is written to
+ * row_scales[cols].  Supersedes the static-scale
  * call of crates/eider-cuda/src/modelopt_device.rs:178-194 for inputs without a calibrated scale. */
 EIDER_B200_API cudaError_t eider_b200_quantize_nvfp4_rowscale_on_stream(const void* input, int input_is_bf16,
                                                                         uint8_t* packed, uint8_t* scales,
@@ -105,6 +106,64 @@ EIDER_B200_API cudaError_t eider_b200_silu_mul_halves_quantize_nvfp4_batch_on_st
                                                                                      uint32_t rows, float input_scale,
                                                                                      cudaStream_t stream);
 
+/* Staged halves of the fused producers above: the reference keeps them as separate operators and its tests require
+ * fused == staged byte for byte (crates/eider-cuda/src/kernels/non_gemm.rs:19687-19750, 19873-20240); here both halves take
+ * every sum and product from the same device functions.
+ * crates/eider-cuda/src/ffi.rs:1393 (kernel non_gemm.cu:631-667): output = input * rsqrt(mean(input^2) + eps) * weight. */
+EIDER_B200_API cudaError_t infer_rms_norm_f32_on_stream(const float* input, const float* weight, float* output, uint32_t rows,
+                                                        uint32_t cols, float eps, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1402 (kernel non_gemm.cu:700-727): the same plus `residual`. */
+EIDER_B200_API cudaError_t infer_rms_norm_add_f32_on_stream(const float* input, const float* weight, const float* residual,
+                                                            float* output, uint32_t rows, uint32_t cols, float eps,
+                                                            cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3937 (kernel non_gemm.cu:11514-11549): input * inverse_rms * weight * silu(gate). */
+EIDER_B200_API cudaError_t infer_gated_rms_norm_f32_on_stream(const float* input, const float* gate, const float* weight,
+                                                              float* output, uint32_t rows, uint32_t cols, float eps,
+                                                              cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1506 and :1520 (kernel non_gemm.cu:1357-1370): rows of [gate | up] ->
+ * (gate / (1 + exp(-gate))) * up, f32 [rows][cols]. */
+EIDER_B200_API cudaError_t infer_silu_mul_halves_f32_on_stream(const float* gate_up, float* output, uint32_t len,
+                                                               cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_silu_mul_halves_f32_batch_on_stream(const float* gate_up, float* output, uint32_t rows,
+                                                                     uint32_t cols, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1492: tanh-approximated GELU(gate) * up over `len` elements. */
+EIDER_B200_API cudaError_t infer_gelu_tanh_mul_f32_on_stream(const float* gate, const float* up, float* output, uint32_t len,
+                                                             cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:2873 (kernel non_gemm.cu:8898-8915): attention output [heads][tokens][head_dim] ->
+ * token-major rows [output_row_offset + token][heads * head_dim]. */
+EIDER_B200_API cudaError_t infer_unpack_heads_f32_on_stream(const float* input, float* output, uint32_t tokens, uint32_t heads,
+                                                            uint32_t head_dim, uint32_t output_row_offset, cudaStream_t stream);
+
+/* Fused producer GELU-tanh(gate) * up -> NVFP4 (crates/eider-cuda/src/ffi.rs:2405, kernel non_gemm.cu:421-508): gate and
+ * up are [rows][cols] f32.  This implementation needs cols % 16 == 0 and 16-byte aligned gate and up. */
+EIDER_B200_API cudaError_t infer_gelu_tanh_mul_quantize_nvfp4_col_major_f32_on_stream(const float* gate, const float* up,
+                                                                                      uint8_t* packed, uint8_t* scales,
+                                                                                      uint32_t rows, uint32_t cols,
+                                                                                      float input_scale, cudaStream_t stream);
+/* Fused producer head unpack -> NVFP4 (crates/eider-cuda/src/ffi.rs:2882 and :2893, kernel non_gemm.cu:8951-9060): rows
+ * output_row_offset .. output_row_offset + tokens of an NVFP4 matrix with heads * head_dim columns; other rows are not
+ * touched.  This implementation needs head_dim % 16 == 0. */
+EIDER_B200_API cudaError_t infer_unpack_heads_quantize_nvfp4_col_major_f32_on_stream(const float* input, uint8_t* packed,
+                                                                                     uint8_t* scales, uint32_t tokens,
+                                                                                     uint32_t heads, uint32_t head_dim,
+                                                                                     uint32_t output_row_offset,
+                                                                                     float input_scale, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_unpack_heads_quantize_nvfp4_col_major_bf16_on_stream(const uint16_t* input, uint8_t* packed,
+                                                                                      uint8_t* scales, uint32_t tokens,
+                                                                                      uint32_t heads, uint32_t head_dim,
+                                                                                      uint32_t output_row_offset,
+                                                                                      float input_scale, cudaStream_t stream);
+/* Fused producer per-head gated RMSNorm -> NVFP4 (crates/eider-cuda/src/ffi.rs:3948, kernel non_gemm.cu:12029-12120):
+ * head_dim must be 128, as in the reference. */
+EIDER_B200_API cudaError_t infer_gated_rms_norm_quantize_nvfp4_col_major_f32_on_stream(
+    const float* input, const float* gate, const float* weight, uint8_t* packed, uint8_t* scales, uint32_t rows, uint32_t heads,
+    uint32_t head_dim, float eps, float input_scale, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:2415 (kernel non_gemm.cu:510-557): one vector of `rows` values; scales[b] is the scale
+ * byte of values 16b .. 16b + 15 in plain order (no tiling). */
+EIDER_B200_API cudaError_t infer_quantize_nvfp4_vector_simple_scales_f32_on_stream(const float* input, uint8_t* packed,
+                                                                                   uint8_t* scales, uint32_t rows,
+                                                                                   float input_scale, cudaStream_t stream);
+
 /* ---- FP8 E4M3 quantizers -------------------------------------------------------------------- */
 
 /* crates/eider-cuda/src/ffi.rs:3198 and :3206 (kernels non_gemm.cu:9952-9974, 10028-10066). */
@@ -126,6 +185,16 @@ EIDER_B200_API cudaError_t infer_quantize_fp8_e4m3_f32_on_stream(const float* in
 EIDER_B200_API cudaError_t eider_b200_quantize_fp8_weight_on_stream(const void* weight, int input_is_bf16, uint8_t* q,
                                                                     float* channel_scale, uint32_t out_features,
                                                                     uint32_t in_features, cudaStream_t stream);
+
+/* crates/eider-cuda/src/ffi.rs:3223 and :3231: in-place values[i] *= channel_scale[i] * scalar[0], and
+ * values[r][c] *= channel_scale[c] * row_scale[r].  The fused FP8 plans below apply both scales in their epilogue; these
+ * stay for callers that still scale in a separate pass. */
+EIDER_B200_API cudaError_t infer_scale_channel_f32_device_scalar_on_stream(float* values, const float* channel_scale,
+                                                                           const float* scalar, uint32_t len,
+                                                                           cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_scale_channel_f32_device_row_scalar_on_stream(float* values, const float* channel_scale,
+                                                                               const float* row_scale, uint32_t rows,
+                                                                               uint32_t channels, cudaStream_t stream);
 
 /* ---- decode GEMV on CUDA cores (exact f32 semantics of the reference) ------------------------ */
 
@@ -199,10 +268,35 @@ EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_on_stream(void* plan, co
                                                                   int out_is_bf16, cudaStream_t stream);
 EIDER_B200_API void eider_b200_decode_destroy(void* plan);
 EIDER_B200_API cudaError_t eider_b200_decode_plan_status(void* plan, uint32_t* host_status);
-/* Kernel family for one or two tokens of an NVFP4 decode plan: 0 = automatic (the CUDA-core streaming GEMV),
- * 1 = streaming GEMV only, 2 = single-launch tcgen05 kernel with in-kernel activation expansion, 3 = expansion kernel +
- * split-K tcgen05 GEMM (what three or more tokens always use).  Returns 1 on success. */
+/* Kernel family for a few tokens of an NVFP4 decode plan: 0 = automatic (the single-launch tcgen05 kernel, one work item
+ * per CTA, for up to three bf16 or two f32 tokens; the expansion kernel + split-K tcgen05 GEMM beyond), 1 = CUDA-core
+ * streaming GEMV (one or two tokens), 2 = single-launch tcgen05 kernel with persistent CTAs, 3 = expansion kernel + split-K
+ * tcgen05 GEMM always, 4 = single-launch kernel with one work item per CTA.  Returns 1 on success. */
 EIDER_B200_API int eider_b200_decode_plan_set_path(void* plan, uint32_t path);
+
+/* Plan-less entry points of the reference, served by the kernels above through plans the library keeps per (device, out
+ * features, in features).  The first call with a shape allocates its plan and must come before any stream capture; calls
+ * with the same shape share the plan's scratch and must not overlap on one GPU.  in_features % 16 == 0 (FP8), % 32 (NVFP4).
+ * crates/eider-cuda/src/ffi.rs:576-588 (crates/eider-cuda/native/cutlass_gemv.cu:165-243): W4A4 GEMV with F32 output,
+ * d[m] = alpha * sum_k a[m][k] * b[k]; a = weight rows, b = one NVFP4 activation row, both with tiled scales; c must be
+ * non-null as in the reference and is not read. */
+EIDER_B200_API int infer_cutlass_fp4_gemv_f32_supported(uint32_t m, uint32_t k);
+EIDER_B200_API cudaError_t infer_cutlass_fp4_gemv_f32_on_stream(const uint8_t* a_values, const uint8_t* a_scales,
+                                                                const uint8_t* b_values, const uint8_t* b_scales, const float* c,
+                                                                float* d, uint32_t m, uint32_t k, float alpha,
+                                                                cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3131, :3151 and :3239 (kernels non_gemm.cu:9826-10011): one token, rows = out features,
+ * cols = in features. */
+EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_f32_on_stream(const float* input, const uint8_t* weight,
+                                                                                 const float* channel_weight_scale,
+                                                                                 float* output, uint32_t rows, uint32_t cols,
+                                                                                 cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream(
+    const float* input, uint8_t* quantized_input, const uint8_t* weight, const float* channel_weight_scale, float* input_scale,
+    float* output, uint32_t rows, uint32_t cols, uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_w8a8_f32_on_stream(const float* input, const uint8_t* weight, float* output,
+                                                               uint32_t rows, uint32_t cols, float weight_scale,
+                                                               float input_scale, cudaStream_t stream);
 
 /* ---- routed MoE ----------------------------------------------------------------------------------- */
 
@@ -235,6 +329,37 @@ EIDER_B200_API cudaError_t eider_b200_moe_sort_routes_noalloc_on_stream(const ui
                                                                         uint32_t* route_to_sorted, uint32_t routes,
                                                                         uint32_t experts, cudaStream_t stream);
 EIDER_B200_API size_t eider_b200_moe_sort_noalloc_max_entries(void);
+/* crates/eider-cuda/src/ffi.rs:1701 (kernels non_gemm.cu:2473-2550): the reference's sort call as it is, without scratch.
+ * It runs the stable sort above through the table inside the library, so it has the same limit on ceil(routes / 256) *
+ * experts and the same rules (first call per device before any capture, no overlapping sorts on one GPU). */
+EIDER_B200_API cudaError_t infer_moe_sort_routes_on_stream(const uint32_t* indices, uint32_t* expert_counts,
+                                                           uint32_t* expert_offsets, uint32_t* expert_cursors,
+                                                           uint32_t* sorted_routes, uint32_t* sorted_experts,
+                                                           uint32_t* route_to_sorted, uint32_t routes, uint32_t experts,
+                                                           cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1728 (kernel non_gemm.cu:2621-2700): quantize sorted rows straight from f32 rows (unit
+ * global scale); row of sorted route s = gather_rows ? sorted_routes[s] / routes_per_row : s.  in_features % 16 == 0. */
+EIDER_B200_API cudaError_t infer_moe_quantize_sorted_routes_nvfp4_on_stream(
+    const float* input, const uint32_t* sorted_routes, const uint32_t* sorted_experts, const uint32_t* expert_offsets,
+    uint8_t* packed, uint8_t* scales, uint32_t routes, uint32_t routes_per_row, uint32_t in_features, uint32_t scale_tile_bytes,
+    int gather_rows, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1713 (kernel non_gemm.cu:2562-2619): per-expert calibrated scales, value = x * (1 /
+ * input_scales[expert]); relu_squared = 0: f32 token rows gathered by route; 1: sorted bf16 rows, max(x, 0)^2 first. */
+EIDER_B200_API cudaError_t infer_moe_calibrated_quantize_on_stream(
+    const void* input, const float* input_scales, const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+    const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales, uint32_t routes, uint32_t routes_per_row,
+    uint32_t features, uint32_t scale_tile_bytes, int relu_squared, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1742 (kernel non_gemm.cu:2705-2803): GELU-tanh(gate) * up of sorted bf16 rows. */
+EIDER_B200_API cudaError_t infer_moe_gelu_tanh_mul_quantize_sorted_routes_nvfp4_on_stream(
+    const uint16_t* gate, const uint16_t* up, const uint32_t* sorted_experts, const uint32_t* expert_offsets, uint8_t* packed,
+    uint8_t* scales, uint32_t routes, uint32_t in_features, uint32_t scale_tile_bytes, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1765 (kernel non_gemm.cu:3000-3064): RMSNorm each token once, quantize it (unit scale)
+ * into source_packed / source_scales, then scatter as the gather + quantize call below does. */
+EIDER_B200_API cudaError_t infer_moe_gather_rms_norm_quantize_sorted_routes_nvfp4_on_stream(
+    const float* input, const float* weight, const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+    const uint32_t* expert_offsets, uint8_t* source_packed, uint8_t* source_scales, uint8_t* packed, uint8_t* scales,
+    uint32_t rows, uint32_t routes, uint32_t routes_per_row, uint32_t in_features, uint32_t scale_tile_bytes, float eps,
+    cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:1783 (kernels non_gemm.cu:2899-2998): quantize each token once (unit global scale) into
  * source_packed / source_scales, then scatter the bytes into expert-major rows and per-expert 128-row scale tiles. */
 EIDER_B200_API cudaError_t infer_moe_gather_quantize_sorted_routes_nvfp4_on_stream(

@@ -21,9 +21,10 @@ _REF_PATH = os.path.join(_DIR, "_ref", "libfp4_oracle.so")
 
 
 def build(ref: bool = True) -> None:
-    """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
+    """Compile liboracle.so and, when a checkout of the reference is found (REFERENCE_ROOT, or a `reference`
+    directory beside the repository), its C++ conversion oracle into oracle/_ref."""
     subprocess.run(["make", "-C", _DIR, "all"], check=True, capture_output=True)
-    ref_root = os.environ.get("REFERENCE_ROOT", "/root/reference")
+    ref_root = os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_DIR)), "reference")
     if ref and os.path.exists(os.path.join(ref_root, "crates/eider-cuda/native/fp4_oracle.cpp")):
         subprocess.run(["make", "-C", _DIR, "ref", f"REFERENCE_ROOT={ref_root}"], check=True,
                        capture_output=True)
