@@ -427,6 +427,49 @@ def moe_combine(route_to_sorted, route_weights, sorted_bf16_bits, rows, routes_p
     return out
 
 
+def gelu_tanh_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * up in f32, operation by operation
+    (crates/eider-cuda/native/non_gemm.cu:446-451); tanh is numpy's, so the last place may differ from the device's."""
+    g, u = _f32(gate), _f32(up)
+    cubic = (g * g) * g
+    inner = np.float32(0.7978845608028654) * (g + np.float32(0.044715) * cubic)
+    return ((np.float32(0.5) * g) * (np.float32(1.0) + np.tanh(inner).astype(np.float32))) * u
+
+
+def quantize_nvfp4_vector_simple_scales(x: np.ndarray, input_scale: float = 1.0):
+    """One vector, one scale byte per 16 values in plain order (crates/eider-cuda/native/non_gemm.cu:510-541):
+    -> (packed [(n + 1) // 2], scales [ceil(n / 16)])."""
+    v = _f32(x).reshape(-1)
+    n = v.size
+    blocks = (n + 15) // 16
+    padded = np.zeros((1, blocks * 16), np.float32)
+    padded[0, :n] = v
+    packed, tiled = quantize_nvfp4(padded, input_scale)
+    scales = np.array([tiled[tiled_scale_offset(0, b, blocks * 16)] for b in range(blocks)], np.uint8)
+    return packed.reshape(-1)[:(n + 1) // 2].copy(), scales
+
+
+def moe_quantize_rows_into_expert_tiles(values: np.ndarray, sorted_experts, offsets, experts: int):
+    """Quantize already sorted f32 rows (unit global scale) into expert-major NVFP4 rows and per-expert scale tiles
+    (crates/eider-cuda/native/non_gemm.cu:2554-2557, 2621-2676): -> (packed [R, K/2], scales)."""
+    v = _f32(values)
+    r, k = v.shape
+    return moe_gather_quantize(v, np.arange(r, dtype=np.uint32), np.ascontiguousarray(sorted_experts, np.uint32),
+                               np.ascontiguousarray(offsets, np.uint32), 1, experts, gather_rows=False)
+
+
+def moe_calibrated_values(x: np.ndarray, input_scales, sorted_routes, sorted_experts, routes_per_row: int,
+                          relu_squared: bool = False) -> np.ndarray:
+    """The f32 values the per-expert calibrated quantizer sees (crates/eider-cuda/native/non_gemm.cu:2562-2585):
+    value = x * (1 / input_scales[expert]); relu_squared: x = max(bf16 row, 0)^2 of the sorted row itself."""
+    inv = (np.float32(1.0) / _f32(input_scales))[np.asarray(sorted_experts, np.int64)][:, None]
+    if relu_squared:
+        v = np.maximum(_f32(x), np.float32(0.0))
+        return (v * v) * inv
+    rows = np.asarray(sorted_routes, np.int64) // routes_per_row
+    return _f32(x)[rows] * inv
+
+
 # ---- reference's own conversion oracle (oracle/_ref) ---------------------------------------
 def load_reference_codec():
     """ctypes handle on oracle/_ref/libfp4_oracle.so or None when it was not built."""

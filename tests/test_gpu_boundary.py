@@ -1,0 +1,284 @@
+"""Entry points that keep the reference's names and argument lists (crates/eider-cuda/src/ffi.rs), called through ctypes
+exactly as a binding would call them, against the CPU oracle: the scratch-free route sort, the direct sorted-row
+quantizers (plain, calibrated, ReLU^2, GELU), the RMSNorm gather, the pointer tables, the plan-less W4A4 GEMV and the
+plan-less FP8 linears."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from tests.util import gemm_close, require_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    require_cuda()
+    from eider_b200 import _lib
+    return _lib.load()
+
+
+def dev(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def i32(a):
+    return dev(np.ascontiguousarray(a, np.uint32).view(np.int32))
+
+
+def u32(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+def sort_on_device(lib, ind, experts):
+    import torch
+    routes = ind.size
+    z = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")
+    out = dict(counts=z(experts), offsets=z(experts + 1), cursors=z(experts), sorted_routes=z(routes), sorted_experts=z(routes),
+               inverse=z(routes))
+    ind_d = i32(ind)
+    st = lib.infer_moe_sort_routes_on_stream(ind_d.data_ptr(), out["counts"].data_ptr(), out["offsets"].data_ptr(),
+                                             out["cursors"].data_ptr(), out["sorted_routes"].data_ptr(),
+                                             out["sorted_experts"].data_ptr(), out["inverse"].data_ptr(), routes, experts, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    return out
+
+
+def moe_buffers(routes, experts, k):
+    import torch
+    tile = 128 * ((k // 16 + 3) // 4 * 4)
+    return (torch.zeros(routes, k // 2, dtype=torch.uint8, device="cuda"),
+            torch.zeros(((routes + 127) // 128 + experts) * tile, dtype=torch.uint8, device="cuda"), tile)
+
+
+@pytest.mark.parametrize("routes,experts", [(8, 4), (21, 5), (32768, 128), (65536, 1024)])
+def test_reference_sort_call_matches_oracle(lib, oracle, routes, experts):
+    # crates/eider-cuda/src/ffi.rs:1701; (65536, 1024) is exactly the 262144-entry limit of the built-in table
+    rng = np.random.default_rng(routes)
+    ind = (np.array([3, 1, 3, 0, 1, 2, 3, 2], np.uint32) if routes == 8 else rng.integers(0, experts, routes).astype(np.uint32))
+    got = sort_on_device(lib, ind, experts)
+    counts, offsets, sorted_routes, sorted_experts, inverse = oracle.moe_sort_routes(ind, experts)
+    assert np.array_equal(u32(got["counts"]), counts)
+    assert np.array_equal(u32(got["offsets"]), offsets)
+    assert np.array_equal(u32(got["cursors"]), offsets[1:])  # where the reference's atomic cursors end up
+    assert np.array_equal(u32(got["sorted_routes"]), sorted_routes)
+    assert np.array_equal(u32(got["sorted_experts"]), sorted_experts)
+    assert np.array_equal(u32(got["inverse"]), inverse)
+    if routes == 8:
+        assert counts.tolist() == [1, 2, 2, 3] and offsets.tolist() == [0, 1, 3, 5, 8]
+
+
+def test_reference_sort_call_rejects_what_the_table_cannot_hold(lib):
+    import torch
+    routes, experts = 65536 + 256, 1024
+    z = torch.zeros(routes + experts + 1, dtype=torch.int32, device="cuda")
+    assert lib.infer_moe_sort_routes_on_stream(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
+                                               z.data_ptr(), routes, experts, None) == 1
+    assert lib.infer_moe_sort_routes_on_stream(None, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(),
+                                               z.data_ptr(), 8, 4, None) == 1
+
+
+@pytest.mark.parametrize("gather", [1, 0])
+@pytest.mark.parametrize("tokens,top,experts,k", [(7, 3, 5, 80), (512, 8, 16, 2048)])
+def test_quantize_sorted_routes_matches_oracle(lib, oracle, tokens, top, experts, k, gather):
+    # crates/eider-cuda/src/ffi.rs:1728: rows gathered by route, or already in sorted order
+    import torch
+    rng = np.random.default_rng(tokens + k)
+    routes = tokens * top
+    ind = rng.integers(0, experts, routes).astype(np.uint32)
+    s = sort_on_device(lib, ind, experts)
+    x = rng.standard_normal((tokens if gather else routes, k)).astype(np.float32)
+    packed, scales, tile = moe_buffers(routes, experts, k)
+    st = lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(dev(x).data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
+                                                              s["offsets"].data_ptr(), packed.data_ptr(), scales.data_ptr(), routes, top, k,
+                                                              tile, gather, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    _, offsets, sorted_routes, sorted_experts, _ = oracle.moe_sort_routes(ind, experts)
+    p_ref, s_ref = oracle.moe_gather_quantize(x, sorted_routes, sorted_experts, offsets, top, experts, gather_rows=bool(gather))
+    assert np.array_equal(packed.cpu().numpy(), p_ref)
+    assert np.array_equal(scales.cpu().numpy(), s_ref)
+
+
+@pytest.mark.parametrize("relu", [0, 1])
+def test_calibrated_quantize_reference_fixture(lib, oracle, relu):
+    # crates/eider-cuda/src/kernels/non_gemm.rs:15168-15249: 7 tokens x top-3 x 5 experts x K = 80, index pattern
+    # [0, 4, 1, 0, 1, 4, 3], per-expert scales [.125, .25, 1, 2, .5]
+    import torch
+    rows, top, experts, k = 7, 3, 5, 80
+    routes = rows * top
+    ind = np.array([[0, 4, 1, 0, 1, 4, 3][i % 7] for i in range(routes)], np.uint32)
+    scales_in = np.array([0.125, 0.25, 1.0, 2.0, 0.5], np.float32)
+    values = ((np.arange(rows * k) % 29).astype(np.float32) / 16.0 - 0.75).astype(np.float32).reshape(rows, k)
+    sorted_bf16 = oracle.bf16_round(((np.arange(routes * k) % 37).astype(np.float32) / 16.0 - 1.0).astype(np.float32)).reshape(routes, k)
+    s = sort_on_device(lib, ind, experts)
+    packed, scales, tile = moe_buffers(routes, experts, k)
+    src = dev(sorted_bf16, torch.bfloat16) if relu else dev(values)
+    st = lib.infer_moe_calibrated_quantize_on_stream(src.data_ptr(), dev(scales_in).data_ptr(), s["sorted_routes"].data_ptr(),
+                                                     s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(), packed.data_ptr(),
+                                                     scales.data_ptr(), routes, top, k, tile, relu, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    _, offsets, sorted_routes, sorted_experts, _ = oracle.moe_sort_routes(ind, experts)
+    vals = oracle.moe_calibrated_values(sorted_bf16 if relu else values, scales_in, sorted_routes, sorted_experts, top, bool(relu))
+    p_ref, s_ref = oracle.moe_quantize_rows_into_expert_tiles(vals, sorted_experts, offsets, experts)
+    assert np.array_equal(packed.cpu().numpy(), p_ref)
+    assert np.array_equal(scales.cpu().numpy(), s_ref)
+    # and the reference's own per-row statement: each sorted row equals the host quantizer on value / scale
+    for srt in range(routes):
+        e = int(sorted_experts[srt])
+        row = (np.maximum(sorted_bf16[srt], 0) ** 2 if relu else values[int(sorted_routes[srt]) // top]) / scales_in[e]
+        pr, _ = oracle.quantize_nvfp4(row[None].astype(np.float32), 1.0)
+        assert np.array_equal(packed.cpu().numpy()[srt], pr[0])
+
+
+def test_gelu_sorted_routes_matches_staged_quantizer(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:1742: GELU-tanh(gate) * up of sorted bf16 rows == the same values through the f32 operator
+    # and the direct sorted-row quantizer (byte for byte), and the CPU oracle up to tanh's last place
+    import torch
+    routes, experts, k = 600, 9, 768
+    rng = np.random.default_rng(3)
+    ind = rng.integers(0, experts, routes).astype(np.uint32)
+    s = sort_on_device(lib, ind, experts)
+    gate = oracle.bf16_round((rng.standard_normal((routes, k)) * 2).astype(np.float32))
+    up = oracle.bf16_round(rng.standard_normal((routes, k)).astype(np.float32))
+    fused_p, fused_s, tile = moe_buffers(routes, experts, k)
+    st = lib.infer_moe_gelu_tanh_mul_quantize_sorted_routes_nvfp4_on_stream(
+        dev(gate, torch.bfloat16).data_ptr(), dev(up, torch.bfloat16).data_ptr(), s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(),
+        fused_p.data_ptr(), fused_s.data_ptr(), routes, k, tile, None)
+    assert st == 0
+    act = torch.empty(routes, k, device="cuda")
+    assert lib.infer_gelu_tanh_mul_f32_on_stream(dev(gate).data_ptr(), dev(up).data_ptr(), act.data_ptr(), routes * k, None) == 0
+    staged_p, staged_s, _ = moe_buffers(routes, experts, k)
+    assert lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(act.data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
+                                                                s["offsets"].data_ptr(), staged_p.data_ptr(), staged_s.data_ptr(), routes, 1, k,
+                                                                tile, 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(fused_p, staged_p) and torch.equal(fused_s, staged_s)
+    _, offsets, _, sorted_experts, _ = oracle.moe_sort_routes(ind, experts)
+    p_ref, _ = oracle.moe_quantize_rows_into_expert_tiles(oracle.gelu_tanh_mul(gate, up), sorted_experts, offsets, experts)
+    assert np.count_nonzero(fused_p.cpu().numpy() != p_ref) / p_ref.size < 2e-3
+
+
+def test_gather_rms_norm_quantize_equals_norm_then_gather(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:1765 == RMSNorm -> NVFP4 of every token (unit scale), then the byte scatter
+    import torch
+    tokens, top, experts, k = 96, 4, 8, 1024
+    routes = tokens * top
+    rng = np.random.default_rng(5)
+    ind = rng.integers(0, experts, routes).astype(np.uint32)
+    s = sort_on_device(lib, ind, experts)
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, k).astype(np.float32)
+    xd, wd = dev(x), dev(w)
+    src_p = torch.zeros(tokens, k // 2, dtype=torch.uint8, device="cuda")
+    from eider_b200 import ops
+    src_s = torch.zeros(ops.scale_layout_len(tokens, k), dtype=torch.uint8, device="cuda")
+    packed, scales, tile = moe_buffers(routes, experts, k)
+    st = lib.infer_moe_gather_rms_norm_quantize_sorted_routes_nvfp4_on_stream(
+        xd.data_ptr(), wd.data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(),
+        src_p.data_ptr(), src_s.data_ptr(), packed.data_ptr(), scales.data_ptr(), tokens, routes, top, k, tile, 1e-6, None)
+    assert st == 0
+    # staged on the device: norm to f32, then the direct gather quantizer
+    normed = torch.empty_like(xd)
+    assert lib.infer_rms_norm_f32_on_stream(xd.data_ptr(), wd.data_ptr(), normed.data_ptr(), tokens, k, 1e-6, None) == 0
+    p2, s2, _ = moe_buffers(routes, experts, k)
+    assert lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(normed.data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
+                                                                s["offsets"].data_ptr(), p2.data_ptr(), s2.data_ptr(), routes, top, k, tile, 1,
+                                                                None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed, p2) and torch.equal(scales, s2)
+
+
+def test_grouped_pointer_tables(lib):
+    # crates/eider-cuda/src/ffi.rs:1799 (kernel non_gemm.cu:3066-3083): table[e] = base + offset of expert e
+    import torch
+    experts, k, n = 6, 256, 384
+    tile = 128 * ((k // 16 + 3) // 4 * 4)
+    offsets = np.array([0, 5, 5, 140, 141, 300, 301], np.uint32)
+    routes = int(offsets[-1])
+    packed = torch.zeros(routes, k // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(((routes + 127) // 128 + experts) * tile, dtype=torch.uint8, device="cuda")
+    out = torch.zeros(routes, n, dtype=torch.bfloat16, device="cuda")
+    tables = [torch.zeros(experts, dtype=torch.int64, device="cuda") for _ in range(3)]
+    st = lib.infer_moe_grouped_pointer_tables_on_stream(i32(offsets).data_ptr(), packed.data_ptr(), scales.data_ptr(), out.data_ptr(),
+                                                        tables[0].data_ptr(), tables[1].data_ptr(), tables[2].data_ptr(), experts, k, n,
+                                                        tile, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    for e in range(experts):
+        off = int(offsets[e])
+        assert int(tables[0][e]) == packed.data_ptr() + off * (k // 2)
+        assert int(tables[1][e]) == scales.data_ptr() + ((off + 127) // 128 + e) * tile
+        assert int(tables[2][e]) == out.data_ptr() + off * n * 2
+    assert lib.infer_moe_grouped_pointer_tables_on_stream(None, packed.data_ptr(), scales.data_ptr(), out.data_ptr(), tables[0].data_ptr(),
+                                                          tables[1].data_ptr(), tables[2].data_ptr(), experts, k, n, tile, None) == 1
+
+
+@pytest.mark.parametrize("m,k", [(13824, 5120), (5120, 13824), (300, 96)])
+def test_reference_w4a4_gemv_f32(lib, oracle, m, k):
+    # crates/eider-cuda/src/ffi.rs:576-588 (test crates/eider-cuda/src/cublaslt/fp4_tn.rs:1652-1712): both operands NVFP4,
+    # f32 output; the oracle is the host dequantize + f32 dot product
+    import torch
+
+    from eider_b200 import ops
+    rng = np.random.default_rng(m + k)
+    w = (rng.standard_normal((m, k)) * 0.02).astype(np.float32)
+    wp, ws, g = oracle.quantize_weight(w)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    xp, xs = oracle.quantize_nvfp4(x, 1.0)
+    wd = ops.ModelOptWeight.from_checkpoint(dev(wp), dev(ws), float(g))
+    c = torch.zeros(m, device="cuda")
+    d = torch.full((m + 8,), -77.0, device="cuda")
+    assert lib.infer_cutlass_fp4_gemv_f32_supported(m, k) == 1
+    st = lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), dev(xp).data_ptr(), dev(xs).data_ptr(),
+                                                  c.data_ptr(), d.data_ptr(), m, k, float(g), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    ref = oracle.matmul_nt(oracle.dequantize_tiled(xp, xs), oracle.dequantize_weight(wp, ws), alpha=float(g))[0]
+    ok, stats = gemm_close(d[:m].cpu().numpy(), ref, rel=1e-3, abs_frac=1e-3)  # every product is exact; only the accumulation differs
+    assert ok, stats
+    assert torch.all(d[m:] == -77.0)  # guard elements behind the output stay untouched
+    assert lib.infer_cutlass_fp4_gemv_f32_supported(m, k + 16) == 0
+    assert lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), dev(xp).data_ptr(), dev(xs).data_ptr(),
+                                                    None, d.data_ptr(), m, k, float(g), None) == 1
+
+
+def test_reference_fp8_linear_shims(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:3131, :3151, :3239 at the QKV shape of the decode config
+    import torch
+    n, k = 7168, 5120
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    wq, sw = oracle.quantize_fp8_weight(w)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    xq, sx = oracle.quantize_fp8_dynamic(x)
+    ref = oracle.fp8_linear(xq, sx, wq, sw)[0]
+    wd, swd, xd = dev(wq), dev(sw), dev(x)
+    y = torch.zeros(n, device="cuda")
+    assert lib.infer_fp8_linear_channel_scaled_dynamic_f32_on_stream(xd.data_ptr(), wd.data_ptr(), swd.data_ptr(), y.data_ptr(), n, k, None) == 0
+    torch.cuda.synchronize()
+    ok, stats = gemm_close(y.cpu().numpy(), ref, rel=1e-3, abs_frac=1e-3)
+    assert ok, stats
+    y2 = torch.zeros(n, device="cuda")
+    q_out = torch.zeros(k, dtype=torch.uint8, device="cuda")
+    s_out = torch.zeros(1, device="cuda")
+    assert lib.infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream(
+        xd.data_ptr(), q_out.data_ptr(), wd.data_ptr(), swd.data_ptr(), s_out.data_ptr(), y2.data_ptr(), n, k, 256, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(q_out.cpu().numpy(), xq[0]) and float(s_out.item()) == float(sx[0])
+    ok, stats = gemm_close(y2.cpu().numpy(), ref, rel=1e-3, abs_frac=1e-3)
+    assert ok, stats
+    # static activation scale, per-tensor weight scale
+    xs = oracle.quantize_fp8_static(x, 0.03125)
+    ref3 = oracle.fp8_linear(xs, np.array([0.03125], np.float32), wq, np.full(n, 0.5, np.float32))[0]
+    y3 = torch.zeros(n, device="cuda")
+    assert lib.infer_fp8_linear_w8a8_f32_on_stream(xd.data_ptr(), wd.data_ptr(), y3.data_ptr(), n, k, 0.5, 0.03125, None) == 0
+    torch.cuda.synchronize()
+    ok, stats = gemm_close(y3.cpu().numpy(), ref3, rel=1e-3, abs_frac=1e-3)
+    assert ok, stats
+    assert lib.infer_fp8_linear_w8a8_f32_on_stream(xd.data_ptr(), wd.data_ptr(), y3.data_ptr(), n, k, 0.5, 0.0, None) == 1

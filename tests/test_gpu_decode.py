@@ -66,6 +66,24 @@ def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
     assert torch.equal(y, y2)
 
 
+def test_nvfp4_decode_terms_follow_the_call_not_the_plan(ops, oracle):
+    # a plan made for 64 tokens still gives f32 activations eight residual terms when the call's tokens fit
+    import torch
+    rng = np.random.default_rng(21)
+    n, k = 1024, 2048
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales, g = oracle.quantize_weight(w)
+    wd = ops.ModelOptWeight.from_checkpoint(_dev(packed), _dev(scales), float(g))
+    plan = ops.Nvfp4DecodePlan(64, n, k)
+    for tokens, tol in ((8, 1e-4), (32, 1e-4), (33, 1e-2)):
+        x = rng.standard_normal((tokens, k)).astype(np.float32)
+        y = plan.run(_dev(x), wd, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        ok, stats = gemm_close(to_np(y), oracle.nvfp4_linear_host(x, packed, scales, float(g)), rel=tol, abs_frac=tol)
+        assert ok, (tokens, stats)
+
+
 def test_nvfp4_decode_bf16_out_and_beta(ops, oracle):
     import torch
     rng = np.random.default_rng(9)

@@ -145,8 +145,7 @@ def test_nvfp4_gemm_linearity_full_size(ops):
     torch.cuda.synchronize()
     assert plan.status() == 0
     assert torch.equal(y2.float(), 2.0 * y1.float())
-    # and the result agrees with a bf16 torch matmul of the dequantized operands on a column slice
-    assert torch.isfinite(y1.float()).all()
+    assert torch.isfinite(y1.float()).all()  # (element-wise parity at this shape: test_gpu_full_size.py)
 
 
 def test_fp8_fixture(ops, oracle):

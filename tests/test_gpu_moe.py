@@ -1,5 +1,6 @@
 """Routed-MoE pipeline against the oracle: router, permutation (bit-exact), gather + quantize (bit-exact),
-grouped GEMM, SiLU * up + quantize, combine, and the whole pipeline at a reduced and at the benchmark size."""
+grouped GEMM, SiLU * up + quantize, combine, and the whole pipeline at reduced sizes (the benchmark size is in
+test_gpu_full_size.py)."""
 import numpy as np
 import pytest
 

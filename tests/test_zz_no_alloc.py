@@ -38,7 +38,8 @@ def test_noalloc_sort_matches_scratch_sort_twice_in_a_row():
     lib = _lib.load()
     gen = torch.Generator(device="cuda").manual_seed(123)
     # two different problems back to back: the second must not see anything of the first in the shared table
-    for routes, experts in [(32768, 128), (5000, 60)]:
+    # (the last case fills the built-in table exactly: 256 chunks x 1024 experts = 262144 entries)
+    for routes, experts in [(32768, 128), (5000, 60), (65536, 1024)]:
         ind = torch.randint(0, experts, (routes,), device="cuda", generator=gen, dtype=torch.int32)
         ref, got = _sort_both(lib, torch, ind, experts)
         for a, b in zip(ref, got):
