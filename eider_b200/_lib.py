@@ -14,6 +14,8 @@ _U32 = C.c_uint32
 _F = C.c_float
 _I = C.c_int
 _SZ = C.c_size_t
+_U64 = C.c_uint64
+_S = C.c_char_p
 
 # name -> (restype, argtypes).  Mirrors include/eider_b200.h one to one.
 SIGNATURES = {
@@ -98,6 +100,27 @@ SIGNATURES = {
     "eider_b200_gemm_plan_block_n": (_U32, [_P]),
     "eider_b200_gemm_plan_set_output_peers": (_I, [_P, _P, _U32, _U32]),
     "eider_b200_gemm_plan_status": (_I, [_P, _P]),
+    "eider_b200_gemm_plan_set_output_multicast": (_I, [_P, _P]),
+    "eider_b200_peer_barrier_pad_bytes": (_SZ, []),
+    "eider_b200_peer_barrier_state_bytes": (_SZ, []),
+    "eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P, _P]),
+    "eider_b200_ep_publish_counts_on_stream": (_I, [_P, _P, _U32, _U32, _U32, _P]),
+    "eider_b200_ep_offsets_on_stream": (_I, [_P, _U32, _U32, _U32, _P, _P, _P, _P, _P]),
+    "eider_b200_ep_dispatch_rows_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _U32, _U32, _P]),
+    "eider_b200_ep_expand_experts_on_stream": (_I, [_P, _U32, _P, _U32, _P]),
+    "eider_b200_ep_return_rows_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "eider_b200_nvfp4_artifact_write": (_I, [_S, _S, _U64, _U64, _P, _U64, _P, _U64, _F, _F]),
+    "eider_b200_nvfp4_artifact_read_header": (_I, [_S, _P, _P, _P, _P, _P, _P, _P]),
+    "eider_b200_nvfp4_artifact_read": (_I, [_S, _P, _U64, _P, _U64, _P, _U64]),
+    "eider_b200_compressed_tensors_globals": (_I, [_F, _F, _P, _P]),
+    "eider_b200_mxfp4_scales_to_nvfp4": (_I, [_P, _U64, _P]),
+    "eider_b200_gguf_nvfp4_unpack": (_I, [_P, _U64, _U64, _U64, _F, _P, _P]),
+    "eider_b200_nvfp4_requantize_host": (_I, [_I, _P, _P, _F, _P, _U64, _U64, _P, _P]),
+    "eider_b200_nvfp4_scales_to_tiled_host": (None, [_P, _P, _U64, _U64]),
+    "eider_b200_prepared_cache_write": (_I, [_S, _U64, _U64, _P, _P, _F]),
+    "eider_b200_prepared_cache_matches": (_I, [_S, _U64, _U64]),
+    "eider_b200_prepared_cache_read": (_I, [_S, _U64, _U64, _P, _P, _P]),
+    "eider_b200_peer_barrier_on_stream": (_I, [_P, _U32, _U32, _U32, _P, C.c_uint64, _P]),
 }
 
 

@@ -272,6 +272,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             const bool wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
                               (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             const bool staged = p.out_maps != nullptr;  // (the host sets the maps only for plain bf16 output)
+            const bool multicast = p.out_multicast != nullptr;  // (likewise, and only when the column count is a multiple of 8)
             constexpr uint32_t kSteps = kPairN / 64;
             uint32_t raw[2][64];
             issue(0, raw[0]);
@@ -286,6 +287,35 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     if (lane == 0) umma::mbar_arrive_cluster(accempty0_remote + acc * 8);
                 }
                 const uint32_t c = col_of(step);
+                if (multicast) {
+                    // this warp's 32 rows x 64 columns -> bf16 in the (swizzled) staging buffer, read back so that eight
+                    // consecutive lanes cover one row's 128 bytes, and written once through the multicast mapping
+                    uint8_t* sbuf = smem_store + quad * 2 * L::kStoreBuf;
+                    uint32_t w[32];
+                    convert_bf16x64_scaled(&raw[step & 1][0], rs, nullptr, w);
+                    const uint32_t row_base = umma::smem_u32(sbuf) + lane * 128;
+                    __syncwarp();  // the previous step's read-back is over
+#pragma unroll
+                    for (uint32_t ch = 0; ch < 8; ++ch)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((ch ^ (lane & 7)) << 4)), "r"(w[4 * ch]),
+                                     "r"(w[4 * ch + 1]), "r"(w[4 * ch + 2]), "r"(w[4 * ch + 3])
+                                     : "memory");
+                    __syncwarp();
+                    const uint32_t warp_row0 = t.row0 + quad * 32;
+                    const uint32_t ch = lane & 7;
+                    const uint32_t col = t.col0 + c + ch * 8;
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        const uint32_t r = i * 4 + (lane >> 3);
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                     : "r"(umma::smem_u32(sbuf) + r * 128 + ((ch ^ (r & 7)) << 4)) : "memory");
+                        if (warp_row0 + r < p.rows && col + 8 <= p.cols)
+                            umma::multimem_store_16(static_cast<uint16_t*>(p.out_multicast) + static_cast<size_t>(warp_row0 + r) * p.ld_out + col,
+                                                    v0, v1, v2, v3);
+                    }
+                    continue;
+                }
                 if (staged) {
                     // this warp's 32 rows x 64 columns -> bf16 in a 128-byte-swizzled staging buffer -> one TMA store per
                     // destination (the hardware clips rows and columns past the end of the output)

@@ -218,6 +218,7 @@ struct DensePlan {
     uint32_t n_peers;
     uint32_t peer_ld;       // row pitch (elements) of those outputs
     CUtensorMap* peer_maps; // device array of n_peers bf16 tensor maps over the same column blocks (TMA-store epilogue)
+    void* multicast;        // the same column block inside an NVLink multicast mapping of every rank's output (null = off)
     MapCache maps_x, maps_w;
 };
 
@@ -331,6 +332,11 @@ cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x
         p.ld_out = plan.peer_ld;
         // plain bf16 output on the CTA-pair kernel: whole tiles leave through shared memory and TMA stores
         if (plan.peer_maps && out_is_bf16 && !channel_scale && plan.block_n == kPairBlockCode) p.out_maps = plan.peer_maps;
+        // one multicast store per tile instead of one store per peer
+        if (plan.multicast && out_is_bf16 && !channel_scale && plan.block_n == kPairBlockCode && plan.n % 8 == 0) {
+            p.out_multicast = plan.multicast;
+            p.out_maps = nullptr;
+        }
     }
     if (plan.block_n == kPairBlockCode) {
         // 256 x 256 tiles on CTA pairs
@@ -557,6 +563,14 @@ cudaError_t eider_b200_gemm_plan_set_output_peers(void* raw, void* const* peers,
     for (uint32_t q = 0; q < 8; ++q) plan->peers[q] = q < count ? peers[q] : nullptr;
     plan->n_peers = count;
     plan->peer_ld = ld_out;
+    return cudaSuccess;
+}
+
+cudaError_t eider_b200_gemm_plan_set_output_multicast(void* raw, void* multicast_block) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan || (reinterpret_cast<uintptr_t>(multicast_block) & 15) != 0) return cudaErrorInvalidValue;
+    if (multicast_block && plan->n_peers == 0) return cudaErrorInvalidValue;  // the peer list carries the row pitch and is the fallback
+    plan->multicast = multicast_block;
     return cudaSuccess;
 }
 

@@ -70,6 +70,10 @@ struct Params {
     // n_peers of them: the CTA-pair kernel stages each warp's 32 x 64 block in shared memory and lets the TMA write
     // whole 128-byte lines, which is what makes stores over NVLink efficient.  Null: plain stores.
     const CUtensorMap* out_maps;
+    // The same column block once more, as an address inside an NVLink multicast mapping that covers every rank's output
+    // (this rank's included).  When set, the CTA-pair kernel writes each staged tile ONCE with multimem.st and the switch
+    // replicates it, so a tile leaves this GPU once instead of once per peer.  Stores only.
+    void* out_multicast;
 };
 
 // Calls f(base) for every output buffer of the launch.

@@ -277,10 +277,12 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quantize_kernel(const uint16
                                                                     const uint32_t* __restrict__ sorted_experts,
                                                                     const uint32_t* __restrict__ offsets,
                                                                     uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                                    uint32_t routes, uint32_t k, uint32_t tile_bytes) {
+                                                                    uint32_t routes, uint32_t k, uint32_t tile_bytes,
+                                                                    const uint32_t* __restrict__ routes_limit) {
     const uint32_t halves = k / 8;
     const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const bool live = unit < static_cast<uint64_t>(routes) * halves;
+    // (routes_limit: optional device-resident row count below the launch's capacity, for buffers filled by other ranks)
+    const bool live = unit < static_cast<uint64_t>(routes) * halves && (!routes_limit || unit / halves < __ldg(routes_limit));
     const uint32_t sorted = live ? static_cast<uint32_t>(unit / halves) : 0;
     const uint32_t h = live ? static_cast<uint32_t>(unit % halves) : 0;
     float v[8];
@@ -593,19 +595,26 @@ cudaError_t eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf16_on_stream(
     return cudaGetLastError();
 }
 
+cudaError_t eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream(
+    const uint16_t* gate_up, const uint32_t* sorted_experts, const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales,
+    uint32_t routes, uint32_t in_features, uint32_t scale_tile_bytes, const uint32_t* routes_limit, cudaStream_t stream) {
+    if (!gate_up || !sorted_experts || !expert_offsets || !packed || !scales || routes == 0 || in_features == 0 ||
+        in_features % 16 != 0 || scale_tile_bytes == 0 || (reinterpret_cast<uintptr_t>(gate_up) & 15) != 0)
+        return cudaErrorInvalidValue;
+    const uint64_t units = static_cast<uint64_t>(routes) * (in_features / 8);
+    moe_silu_mul_quantize_kernel<<<static_cast<uint32_t>((units + 255) / 256), 256, 0, stream>>>(
+        gate_up, sorted_experts, expert_offsets, packed, scales, routes, in_features, scale_tile_bytes, routes_limit);
+    return cudaGetLastError();
+}
+
 cudaError_t infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(const uint16_t* gate_up,
                                                                              const uint32_t* sorted_experts,
                                                                              const uint32_t* expert_offsets, uint8_t* packed,
                                                                              uint8_t* scales, uint32_t routes,
                                                                              uint32_t in_features, uint32_t scale_tile_bytes,
                                                                              cudaStream_t stream) {
-    if (!gate_up || !sorted_experts || !expert_offsets || !packed || !scales || routes == 0 || in_features == 0 ||
-        in_features % 16 != 0 || scale_tile_bytes == 0 || (reinterpret_cast<uintptr_t>(gate_up) & 15) != 0)
-        return cudaErrorInvalidValue;
-    const uint64_t units = static_cast<uint64_t>(routes) * (in_features / 8);
-    moe_silu_mul_quantize_kernel<<<static_cast<uint32_t>((units + 255) / 256), 256, 0, stream>>>(
-        gate_up, sorted_experts, expert_offsets, packed, scales, routes, in_features, scale_tile_bytes);
-    return cudaGetLastError();
+    return eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream(
+        gate_up, sorted_experts, expert_offsets, packed, scales, routes, in_features, scale_tile_bytes, nullptr, stream);
 }
 
 static cudaError_t launch_sorted_quant(int mode, const void* input, const void* input2, const float* input_scales,

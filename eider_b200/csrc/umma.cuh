@@ -137,6 +137,11 @@ __device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_s
                  "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                  : "memory");
 }
+// 16 bytes to every GPU bound to the multicast object behind `addr` (an address inside an NVLink multicast mapping);
+// a plain store as far as this thread is concerned: the switch replicates it.
+__device__ __forceinline__ void multimem_store_16(void* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int kPending> __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");

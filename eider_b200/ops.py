@@ -180,6 +180,12 @@ class Fp4TnMatmulPlan:
         check("eider_b200_gemm_plan_set_output_peers",
               self._lib.eider_b200_gemm_plan_set_output_peers(self._plan, arr, len(pointers), ld_out))
 
+    def set_output_multicast(self, address: int) -> None:
+        """Fused all-gather through the switch: `address` = this rank's first output column inside an NVLink multicast
+        mapping of every rank's full output (0 switches it off).  Needs set_output_peers first."""
+        check("eider_b200_gemm_plan_set_output_multicast",
+              self._lib.eider_b200_gemm_plan_set_output_multicast(self._plan, C.c_void_p(int(address)) if address else None))
+
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
             raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
@@ -244,6 +250,12 @@ class Fp8TnMatmulPlan:
         arr = (C.c_void_p * max(1, len(pointers)))(*[C.c_void_p(int(a)) for a in pointers])
         check("eider_b200_gemm_plan_set_output_peers",
               self._lib.eider_b200_gemm_plan_set_output_peers(self._plan, arr, len(pointers), ld_out))
+
+    def set_output_multicast(self, address: int) -> None:
+        """Fused all-gather through the switch: `address` = this rank's first output column inside an NVLink multicast
+        mapping of every rank's full output (0 switches it off).  Needs set_output_peers first."""
+        check("eider_b200_gemm_plan_set_output_multicast",
+              self._lib.eider_b200_gemm_plan_set_output_multicast(self._plan, C.c_void_p(int(address)) if address else None))
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):

@@ -374,6 +374,11 @@ EIDER_B200_API cudaError_t eider_b200_moe_gather_quantize_sorted_routes_nvfp4_bf
 EIDER_B200_API cudaError_t infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream(
     const uint16_t* gate_up, const uint32_t* sorted_experts, const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales,
     uint32_t routes, uint32_t in_features, uint32_t scale_tile_bytes, cudaStream_t stream);
+/* The same with a device-resident row count: rows at or beyond *routes_limit are skipped (`routes` is then the capacity the
+ * launch is sized for).  For buffers whose fill level only the device knows, as in the expert-parallel path below. */
+EIDER_B200_API cudaError_t eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream(
+    const uint16_t* gate_up, const uint32_t* sorted_experts, const uint32_t* expert_offsets, uint8_t* packed, uint8_t* scales,
+    uint32_t routes, uint32_t in_features, uint32_t scale_tile_bytes, const uint32_t* routes_limit, cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:1799 (kernel non_gemm.cu:3066-3110). */
 EIDER_B200_API cudaError_t infer_moe_grouped_pointer_tables_on_stream(const uint32_t* expert_offsets, const uint8_t* packed,
                                                                       const uint8_t* scales, uint16_t* output,
@@ -412,7 +417,117 @@ EIDER_B200_API uint32_t eider_b200_gemm_plan_block_n(void* plan); /* the tile co
  * switches it off. */
 EIDER_B200_API cudaError_t eider_b200_gemm_plan_set_output_peers(void* plan, void* const* peers, uint32_t count,
                                                                  uint32_t ld_out);
+/* Optional on top of set_output_peers: `multicast_block` = the same column block as an address inside an NVLink multicast
+ * mapping that covers every rank's output (CUDA multicast object / symmetric memory's multicast pointer), 16-byte
+ * aligned.  The CTA-pair kernel then writes every output tile once with multimem.st and the switch copies it to all
+ * ranks, so a tile leaves the GPU once instead of once per peer; other kernels and outputs keep using the peer list.
+ * NULL switches it off.  No reference counterpart. */
+EIDER_B200_API cudaError_t eider_b200_gemm_plan_set_output_multicast(void* plan, void* multicast_block);
 EIDER_B200_API cudaError_t eider_b200_gemm_plan_status(void* plan, uint32_t* host_status);
+
+/* ---- meeting of the ranks of one node (no reference counterpart: the reference is single-GPU) --------- */
+
+/* Bounded device-side barrier over peer memory, for the step of the fused all-gather where every rank's columns must have
+ * arrived.  signal_pads[q] = rank q's pad of eider_b200_peer_barrier_pad_bytes() zeroed bytes in memory every rank can
+ * write (symmetric memory / CUDA IPC), `state` = eider_b200_peer_barrier_state_bytes() zeroed bytes of this rank's own
+ * device memory (16 per-channel epochs, then one status word).  All ranks must call with the same channel in the same
+ * order.  The wait gives up after timeout_cycles SM cycles (0 = about one second), records 0xBA000000 | channel << 8 |
+ * missing rank in the status word and returns: nothing spins forever and the context stays usable. */
+EIDER_B200_API size_t eider_b200_peer_barrier_pad_bytes(void);
+EIDER_B200_API size_t eider_b200_peer_barrier_state_bytes(void);
+EIDER_B200_API cudaError_t eider_b200_peer_barrier_on_stream(void* const* signal_pads, uint32_t world, uint32_t rank,
+                                                             uint32_t channel, uint32_t* state, uint64_t timeout_cycles,
+                                                             cudaStream_t stream);
+
+/* ---- host-side weight ingest (no device work; host pointers) ------------------------------------------------- */
+/* Return codes of this group: 0 ok, 1 shape error, 2 format error, 3 I/O error (the reference's Error::Shape /
+ * Error::Format kinds, crates/eider-format/src/lib.rs).
+ *
+ * Nvfp4Artifact, the reference's per-linear disk record, bit-compatible in both directions
+ * (crates/eider-format/src/nvfp4_artifact.rs:12-75: "EIDNVF4\0", version 1, 60-byte little-endian header, prefix, packed
+ * E2M1 bytes [out][in/2], E4M3 K16 scales [out][in/16]); written through a temporary file and a rename. */
+EIDER_B200_API int eider_b200_nvfp4_artifact_write(const char* path, const char* prefix, uint64_t out_features,
+                                                   uint64_t in_features, const uint8_t* packed_weight, uint64_t packed_len,
+                                                   const uint8_t* weight_scale, uint64_t scale_len, float weight_scale_2,
+                                                   float input_scale);
+EIDER_B200_API int eider_b200_nvfp4_artifact_read_header(const char* path, uint64_t* out_features, uint64_t* in_features,
+                                                         uint64_t* packed_len, uint64_t* scale_len, uint64_t* prefix_len,
+                                                         float* weight_scale_2, float* input_scale);
+EIDER_B200_API int eider_b200_nvfp4_artifact_read(const char* path, char* prefix, uint64_t prefix_capacity,
+                                                  uint8_t* packed_weight, uint64_t packed_capacity, uint8_t* weight_scale,
+                                                  uint64_t scale_capacity);
+/* compressed-tensors stores divisors: weight_scale_2 = 1 / weight_global_scale, input_scale = 1 / input_global_scale
+ * (crates/eider-format/src/modelopt.rs:480-519, 1137-1145); non-positive or non-finite divisors are format errors. */
+EIDER_B200_API int eider_b200_compressed_tensors_globals(float weight_global_scale, float input_global_scale,
+                                                         float* weight_scale_2, float* input_scale);
+/* MXFP4 -> NVFP4 scale widening (crates/eider-format/src/modelopt.rs:173-248): `count` E8M0 K32 scales become 2 * count
+ * UE4M3 K16 scales; a NaN code or a power of two UE4M3 cannot hold exactly is a format error. */
+EIDER_B200_API int eider_b200_mxfp4_scales_to_nvfp4(const uint8_t* e8m0_scales, uint64_t count, uint8_t* ue4m3_scales);
+/* GGML NVFP4 blocks (four scales + 32 split-half nibble bytes per 64 values) -> ModelOpt row-major storage, no decoding
+ * (crates/eider-format/src/gguf_nvfp4.rs:12-64). */
+EIDER_B200_API int eider_b200_gguf_nvfp4_unpack(const uint8_t* blocks, uint64_t bytes, uint64_t out_features,
+                                                uint64_t in_features, float global_scale, uint8_t* packed_weight,
+                                                uint8_t* weight_scale);
+/* ModelOptNvfp4Linear::quantize_values and its front ends (crates/eider-format/src/modelopt.rs:524-716), unit global scale.
+ * source_kind 0: f32 values; 1: bf16 bits; 2: FP8 E4M3 bytes times channel_scale[row] (or tensor_scale when NULL);
+ * 3: FP8 E4M3 bytes times 128 x 128 E8M0 block scales. */
+EIDER_B200_API int eider_b200_nvfp4_requantize_host(int source_kind, const void* values, const float* channel_scale,
+                                                    float tensor_scale, const uint8_t* block_scale_e8m0, uint64_t out_features,
+                                                    uint64_t in_features, uint8_t* packed_weight, uint8_t* weight_scale);
+/* modelopt_scales_to_cublaslt on the host (crates/eider-format/src/modelopt.rs:1148-1161). */
+EIDER_B200_API void eider_b200_nvfp4_scales_to_tiled_host(const uint8_t* scales_row_major, uint8_t* scales_tiled,
+                                                          uint64_t out_features, uint64_t in_features);
+/* Prepared-layout cache "EIDB2P01" (48-byte header: magic, version 1, out, in, weight bytes, scale bytes, weight_scale_2;
+ * then the packed bytes as they are and the 128 x 4 tiled scales), the analogue of the reference's EIDW4A01 file
+ * (crates/eider-cuda/src/kernels/sm121_w4a16.rs:18-20, 146-240).  `matches` returns 1 when the file holds the complete
+ * payload for the shape. */
+EIDER_B200_API int eider_b200_prepared_cache_write(const char* path, uint64_t out_features, uint64_t in_features,
+                                                   const uint8_t* packed_weight, const uint8_t* scales_tiled,
+                                                   float weight_scale_2);
+EIDER_B200_API int eider_b200_prepared_cache_matches(const char* path, uint64_t out_features, uint64_t in_features);
+EIDER_B200_API int eider_b200_prepared_cache_read(const char* path, uint64_t out_features, uint64_t in_features,
+                                                  uint8_t* packed_weight, uint8_t* scales_tiled, float* weight_scale_2);
+
+/* ---- expert-parallel routed MoE over peer memory (no reference counterpart) ------------------------------ */
+
+/* Experts are split evenly over `world` ranks of one node, tokens start sharded by rows.  Routes travel by plain peer stores
+ * into receive buffers every rank keeps in peer-writable memory; all counts stay on the device (nothing is read back, the
+ * whole step can be captured in a graph).  Order per step, with a barrier (above) between the numbered groups:
+ *   1. top-k and route sort by global expert on the local tokens, then eider_b200_ep_publish_counts_on_stream;
+ *   2. eider_b200_ep_offsets_on_stream, the activation quantizer on the local tokens (unit global scale), then
+ *      eider_b200_ep_dispatch_rows_on_stream;
+ *   3. eider_b200_ep_expand_experts_on_stream, the grouped GEMMs and the SiLU quantizer (..._limited_...) on the received
+ *      rows with recv_offsets as expert offsets, then eider_b200_ep_return_rows_on_stream;
+ *   4. infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream on the return buffer with the identity route map.
+ * Every pointer table has `world` entries, entry q = rank q's buffer mapped into this process (its own included).
+ * counts_all[q]: uint32 [world][experts].  recv_packed[q]: capacity x in_features / 2 bytes; recv_scales[q]:
+ * (ceil(capacity / 128) + experts / world) scale tiles; recv_origin[q]: uint32 [capacity]; return_rows[q]: bf16
+ * [routes of rank q][out_features].  capacity >= the most rows a rank can receive (all routes of all ranks is always safe);
+ * routes per rank < 2^24; in_features % 32 == 0; out_features % 8 == 0. */
+EIDER_B200_API cudaError_t eider_b200_ep_publish_counts_on_stream(const uint32_t* expert_counts, void* const* counts_all,
+                                                                  uint32_t world, uint32_t rank, uint32_t experts,
+                                                                  cudaStream_t stream);
+/* expert_base[e] = first row of expert e in its owner's receive buffer, before_me[e] = rows of e from lower ranks,
+ * recv_offsets[experts / world + 1] = this rank's expert offsets over what it receives, recv_total[1] = their sum. */
+EIDER_B200_API cudaError_t eider_b200_ep_offsets_on_stream(const uint32_t* counts_all, uint32_t world, uint32_t rank,
+                                                           uint32_t experts, uint32_t* expert_base, uint32_t* before_me,
+                                                           uint32_t* recv_offsets, uint32_t* recv_total, cudaStream_t stream);
+/* source_packed / source_scales: the local tokens quantized once (tiled scales, outer = token); sorted_routes /
+ * sorted_experts / local_offsets: the local route sort by global expert. */
+EIDER_B200_API cudaError_t eider_b200_ep_dispatch_rows_on_stream(
+    const uint8_t* source_packed, const uint8_t* source_scales, const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+    const uint32_t* local_offsets, const uint32_t* expert_base, const uint32_t* before_me, void* const* recv_packed,
+    void* const* recv_scales, void* const* recv_origin, uint32_t routes, uint32_t routes_per_row, uint32_t in_features,
+    uint32_t scale_tile_bytes, uint32_t experts, uint32_t world, uint32_t rank, cudaStream_t stream);
+/* sorted_experts[row] for received rows: the local expert whose range holds the row (experts / world past the total). */
+EIDER_B200_API cudaError_t eider_b200_ep_expand_experts_on_stream(const uint32_t* recv_offsets, uint32_t local_experts,
+                                                                  uint32_t* sorted_experts, uint32_t capacity,
+                                                                  cudaStream_t stream);
+/* rows [capacity][out_features] bf16: row i < *recv_total goes to return_rows[source rank of i] at the route's own index. */
+EIDER_B200_API cudaError_t eider_b200_ep_return_rows_on_stream(const uint16_t* rows, const uint32_t* recv_origin,
+                                                               const uint32_t* recv_total, void* const* return_rows,
+                                                               uint32_t capacity, uint32_t out_features, uint32_t world,
+                                                               cudaStream_t stream);
 
 #ifdef __cplusplus
 }

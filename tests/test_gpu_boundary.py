@@ -93,7 +93,8 @@ def test_quantize_sorted_routes_matches_oracle(lib, oracle, tokens, top, experts
     s = sort_on_device(lib, ind, experts)
     x = rng.standard_normal((tokens if gather else routes, k)).astype(np.float32)
     packed, scales, tile = moe_buffers(routes, experts, k)
-    st = lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(dev(x).data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
+    xd = dev(x)  # (device operands are held in names: a temporary's memory may be handed out again before the launch)
+    st = lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(xd.data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
                                                               s["offsets"].data_ptr(), packed.data_ptr(), scales.data_ptr(), routes, top, k,
                                                               tile, gather, None)
     assert st == 0
@@ -118,7 +119,8 @@ def test_calibrated_quantize_reference_fixture(lib, oracle, relu):
     s = sort_on_device(lib, ind, experts)
     packed, scales, tile = moe_buffers(routes, experts, k)
     src = dev(sorted_bf16, torch.bfloat16) if relu else dev(values)
-    st = lib.infer_moe_calibrated_quantize_on_stream(src.data_ptr(), dev(scales_in).data_ptr(), s["sorted_routes"].data_ptr(),
+    scales_d = dev(scales_in)
+    st = lib.infer_moe_calibrated_quantize_on_stream(src.data_ptr(), scales_d.data_ptr(), s["sorted_routes"].data_ptr(),
                                                      s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(), packed.data_ptr(),
                                                      scales.data_ptr(), routes, top, k, tile, relu, None)
     assert st == 0
@@ -147,12 +149,13 @@ def test_gelu_sorted_routes_matches_staged_quantizer(lib, oracle):
     gate = oracle.bf16_round((rng.standard_normal((routes, k)) * 2).astype(np.float32))
     up = oracle.bf16_round(rng.standard_normal((routes, k)).astype(np.float32))
     fused_p, fused_s, tile = moe_buffers(routes, experts, k)
+    gate_bf, up_bf, gate_f, up_f = dev(gate, torch.bfloat16), dev(up, torch.bfloat16), dev(gate), dev(up)
     st = lib.infer_moe_gelu_tanh_mul_quantize_sorted_routes_nvfp4_on_stream(
-        dev(gate, torch.bfloat16).data_ptr(), dev(up, torch.bfloat16).data_ptr(), s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(),
+        gate_bf.data_ptr(), up_bf.data_ptr(), s["sorted_experts"].data_ptr(), s["offsets"].data_ptr(),
         fused_p.data_ptr(), fused_s.data_ptr(), routes, k, tile, None)
     assert st == 0
     act = torch.empty(routes, k, device="cuda")
-    assert lib.infer_gelu_tanh_mul_f32_on_stream(dev(gate).data_ptr(), dev(up).data_ptr(), act.data_ptr(), routes * k, None) == 0
+    assert lib.infer_gelu_tanh_mul_f32_on_stream(gate_f.data_ptr(), up_f.data_ptr(), act.data_ptr(), routes * k, None) == 0
     staged_p, staged_s, _ = moe_buffers(routes, experts, k)
     assert lib.infer_moe_quantize_sorted_routes_nvfp4_on_stream(act.data_ptr(), s["sorted_routes"].data_ptr(), s["sorted_experts"].data_ptr(),
                                                                 s["offsets"].data_ptr(), staged_p.data_ptr(), staged_s.data_ptr(), routes, 1, k,
@@ -234,8 +237,9 @@ def test_reference_w4a4_gemv_f32(lib, oracle, m, k):
     wd = ops.ModelOptWeight.from_checkpoint(dev(wp), dev(ws), float(g))
     c = torch.zeros(m, device="cuda")
     d = torch.full((m + 8,), -77.0, device="cuda")
+    xpd, xsd = dev(xp), dev(xs)
     assert lib.infer_cutlass_fp4_gemv_f32_supported(m, k) == 1
-    st = lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), dev(xp).data_ptr(), dev(xs).data_ptr(),
+    st = lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), xpd.data_ptr(), xsd.data_ptr(),
                                                   c.data_ptr(), d.data_ptr(), m, k, float(g), None)
     assert st == 0
     torch.cuda.synchronize()
@@ -244,7 +248,7 @@ def test_reference_w4a4_gemv_f32(lib, oracle, m, k):
     assert ok, stats
     assert torch.all(d[m:] == -77.0)  # guard elements behind the output stay untouched
     assert lib.infer_cutlass_fp4_gemv_f32_supported(m, k + 16) == 0
-    assert lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), dev(xp).data_ptr(), dev(xs).data_ptr(),
+    assert lib.infer_cutlass_fp4_gemv_f32_on_stream(wd.packed.data_ptr(), wd.scales_tiled.data_ptr(), xpd.data_ptr(), xsd.data_ptr(),
                                                     None, d.data_ptr(), m, k, float(g), None) == 1
 
 

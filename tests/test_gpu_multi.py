@@ -45,13 +45,21 @@ def _worker(rank, world, port, result):
         plan_fused = ops.Fp4TnMatmulPlan(m, e - b, k)
         lin_fused = parallel.ColumnShardedLinear(n, lambda t: plan_fused.run(ops.quantize_nvfp4_rowscale(t), shard))
         lin_fused.fuse_into(plan_fused, m)
-        for code in (0, 512):  # plain peer stores (tile shape chosen by the plan), then CTA pairs with TMA stores to the peers
+        # plain peer stores (tile shape chosen by the plan), CTA pairs with one multicast store per tile (when the box
+        # offers an NVLink multicast mapping), CTA pairs with one TMA store per peer
+        for code, use_multicast in ((0, False), (512, True), (512, False)):
             if code:
                 plan_fused.set_block_n(code)
+            if not use_multicast:
+                plan_fused.set_output_multicast(0)
+            elif not lin_fused.multicast:
+                continue
             for _ in range(3):  # repeated steps reuse the symmetric buffer
-                y_fused = lin_fused.forward(x)
+                y_fused = lin_fused.forward(x).clone()
             torch.cuda.synchronize()
+            lin_fused.check()
             ok_dense = ok_dense and bool(torch.equal(y_fused, y_ref)) and plan_fused.status() == 0
+            y_fused.zero_()
 
         # ---- MoE: expert parallel vs single GPU
         tokens, experts, top_k, hidden, inter = 64 * world, 8, 2, 256, 128
@@ -89,9 +97,46 @@ def test_two_rank_partitioned_paths():
     ctx = mp.get_context("spawn")
     result = ctx.Manager().dict()
     procs = [ctx.Process(target=_worker, args=(r, world, port, result)) for r in range(world)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=300)
+    finally:
+        for p in procs:  # never leave a worker (and whatever it has on the GPU) behind a failed run
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
+    assert [p.exitcode for p in procs] == [0] * world
     assert dict(result) == {0: (True, True), 1: (True, True)}
+
+
+def test_peer_barrier_gives_up_instead_of_spinning():
+    # one GPU, two pads: "rank 0" waits for a rank 1 that never signals; the wait must run out, leave a status word and
+    # return, and a later barrier that can complete (world of one) must still work on the same context
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import ctypes as C
+
+    from eider_b200 import _lib
+    lib = _lib.load()
+    words = lib.eider_b200_peer_barrier_pad_bytes() // 4
+    pads = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(2)]
+    state = torch.zeros(lib.eider_b200_peer_barrier_state_bytes() // 4, dtype=torch.int32, device="cuda")
+    table = (C.c_void_p * 2)(*[C.c_void_p(p.data_ptr()) for p in pads])
+    assert lib.eider_b200_peer_barrier_on_stream(table, 2, 0, 3, state.data_ptr(), 2_000_000, None) == 0  # ~1 ms budget
+    torch.cuda.synchronize()
+    status = int(state[-1].item()) & 0xFFFFFFFF
+    assert status == (0xBA000000 | (3 << 8) | 1)
+    assert int(pads[1][3 * 8 + 0].item()) == 1 and int(pads[0][3 * 8 + 0].item()) == 1  # rank 0 did announce epoch 1
+    # the peer arrives late (its flag is set by hand): the next epoch of the same channel completes
+    pads[0][3 * 8 + 1] = 2
+    state[-1] = 0
+    assert lib.eider_b200_peer_barrier_on_stream(table, 2, 0, 3, state.data_ptr(), 2_000_000_000, None) == 0
+    torch.cuda.synchronize()
+    assert int(state[-1].item()) == 0 and int(state[3].item()) == 2
+    assert lib.eider_b200_peer_barrier_on_stream(table, 9, 0, 0, state.data_ptr(), 0, None) == 1
+    assert lib.eider_b200_peer_barrier_on_stream(table, 2, 0, 16, state.data_ptr(), 0, None) == 1

@@ -158,7 +158,8 @@ def test_fused_head_unpack_quantize_equals_staged_and_oracle(lib, oracle, tokens
     name = f"infer_unpack_heads_quantize_nvfp4_col_major_{dtype}_on_stream"
     assert getattr(lib, name)(src.data_ptr(), fused[0].data_ptr(), fused[1].data_ptr(), tokens, heads, head_dim, offset, 0.375, None) == 0
     unpacked = torch.zeros(rows, features, device="cuda")
-    assert lib.infer_unpack_heads_f32_on_stream(dev(head_major).data_ptr(), unpacked.data_ptr(), tokens, heads, head_dim, offset, None) == 0
+    src_f32 = dev(head_major)
+    assert lib.infer_unpack_heads_f32_on_stream(src_f32.data_ptr(), unpacked.data_ptr(), tokens, heads, head_dim, offset, None) == 0
     staged = staged_quantize(lib, unpacked, rows, features, 0.375)
     assert same_bytes(fused, staged)
     full = np.zeros((rows, features), np.float32)
@@ -222,11 +223,12 @@ def test_vector_simple_scales_matches_oracle(lib, oracle, rows):
     blocks = (rows + 15) // 16
     p = torch.zeros((rows + 1) // 2, dtype=torch.uint8, device="cuda")
     s = torch.zeros(blocks, dtype=torch.uint8, device="cuda")
-    assert lib.infer_quantize_nvfp4_vector_simple_scales_f32_on_stream(dev(x).data_ptr(), p.data_ptr(), s.data_ptr(), rows, 0.25, None) == 0
+    xd = dev(x)
+    assert lib.infer_quantize_nvfp4_vector_simple_scales_f32_on_stream(xd.data_ptr(), p.data_ptr(), s.data_ptr(), rows, 0.25, None) == 0
     torch.cuda.synchronize()
     p_ref, s_ref = oracle.quantize_nvfp4_vector_simple_scales(x, 0.25)
     assert np.array_equal(p.cpu().numpy(), p_ref) and np.array_equal(s.cpu().numpy(), s_ref)
-    assert lib.infer_quantize_nvfp4_vector_simple_scales_f32_on_stream(dev(x).data_ptr(), p.data_ptr(), s.data_ptr(), rows, 0.0, None) == 1
+    assert lib.infer_quantize_nvfp4_vector_simple_scales_f32_on_stream(xd.data_ptr(), p.data_ptr(), s.data_ptr(), rows, 0.0, None) == 1
 
 
 def test_scale_channel_in_place(lib):
