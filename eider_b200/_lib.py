@@ -120,6 +120,21 @@ SIGNATURES = {
     "eider_b200_prepared_cache_write": (_I, [_S, _U64, _U64, _P, _P, _F]),
     "eider_b200_prepared_cache_matches": (_I, [_S, _U64, _U64]),
     "eider_b200_prepared_cache_read": (_I, [_S, _U64, _U64, _P, _P, _P]),
+    "infer_nvfp4_w4a16_grouped_matvec_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
+    "infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
+    "infer_cutlass_fp4_grouped_gemv_f32_supported": (_I, [_U32, _U32, _U32]),
+    "infer_cutlass_fp4_grouped_gemv_f32_create": (_P, [_U32, _U32, _U32]),
+    "infer_cutlass_fp4_grouped_gemv_f32_destroy": (None, [_P]),
+    "infer_cutlass_fp4_grouped_gemv_f32_indexed_a_on_stream": (_I, [_P, _P, _P, _P, _U32, _P, _P, _P, _F, _P]),
+    "infer_cutlass_fp4_grouped_gemv_f32_indexed_a_tiled_scales_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _P, _P, _P, _P, _P]),
+    "infer_cutlass_fp4_grouped_gemv_f32_contiguous_b_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _F, _P]),
+    "infer_moe_silu_slots_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_moe_silu_quantize_slots_nvfp4_simple_scales_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_moe_weighted_accumulate_slots_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_moe_weighted_accumulate_slots_f32_batch_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_qwen36_ffn_finalize_routed_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P]),
+    "infer_qwen36_ffn_finalize_routed_batch_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_nvfp4_w4a16_top1_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _P, _P, _U32, _U32, _F, _U32, _P]),
     "eider_b200_peer_barrier_on_stream": (_I, [_P, _U32, _U32, _U32, _P, C.c_uint64, _P]),
 }
 

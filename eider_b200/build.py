@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "lib", "libeider_b200.so")
-SOURCES = ["quantize.cu", "producers.cu", "gemv_simt.cu", "gemm_umma.cu", "moe.cu", "peer.cu", "ingest.cu"]
+SOURCES = ["quantize.cu", "producers.cu", "gemv_simt.cu", "gemm_umma.cu", "moe.cu", "peer.cu", "ingest.cu", "decode_moe.cu"]
 
 
 def _sources():

@@ -439,6 +439,76 @@ EIDER_B200_API cudaError_t eider_b200_peer_barrier_on_stream(void* const* signal
                                                              uint32_t channel, uint32_t* state, uint64_t timeout_cycles,
                                                              cudaStream_t stream);
 
+/* ---- decode-side routed MoE and lm-head arg-max (CUDA cores, device pointer tables) ----------------------------- */
+
+/* crates/eider-cuda/src/ffi.rs:3320 and :3348 (kernels non_gemm.cu:13316-13397): slot g multiplies the weights of expert
+ * indices[g] (table entries: packed [out][in/2], row-major scales [out][in/16], weight_scale_2) with the shared f32 input
+ * (or with input_table[g]) and writes output_table[g][out].  Slots whose expert is >= table_len are skipped, as in the
+ * reference.  This implementation needs in_features % 32 == 0 and 16-byte aligned weight rows. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_grouped_matvec_f32_on_stream(
+    const uint32_t* indices, const float* input, const uint8_t* const* packed_weight_table, const uint8_t* const* weight_scale_table,
+    const float* weight_scale_2_table, float* const* output_table, uint32_t table_len, uint32_t groups, uint32_t out_features,
+    uint32_t in_features, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream(
+    const uint32_t* indices, const float* const* input_table, const uint8_t* const* packed_weight_table,
+    const uint8_t* const* weight_scale_table, const float* weight_scale_2_table, float* const* output_table, uint32_t table_len,
+    uint32_t groups, uint32_t out_features, uint32_t in_features, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:589-642 (crates/eider-cuda/native/cutlass_gemv.cu:277-880): grouped W4A4 GEMV with F32 output;
+ * a = expert weights with tiled scales (found through tables), b = one NVFP4 activation row with tiled scales (outer = 0).
+ * indexed_a: d[g] = alpha * A[indices[g]] . b; ..._tiled_scales: per-expert alpha_table, c is not read (beta 0);
+ * contiguous_b: group g uses table entry g and writes d + g * m.  The plan records the shape only. */
+EIDER_B200_API int infer_cutlass_fp4_grouped_gemv_f32_supported(uint32_t m, uint32_t k, uint32_t groups);
+EIDER_B200_API void* infer_cutlass_fp4_grouped_gemv_f32_create(uint32_t m, uint32_t k, uint32_t groups);
+EIDER_B200_API void infer_cutlass_fp4_grouped_gemv_f32_destroy(void* plan);
+EIDER_B200_API cudaError_t infer_cutlass_fp4_grouped_gemv_f32_indexed_a_on_stream(
+    void* plan, const uint32_t* indices, const uint8_t* const* a_values_table, const uint8_t* const* a_scales_table, uint32_t table_len,
+    const uint8_t* b_values, const uint8_t* b_scales, float* const* d, float alpha, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_cutlass_fp4_grouped_gemv_f32_indexed_a_tiled_scales_on_stream(
+    void* plan, const uint32_t* indices, const uint8_t* const* a_values_table, const uint8_t* const* a_scales_table,
+    const float* alpha_table, uint32_t table_len, const uint8_t* b_values, const uint8_t* b_scales, const float* c, float* const* d,
+    cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_cutlass_fp4_grouped_gemv_f32_contiguous_b_on_stream(
+    void* plan, const uint8_t* const* a_values_table, const uint8_t* const* a_scales_table, const uint8_t* b_values,
+    const uint8_t* b_scales, float* d, float alpha, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1887 and kernel non_gemm.cu:3558-3593: per slot, g = gate * alpha[expert], u = up * alpha[expert],
+ * value = g * sigmoid(g) * u; f32 out, or value / input_scale[expert] -> NVFP4 with one scale byte per 16 values in plain
+ * order (a slot whose input scale is not positive and finite is left untouched, as in the reference). */
+EIDER_B200_API cudaError_t infer_moe_silu_slots_f32_on_stream(const uint32_t* indices, const float* const* gate_up_table,
+                                                              float* const* output_table, const float* gate_up_alpha_table,
+                                                              uint32_t rows, uint32_t groups, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_moe_silu_quantize_slots_nvfp4_simple_scales_on_stream(
+    const uint32_t* indices, const float* const* gate_up_table, uint8_t* const* packed_table, uint8_t* const* scales_table,
+    const float* input_scale_table, const float* gate_up_alpha_table, uint32_t rows, uint32_t groups, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:1898 and :1908 (kernels non_gemm.cu:3595-3639): output[row][c] = sum over the row's slots of
+ * inputs[route][c] * route_weights[route] * alpha_table[indices[route]], slot order. */
+EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_slots_f32_on_stream(const uint32_t* indices, const float* route_weights,
+                                                                             const float* const* inputs, const float* alpha_table,
+                                                                             float* output, uint32_t len, uint32_t groups,
+                                                                             cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_slots_f32_batch_on_stream(const uint32_t* indices, const float* route_weights,
+                                                                                   const float* const* inputs, const float* alpha_table,
+                                                                                   float* output, uint32_t rows, uint32_t len,
+                                                                                   uint32_t groups, cudaStream_t stream);
+/* Kernels non_gemm.cu:3823-3875: the same sum + shared_output * sigmoid(shared_gate_logit[row]) + residual, rounded to bf16
+ * precision (the value stays f32). */
+EIDER_B200_API cudaError_t infer_qwen36_ffn_finalize_routed_f32_on_stream(
+    const uint32_t* indices, const float* route_weights, const float* const* routed_outputs, const float* alpha_table,
+    const float* shared_gate_logit, const float* shared_output, const float* residual, float* output, uint32_t len, uint32_t groups,
+    cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_qwen36_ffn_finalize_routed_batch_f32_on_stream(
+    const uint32_t* indices, const float* route_weights, const float* const* routed_outputs, const float* alpha_table,
+    const float* shared_gate_logit, const float* shared_output, const float* residual, float* output, uint32_t rows, uint32_t cols,
+    uint32_t groups_per_row, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3473 (kernels non_gemm.cu:13423-13482, 8287-8328): arg-max of weight_scale_2 * W . x over the
+ * output features without materialising the logits; ties go to the lower row.  scratch_value / scratch_index: scratch_len
+ * entries each (any scratch_len >= 1; up to 1024 are used).  warps_per_block must be 4, 8, 16 or 32 as in the reference and
+ * has no other meaning here; in_features % 32 == 0. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_top1_f32_on_stream(const float* input, const uint8_t* packed_weight,
+                                                                const uint8_t* weight_scale, float* scratch_value,
+                                                                uint32_t* scratch_index, uint32_t scratch_len, uint32_t* out_index,
+                                                                float* out_value, uint32_t out_features, uint32_t in_features,
+                                                                float weight_scale_2, uint32_t warps_per_block, cudaStream_t stream);
+
 /* ---- host-side weight ingest (no device work; host pointers) ------------------------------------------------- */
 /* Return codes of this group: 0 ok, 1 shape error, 2 format error, 3 I/O error (the reference's Error::Shape /
  * Error::Format kinds, crates/eider-format/src/lib.rs).
