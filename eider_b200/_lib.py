@@ -95,6 +95,7 @@ SIGNATURES = {
     "eider_b200_nvfp4_grouped_gemm_destroy": (None, [_P]),
     "eider_b200_nvfp4_grouped_gemm_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _P]),
     "eider_b200_grouped_plan_status": (_I, [_P, _P]),
+    "eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _P, _P, _U32, _P]),
     "infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "eider_b200_gemm_plan_set_block_n": (_I, [_P, _U32]),
     "eider_b200_gemm_plan_block_n": (_U32, [_P]),

@@ -447,8 +447,9 @@ cudaError_t run_decode(DecodePlan& plan, uint32_t terms, const uint8_t* x_values
 
 cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
                         const uint8_t* w_scales, uint16_t* output, const float* alpha, const uint32_t* expert_offsets,
-                        uint32_t total_routes, cudaStream_t stream) {
-    if (!a_values || !a_scales || !w_values || !w_scales || !output || !alpha || !expert_offsets || total_routes == 0)
+                        uint32_t total_routes, cudaStream_t stream, uint8_t* act_packed = nullptr, uint8_t* act_scales = nullptr,
+                        uint32_t act_tile_bytes = 0) {
+    if (!a_values || !a_scales || !w_values || !w_scales || (!output && !act_packed) || !alpha || !expert_offsets || total_routes == 0)
         return cudaErrorInvalidValue;
     const uint32_t k_bytes = plan.k / 2;
     const CUtensorMap *map_rows_p, *map_cols_p;
@@ -480,6 +481,9 @@ cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_
     p.group_cols = plan.m;
     p.group_alpha = alpha;
     p.status = plan.status;
+    p.act_packed = act_packed;
+    p.act_scales = act_scales;
+    p.act_tile_bytes = act_tile_bytes;
     // upper bound on work items: every expert may add one partial row tile
     const uint32_t max_row_tiles = (total_routes + kTileRows - 1) / kTileRows + plan.groups;
     if (plan.m % 256 == 0) {
@@ -1071,6 +1075,22 @@ cudaError_t eider_b200_nvfp4_grouped_gemm_on_stream(void* raw, const uint8_t* a_
     auto* plan = static_cast<GroupedPlan*>(raw);
     if (!plan) return cudaErrorInvalidValue;
     return run_grouped(*plan, a_values, a_scales, w_values, w_scales_tiled, output, alpha, expert_offsets, total_routes, stream);
+}
+
+cudaError_t eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream(void* raw, const uint8_t* a_values, const uint8_t* a_scales,
+                                                                  const uint8_t* w_values_interleaved,
+                                                                  const uint8_t* w_scales_tiled_interleaved, const float* alpha,
+                                                                  const uint32_t* expert_offsets, uint32_t total_routes,
+                                                                  uint8_t* packed, uint8_t* scales, uint32_t scale_tile_bytes,
+                                                                  cudaStream_t stream) {
+    auto* plan = static_cast<GroupedPlan*>(raw);
+    // m = 2 * intermediate: 32 interleaved weight rows give one 16-feature block, and the 16-byte packed stores of two blocks
+    // need whole 64-column steps
+    if (!plan || !packed || !scales || scale_tile_bytes == 0 || plan->m % 128 != 0 || (reinterpret_cast<uintptr_t>(packed) & 15) != 0 ||
+        (plan->m / 4) % 16 != 0 || (reinterpret_cast<uintptr_t>(scales) & 1) != 0)
+        return cudaErrorInvalidValue;
+    return run_grouped(*plan, a_values, a_scales, w_values_interleaved, w_scales_tiled_interleaved, nullptr, alpha, expert_offsets,
+                       total_routes, stream, packed, scales, scale_tile_bytes);
 }
 
 cudaError_t eider_b200_grouped_plan_status(void* raw, uint32_t* host_status) {

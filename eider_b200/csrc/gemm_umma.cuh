@@ -74,6 +74,14 @@ struct Params {
     // (this rank's included).  When set, the CTA-pair kernel writes each staged tile ONCE with multimem.st and the switch
     // replicates it, so a tile leaves this GPU once instead of once per peer.  Stores only.
     void* out_multicast;
+    // Grouped GEMM with the SiLU(gate) * up -> NVFP4 quantizer in its epilogue (the down projection's input, without the
+    // bf16 round trip): when act_packed is set, the weight rows of every group are interleaved [16 gate rows, 16 up rows]
+    // so that 32 consecutive accumulator columns are one 16-feature block of both halves; the epilogue rounds them to bf16
+    // (what the unfused GEMM stores), applies SiLU * up and writes packed codes [route][group_cols / 4] and the scale bytes
+    // into the group's 128-row scale tiles.  `out` is not written.
+    uint8_t* act_packed;
+    uint8_t* act_scales;
+    uint32_t act_tile_bytes;
 };
 
 // Calls f(base) for every output buffer of the launch.
@@ -132,6 +140,7 @@ struct TileCoord {
     uint32_t k_stage0, k_stage1;  // stage range handled by this work item
     uint32_t split;
     uint32_t row_tile;    // index used for split-K bookkeeping
+    uint32_t group_row0;  // grouped: first row of the tile's group
 };
 
 // Grouped schedule: work items are (128-row tile of a group) x column tiles.  Each CTA walks the group
@@ -166,6 +175,7 @@ __device__ __forceinline__ bool get_tile(const Params& p, uint32_t item, GroupWa
         uint32_t g0 = p.group_offsets[group], g1 = p.group_offsets[group + 1];
         t.row0 = g0 + tile_in_group * kTileRows;
         t.row_end = g1;
+        t.group_row0 = g0;
         t.col0 = group * p.group_cols + col_tile * BLOCK_N;
         t.out_col0 = col_tile * BLOCK_N;
         t.group = group;
@@ -251,6 +261,34 @@ __device__ __forceinline__ void store_row64_all(const Params& p, size_t offset, 
     uint32_t w[32];
     convert_bf16x64_scaled(raw, scale, col_scale, w);
     for_each_out(p, [&](void* base) { store_bf16x64(static_cast<uint16_t*>(base) + offset, w); });
+}
+
+// Fused SiLU * up -> NVFP4 epilogue of the grouped gate/up GEMM: 64 accumulator columns of one row = two 16-feature blocks,
+// each as [16 gate, 16 up].  Same operations, in the same order, as the stand-alone kernel on the bf16 GEMM output
+// (crates/eider-cuda/native/non_gemm.cu:2835-2875), so both paths give the same bytes.
+__device__ __forceinline__ void silu_quantize_store64(const Params& p, const TileCoord& t, uint32_t row, uint32_t c, const uint32_t* raw,
+                                                      float rs) {
+    const uint32_t features = p.group_cols / 2;     // the activation's row length (intermediate size)
+    const uint32_t kb0 = (t.out_col0 + c) / 32;      // first of the two blocks
+    uint32_t words[4];
+    uint32_t scale_pair = 0;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float g = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(raw[32 * b + i]) * rs));
+            const float u = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(raw[32 * b + 16 + i]) * rs));
+            v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+        }
+        uint2 bytes;
+        scale_pair |= static_cast<uint32_t>(quantize_block16(v, 16, &bytes)) << (8 * b);
+        words[2 * b] = bytes.x;
+        words[2 * b + 1] = bytes.y;
+    }
+    *reinterpret_cast<uint4*>(p.act_packed + static_cast<size_t>(row) * (features / 2) + kb0 * 8) = make_uint4(words[0], words[1], words[2], words[3]);
+    const size_t base = ((static_cast<size_t>(t.group_row0) + 127) / 128 + t.group) * p.act_tile_bytes;
+    *reinterpret_cast<uint16_t*>(p.act_scales + base + tiled_scale_offset(row - t.group_row0, kb0, features)) = static_cast<uint16_t>(scale_pair);
 }
 
 // KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
@@ -487,6 +525,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
                 wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
                        t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+                if (GROUPED && p.act_packed) wide = true;  // (the host only sets it for whole tiles)
             }
             if constexpr (kWide) if (wide) {
                 constexpr uint32_t kSteps = BLOCK_N / 64;
@@ -509,9 +548,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
                     }
-                    if (row_ok)
-                        store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs,
-                                        p.col_scale ? p.col_scale + (GROUPED ? t.group * p.group_cols : 0) + t.out_col0 + col_of(step) : nullptr);
+                    if (row_ok) {
+                        if (GROUPED && p.act_packed)
+                            silu_quantize_store64(p, t, row, col_of(step), &raw[step & 1][0], rs);
+                        else
+                            store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs,
+                                            p.col_scale ? p.col_scale + (GROUPED ? t.group * p.group_cols : 0) + t.out_col0 + col_of(step) : nullptr);
+                    }
                 }
                 if (!T::kOverlap) {
                     umma::tmem_load_wait();

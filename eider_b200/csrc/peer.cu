@@ -184,7 +184,16 @@ __global__ void __launch_bounds__(kDispatchWarps * 32) ep_return_rows_kernel(con
     const uint32_t src_rank = o >> 24, route = o & 0xffffffu;
     const uint4* s4 = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(row) * n);
     uint4* d4 = reinterpret_cast<uint4*>(ret.p[src_rank] + static_cast<size_t>(route) * n * 2);
-    for (uint32_t i = lane; i < n / 8; i += 32) d4[i] = __ldg(s4 + i);
+    // four loads in flight per lane before the first store: the row leaves as whole 512-byte runs per warp instruction
+    uint32_t i = lane;
+    for (; i + 96 < n / 8; i += 128) {
+        const uint4 a = __ldg(s4 + i), b = __ldg(s4 + i + 32), c = __ldg(s4 + i + 64), d = __ldg(s4 + i + 96);
+        d4[i] = a;
+        d4[i + 32] = b;
+        d4[i + 64] = c;
+        d4[i + 96] = d;
+    }
+    for (; i < n / 8; i += 32) d4[i] = __ldg(s4 + i);
 }
 
 }  // namespace

@@ -658,6 +658,20 @@ class GroupedNvfp4Weights:
         return GroupedNvfp4Weights(packed, scales_row_major, flat.scales_tiled, weight_scale_2.to(torch.float32).contiguous(),
                                    e, n, kh * 2)
 
+    def interleave_gate_up(self) -> "GroupedNvfp4Weights":
+        """The same gate/up weights with the rows of every expert reordered as [16 gate rows, 16 up rows] per 16 features:
+        the order the grouped GEMM with the fused SiLU * up quantizer wants (32 consecutive output columns = one
+        16-feature block of both halves).  Done once at load."""
+        n = self.out_features
+        half = n // 2
+        if n % 32 != 0:
+            raise ShapeError("gate/up rows must come in multiples of 32")
+        blocks = torch.arange(half // 16, device=self.packed.device).repeat_interleave(32) * 16
+        within = torch.arange(32, device=self.packed.device).repeat(half // 16)
+        order = torch.where(within < 16, blocks + within, half + blocks + within - 16)
+        return GroupedNvfp4Weights.from_checkpoint(self.packed.index_select(1, order).contiguous(),
+                                                   self.scales_row_major.index_select(1, order).contiguous(), self.alpha)
+
     @staticmethod
     def quantize(weights: torch.Tensor) -> "GroupedNvfp4Weights":
         """[E, N, K] f32/bf16 -> per-expert ModelOpt quantization (own global scale per expert)."""
@@ -697,6 +711,20 @@ class Fp4GroupedGemmPlan:
                                                                 w.packed.data_ptr(), w.scales_tiled.data_ptr(), out.data_ptr(),
                                                                 w.alpha.data_ptr(), routes.expert_offsets.data_ptr(),
                                                                 rows.routes, _stream()))
+        return out
+
+    def run_silu_quantize(self, rows: MoeSortedNvfp4Rows, w_interleaved: GroupedNvfp4Weights, routes: MoeSortedRoutes,
+                          out: MoeSortedNvfp4Rows) -> MoeSortedNvfp4Rows:
+        """Gate/up GEMM with SiLU(gate) * up -> NVFP4 in the epilogue: fills `out` (the down projection's input) without
+        materialising the bf16 gate/up rows.  `w_interleaved` = GroupedNvfp4Weights.interleave_gate_up()."""
+        if (rows.k != self.k or w_interleaved.in_features != self.k or w_interleaved.out_features != self.m or
+                w_interleaved.experts != self.groups or out.k * 2 != self.m or out.routes != rows.routes):
+            raise ShapeError("operand shapes do not match the plan")
+        check("eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream",
+              self._lib.eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream(
+                  self._plan, rows.packed.data_ptr(), rows.scales.data_ptr(), w_interleaved.packed.data_ptr(),
+                  w_interleaved.scales_tiled.data_ptr(), w_interleaved.alpha.data_ptr(), routes.expert_offsets.data_ptr(), rows.routes,
+                  out.packed.data_ptr(), out.scales.data_ptr(), out.tile_bytes, _stream()))
         return out
 
     def status(self) -> int:
@@ -749,12 +777,18 @@ class GroupedMoe:
         self.out = torch.empty(tokens, hidden, dtype=torch.float32, device=device)
 
     def run(self, x: torch.Tensor, router_logits: torch.Tensor, w_gate_up: GroupedNvfp4Weights, w_down: GroupedNvfp4Weights,
-            norm_topk_prob: bool = True) -> torch.Tensor:
+            norm_topk_prob: bool = True, w_gate_up_interleaved: GroupedNvfp4Weights | None = None) -> torch.Tensor:
+        """With `w_gate_up_interleaved` (GroupedNvfp4Weights.interleave_gate_up(), made once at load) the SiLU * up
+        quantizer runs in the gate/up GEMM's epilogue and the bf16 gate/up rows never reach HBM; the bytes of the down
+        projection's input are the same either way."""
         idx, weights = moe_topk(router_logits, self.top_k, norm_topk_prob)
         self.routes.sort(idx.reshape(-1))
         self.gate_up_in.gather_quantize(x, self.routes, self.top_k)
-        self.gate_up_plan.run(self.gate_up_in, w_gate_up, self.routes, out=self.gate_up_out)
-        self.down_in.silu_mul_halves_quantize(self.gate_up_out, self.routes)
+        if w_gate_up_interleaved is not None:
+            self.gate_up_plan.run_silu_quantize(self.gate_up_in, w_gate_up_interleaved, self.routes, self.down_in)
+        else:
+            self.gate_up_plan.run(self.gate_up_in, w_gate_up, self.routes, out=self.gate_up_out)
+            self.down_in.silu_mul_halves_quantize(self.gate_up_out, self.routes)
         self.down_plan.run(self.down_in, w_down, self.routes, out=self.down_out)
         self.route_weights = weights
         self.route_indices = idx

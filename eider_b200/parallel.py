@@ -302,6 +302,7 @@ class PeerExpertParallelMoe:
         self.routes_local = tokens_local * top_k
         self.capacity = capacity if capacity is not None else self.routes_local * world  # all routes of all ranks always fit
         self.w_gate_up, self.w_down = w_gate_up, w_down
+        self.w_gate_up_interleaved = w_gate_up.interleave_gate_up()  # SiLU * up quantizer in the gate/up GEMM's epilogue
         alloc = alloc or (lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=device))
         tile_h, tile_i = ops.moe_scale_tile_bytes(hidden), ops.moe_scale_tile_bytes(intermediate)
         self.tile_h, self.tile_i = tile_h, tile_i
@@ -331,6 +332,7 @@ class PeerExpertParallelMoe:
         self.weights = torch.zeros(tokens_local, top_k, dtype=torch.float32, device=device)
         self.out = torch.empty(tokens_local, hidden, dtype=torch.float32, device=device)
         self._tables = None
+        self.fuse_silu = True
 
     def connect(self, peer_pointers: dict) -> None:
         """peer_pointers[name] = list of `world` device addresses, entry q = rank q's buffer `name` as this process sees it."""
@@ -371,12 +373,19 @@ class PeerExpertParallelMoe:
         lib = self._lib
         cap = self.capacity
         self._call("eider_b200_ep_expand_experts_on_stream", self.recv_offsets.data_ptr(), self.per, self.recv_experts.data_ptr(), cap)
-        self._call("eider_b200_nvfp4_grouped_gemm_on_stream", self.gate_up_plan._plan, self.buffers["recv_packed"].data_ptr(),
-                   self.buffers["recv_scales"].data_ptr(), self.w_gate_up.packed.data_ptr(), self.w_gate_up.scales_tiled.data_ptr(),
-                   self.gate_up_out.data_ptr(), self.w_gate_up.alpha.data_ptr(), self.recv_offsets.data_ptr(), cap)
-        self._call("eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream", self.gate_up_out.data_ptr(),
-                   self.recv_experts.data_ptr(), self.recv_offsets.data_ptr(), self.down_in_packed.data_ptr(),
-                   self.down_in_scales.data_ptr(), cap, self.inter, self.tile_i, self.recv_total.data_ptr())
+        if self.fuse_silu:
+            wi = self.w_gate_up_interleaved
+            self._call("eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream", self.gate_up_plan._plan,
+                       self.buffers["recv_packed"].data_ptr(), self.buffers["recv_scales"].data_ptr(), wi.packed.data_ptr(),
+                       wi.scales_tiled.data_ptr(), wi.alpha.data_ptr(), self.recv_offsets.data_ptr(), cap,
+                       self.down_in_packed.data_ptr(), self.down_in_scales.data_ptr(), self.tile_i)
+        else:
+            self._call("eider_b200_nvfp4_grouped_gemm_on_stream", self.gate_up_plan._plan, self.buffers["recv_packed"].data_ptr(),
+                       self.buffers["recv_scales"].data_ptr(), self.w_gate_up.packed.data_ptr(), self.w_gate_up.scales_tiled.data_ptr(),
+                       self.gate_up_out.data_ptr(), self.w_gate_up.alpha.data_ptr(), self.recv_offsets.data_ptr(), cap)
+            self._call("eider_b200_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_limited_on_stream", self.gate_up_out.data_ptr(),
+                       self.recv_experts.data_ptr(), self.recv_offsets.data_ptr(), self.down_in_packed.data_ptr(),
+                       self.down_in_scales.data_ptr(), cap, self.inter, self.tile_i, self.recv_total.data_ptr())
         self._call("eider_b200_nvfp4_grouped_gemm_on_stream", self.down_plan._plan, self.down_in_packed.data_ptr(),
                    self.down_in_scales.data_ptr(), self.w_down.packed.data_ptr(), self.w_down.scales_tiled.data_ptr(),
                    self.down_out.data_ptr(), self.w_down.alpha.data_ptr(), self.recv_offsets.data_ptr(), cap)

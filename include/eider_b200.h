@@ -398,6 +398,16 @@ EIDER_B200_API cudaError_t eider_b200_nvfp4_grouped_gemm_on_stream(void* plan, c
                                                                    const uint8_t* w_scales_tiled, uint16_t* output,
                                                                    const float* alpha, const uint32_t* expert_offsets,
                                                                    uint32_t total_routes, cudaStream_t stream);
+/* The gate/up grouped GEMM with SiLU(gate) * up -> NVFP4 in its epilogue: what infer_cutlass_fp4_grouped_gemm_on_stream
+ * followed by infer_moe_silu_mul_halves_quantize_sorted_routes_nvfp4_on_stream compute, byte for byte, without the bf16
+ * [route][2 * intermediate] round trip through HBM.  The plan's m is 2 * intermediate; the weight rows of every expert must
+ * be interleaved as [16 gate rows, 16 up rows] per 16 features (and the scales tiled over that order).  packed
+ * [route][intermediate / 2] (16-byte aligned, intermediate % 32 == 0) and scales (per-expert 128-row tiles of
+ * scale_tile_bytes) are the down projection's input. */
+EIDER_B200_API cudaError_t eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream(
+    void* plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values_interleaved,
+    const uint8_t* w_scales_tiled_interleaved, const float* alpha, const uint32_t* expert_offsets, uint32_t total_routes,
+    uint8_t* packed, uint8_t* scales, uint32_t scale_tile_bytes, cudaStream_t stream);
 EIDER_B200_API cudaError_t eider_b200_grouped_plan_status(void* plan, uint32_t* host_status);
 /* crates/eider-cuda/src/ffi.rs:1931 (kernel non_gemm.cu:3735-3780): un-permute + weighted sum, f32 [rows][len]. */
 EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream(

@@ -201,3 +201,39 @@ def test_pipeline_ragged_experts(ops, oracle):
 
 def test_pipeline_medium(ops, oracle):
     _pipeline(ops, oracle, tokens=512, experts=16, top_k=4, hidden=1024, inter=384, seed=3)
+
+
+@pytest.mark.parametrize("tokens,experts,top_k,hidden,inter", [(96, 8, 2, 256, 128), (20, 16, 3, 512, 128), (512, 16, 4, 1024, 384),
+                                                               (2048, 128, 8, 2048, 768)])
+def test_fused_silu_epilogue_equals_staged_pipeline(ops, tokens, experts, top_k, hidden, inter):
+    # the gate/up grouped GEMM with SiLU * up -> NVFP4 in its epilogue against the GEMM + stand-alone quantizer: the down
+    # projection's input must be the same bytes (ragged and empty experts included), hence the same layer output
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(tokens + experts)
+    x = torch.randn(tokens, hidden, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts, device="cuda", generator=g)
+    w_gu = ops.GroupedNvfp4Weights.quantize(torch.randn(experts, 2 * inter, hidden, device="cuda", generator=g) * 0.02)
+    w_dn = ops.GroupedNvfp4Weights.quantize(torch.randn(experts, hidden, inter, device="cuda", generator=g) * 0.02)
+    staged = ops.GroupedMoe(tokens, experts, top_k, hidden, inter)
+    ref = staged.run(x, logits, w_gu, w_dn).clone()
+    fused = ops.GroupedMoe(tokens, experts, top_k, hidden, inter)
+    out = fused.run(x, logits, w_gu, w_dn, w_gate_up_interleaved=w_gu.interleave_gate_up())
+    torch.cuda.synchronize()
+    assert fused.gate_up_plan.status() == 0 and fused.down_plan.status() == 0
+    assert torch.equal(fused.down_in.packed, staged.down_in.packed)
+    # scale bytes: compare what belongs to routes (padding rows of the per-expert tiles are never written by either path)
+    offsets = staged.routes.expert_offsets.cpu().numpy().view(np.uint32)
+    fs, ss = fused.down_in.scales.cpu().numpy(), staged.down_in.scales.cpu().numpy()
+    tile = staged.down_in.tile_bytes
+    blocks = inter // 16
+    for e in range(experts):
+        n = int(offsets[e + 1] - offsets[e])
+        if n == 0:
+            continue
+        base = ((int(offsets[e]) + 127) // 128 + e) * tile
+        rows_ = np.arange(n)[:, None]
+        kb = np.arange(blocks)[None, :]
+        padded = (blocks + 3) // 4 * 4
+        off = base + ((kb // 4) * 4 + (rows_ // 128) * padded) * 128 + (rows_ % 32) * 16 + ((rows_ % 128) // 32) * 4 + kb % 4
+        assert np.array_equal(fs[off], ss[off]), e
+    assert torch.equal(out, ref)
