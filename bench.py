@@ -415,13 +415,18 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="prefill only: M instead of 512 (the larger-chunk configs)")
     ap.add_argument("--no-multicast", action="store_true", help="N > 1: one store per peer instead of one multimem.st per tile")
     ap.add_argument("--no-extra", action="store_true", help="skip the short decode / larger-chunk measurements of the default line")
+    ap.add_argument("--in-features", type=int, default=0, help="prefill only: K instead of 5120 (13824 with --out-features 5120 = the down projection)")
+    ap.add_argument("--out-features", type=int, default=0, help="prefill only: N instead of 27648")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.tokens:
-        global M, WORKLOAD, FLOPS_PER_STEP
-        M = args.tokens
+    if args.tokens or args.in_features or args.out_features:
+        global M, K, N, WORKLOAD, FLOPS_PER_STEP, NCU_DRAM_BYTES_FULL_LAUNCH
+        M = args.tokens or M
+        K = args.in_features or K
+        N = args.out_features or N
         WORKLOAD = f"nvfp4_w4a4_prefill_gemm_M{M}_K{K}_N{N}"
         FLOPS_PER_STEP = 2.0 * M * N * K
+        NCU_DRAM_BYTES_FULL_LAUNCH = None  # the ncu capture belongs to the default shape only
     if args.impl != "reference" and args.config == "decode":
         return config_decode(args)
     if args.impl != "reference" and args.config == "moe":
@@ -702,7 +707,7 @@ def run_prefill(args):
         "hbm_gbs_at_min_bytes": (n_local * K * 9 / 16 + M * K * 9 / 16 + 2.0 * M * n_local) / (gemm_ms * 1e-3) / 1e9,
         # dram__bytes_read + dram__bytes_write of one launch of this kernel at the full shape (one ncu capture of this
         # command), scaled by this rank's share of the weight rows
-        "traffic": NCU_DRAM_BYTES_FULL_LAUNCH * n_local / N, "traffic_unit": "bytes per launch",
+        "traffic": (NCU_DRAM_BYTES_FULL_LAUNCH * n_local / N) if NCU_DRAM_BYTES_FULL_LAUNCH else None, "traffic_unit": "bytes per launch",
     }
     partition = {"none": "one GPU", "nccl": f"N column-sharded x{world} + NCCL all-gather of bf16 outputs",
                  "fused": f"N column-sharded x{world}, all-gather fused into the GEMM epilogue (one TMA store per peer over NVLink)",

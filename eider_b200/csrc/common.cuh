@@ -148,6 +148,12 @@ __device__ __forceinline__ float div6_rn(float a) {
     return (q0 > 1e-30f && q0 < 1e30f) ? q : __fdiv_rn(a, 6.0f);
 }
 
+// SiLU(gate) * up of the routed-MoE kernels: (g / (1 + e^-g)) * u (crates/eider-cuda/native/non_gemm.cu:2837-2840) with the
+// hardware exponential and reciprocal, which is also what the reference's build (--use_fast_math) turns that line into.
+// The stand-alone quantizer and the grouped GEMM's fused epilogue both call this, so their bytes agree; against a host
+// libm the last place of the exponential may differ.
+__device__ __forceinline__ float moe_silu_mul(float g, float u) { return __fmul_rn(__fdividef(g, __fadd_rn(1.0f, __expf(-g))), u); }
+
 // Quantize one 16-element block already divided by the input scale.  Returns the scale byte and
 // writes 8 packed bytes.  Order of operations: crates/eider-cuda/native/non_gemm.cu:120-153.
 __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32_t valid, uint2* packed_out) {

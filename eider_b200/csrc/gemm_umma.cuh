@@ -279,7 +279,7 @@ __device__ __forceinline__ void silu_quantize_store64(const Params& p, const Til
         for (int i = 0; i < 16; ++i) {
             const float g = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(raw[32 * b + i]) * rs));
             const float u = bf16_bits_to_float(float_to_bf16_bits(__uint_as_float(raw[32 * b + 16 + i]) * rs));
-            v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+            v[i] = moe_silu_mul(g, u);
         }
         uint2 bytes;
         scale_pair |= static_cast<uint32_t>(quantize_block16(v, 16, &bytes)) << (8 * b);

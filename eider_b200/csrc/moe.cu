@@ -297,8 +297,8 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quantize_kernel(const uint16
         for (int j = 0; j < 4; ++j) {
             const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
             const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
-            v[2 * j] = __fdiv_rn(g0, 1.0f + expf(-g0)) * u0;
-            v[2 * j + 1] = __fdiv_rn(g1, 1.0f + expf(-g1)) * u1;
+            v[2 * j] = moe_silu_mul(g0, u0);
+            v[2 * j + 1] = moe_silu_mul(g1, u1);
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(v[i]));

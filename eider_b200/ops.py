@@ -793,3 +793,88 @@ class GroupedMoe:
         self.route_weights = weights
         self.route_indices = idx
         return moe_weighted_accumulate(self.routes, weights.reshape(-1), self.down_out, self.tokens, self.top_k, out=self.out)
+
+
+# ---- operator composition ---------------------------------------------------------------------------------
+class DenseFfn:
+    """The dense gated FFN as the reference composes it for a batch of rows (crates/infer/src/qwen3/qwen36.rs:7175-7280):
+    gate_up = X . W_gu^T (W4A4, f32 out) -> SiLU(gate) * up -> NVFP4 with the down projection's static input scale (one
+    fused producer) -> down = A . W_d^T with beta = 1 on the residual -> bf16.  GEMM plans are cached by row count, as
+    run_nvfp4_batch does (crates/infer/src/qwen3/qwen36/batch.rs:1008-1058), so a new chunk length costs one plan creation
+    and a repeated one costs none."""
+
+    def __init__(self, w_gate_up: ModelOptWeight, w_down: ModelOptWeight):
+        if w_gate_up.out_features % 2 != 0 or w_down.in_features * 2 != w_gate_up.out_features or w_down.out_features != w_gate_up.in_features:
+            raise ShapeError("gate/up must be [2 * intermediate, hidden] and down [hidden, intermediate]")
+        self.w_gate_up, self.w_down = w_gate_up, w_down
+        self.hidden, self.inter = w_gate_up.in_features, w_down.in_features
+        self._plans = {}
+
+    def plans(self, rows: int):
+        if rows not in self._plans:
+            self._plans[rows] = (Fp4TnMatmulPlan(rows, 2 * self.inter, self.hidden), Fp4TnMatmulPlan(rows, self.hidden, self.inter))
+        return self._plans[rows]
+
+    def run(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """x [rows, hidden] bf16 or f32 (quantized on the fly with a per-row scale), residual [rows, hidden] bf16 -> bf16."""
+        rows = x.shape[0]
+        if x.shape[1] != self.hidden or residual.shape != (rows, self.hidden) or residual.dtype != torch.bfloat16:
+            raise ShapeError("x must be [rows, hidden] and residual bf16 of the same shape")
+        gate_up_plan, down_plan = self.plans(rows)
+        xq = quantize_nvfp4_rowscale(x)
+        gate_up = gate_up_plan.run(xq, self.w_gate_up, out_dtype=torch.float32)
+        act = silu_mul_halves_quantize_nvfp4(gate_up, self.w_down.input_scale)
+        out = residual.clone()
+        return down_plan.run(act, self.w_down, out=out, beta=1.0)  # alpha = weight_scale_2 * input_scale
+
+
+class DecodeMoe:
+    """One decode step of a routed-MoE layer for a single token, through the reference's table-driven entry points
+    (crates/eider-cuda/native/non_gemm.cu:13316-13397, 3558-3593, 3823-3845): the experts' weights stay where the
+    checkpoint loader put them and are found through device pointer tables; every slot's expert matrix is streamed once."""
+
+    def __init__(self, gate_up: list, down: list, top_k: int):
+        """gate_up / down: per-expert ModelOptWeight lists ([2 * intermediate, hidden] and [hidden, intermediate])."""
+        lib = _lib.load()
+        self._lib = lib
+        self.experts, self.top_k = len(gate_up), top_k
+        self.hidden, self.inter = gate_up[0].in_features, down[0].in_features
+        dev = gate_up[0].packed.device
+        table = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+        self._keep = (gate_up, down)
+        self.gu_w, self.gu_s = table([w.packed for w in gate_up]), table([w.scales_row_major for w in gate_up])
+        self.dn_w, self.dn_s = table([w.packed for w in down]), table([w.scales_row_major for w in down])
+        self.gu_g = torch.tensor([w.weight_scale_2 for w in gate_up], dtype=torch.float32, device=dev)
+        self.dn_g = torch.tensor([w.weight_scale_2 for w in down], dtype=torch.float32, device=dev)
+        self.ones = torch.ones(self.experts, dtype=torch.float32, device=dev)
+        self.indices = torch.zeros(top_k, dtype=torch.int32, device=dev)
+        self.weights = torch.zeros(top_k, dtype=torch.float32, device=dev)
+        self.gate_up = torch.zeros(top_k, 2 * self.inter, dtype=torch.float32, device=dev)
+        self.act = torch.zeros(top_k, self.inter, dtype=torch.float32, device=dev)
+        self.down = torch.zeros(top_k, self.hidden, dtype=torch.float32, device=dev)
+        self.gate_up_t, self.act_t, self.down_t = table(list(self.gate_up)), table(list(self.act)), table(list(self.down))
+        self.out = torch.zeros(self.hidden, dtype=torch.float32, device=dev)
+
+    def run(self, x: torch.Tensor, router_logits: torch.Tensor, shared_gate_logit: torch.Tensor, shared_output: torch.Tensor,
+            residual: torch.Tensor, norm_topk_prob: bool = True) -> torch.Tensor:
+        """x [hidden] f32, router_logits [experts] f32; returns residual + routed + sigmoid(shared_gate_logit) * shared_output,
+        rounded to bf16 precision (f32 storage), as infer_qwen36_ffn_finalize_routed_f32_on_stream does."""
+        lib, s = self._lib, _stream()
+        for t, name in ((x, "x"), (router_logits, "router_logits"), (shared_gate_logit, "shared_gate_logit"),
+                        (shared_output, "shared_output"), (residual, "residual")):
+            _need(t, torch.float32, name)
+        check("infer_moe_topk_f32_on_stream", lib.infer_moe_topk_f32_on_stream(router_logits.data_ptr(), self.indices.data_ptr(),
+                                                                                self.weights.data_ptr(), self.experts, self.top_k,
+                                                                                int(bool(norm_topk_prob)), s))
+        check("infer_nvfp4_w4a16_grouped_matvec_f32_on_stream", lib.infer_nvfp4_w4a16_grouped_matvec_f32_on_stream(
+            self.indices.data_ptr(), x.data_ptr(), self.gu_w.data_ptr(), self.gu_s.data_ptr(), self.gu_g.data_ptr(), self.gate_up_t.data_ptr(),
+            self.experts, self.top_k, 2 * self.inter, self.hidden, s))
+        check("infer_moe_silu_slots_f32_on_stream", lib.infer_moe_silu_slots_f32_on_stream(
+            self.indices.data_ptr(), self.gate_up_t.data_ptr(), self.act_t.data_ptr(), self.ones.data_ptr(), self.inter, self.top_k, s))
+        check("infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream", lib.infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream(
+            self.indices.data_ptr(), self.act_t.data_ptr(), self.dn_w.data_ptr(), self.dn_s.data_ptr(), self.dn_g.data_ptr(), self.down_t.data_ptr(),
+            self.experts, self.top_k, self.hidden, self.inter, s))
+        check("infer_qwen36_ffn_finalize_routed_f32_on_stream", lib.infer_qwen36_ffn_finalize_routed_f32_on_stream(
+            self.indices.data_ptr(), self.weights.data_ptr(), self.down_t.data_ptr(), self.ones.data_ptr(), shared_gate_logit.data_ptr(),
+            shared_output.data_ptr(), residual.data_ptr(), self.out.data_ptr(), self.hidden, self.top_k, s))
+        return self.out

@@ -197,3 +197,30 @@ def test_lm_head_top1(lib, oracle, n, k):
     assert int(out_i.item()) == min(best, n - 1)
     assert lib.infer_nvfp4_w4a16_top1_f32_on_stream(x.data_ptr(), w.packed.data_ptr(), w.scales_row_major.data_ptr(), sv.data_ptr(), si.data_ptr(),
                                                     2048, out_i.data_ptr(), out_v.data_ptr(), n, k, w.weight_scale_2, 5, None) == 1
+
+
+def test_decode_moe_operator(lib, oracle):
+    # the host mirror composes the same calls for one token
+    import torch
+
+    from eider_b200 import ops
+    experts, top_k, hidden, inter = 8, 2, 256, 128
+    rng = np.random.default_rng(2)
+    gu = make_experts(oracle, rng, experts, 2 * inter, hidden)
+    dn = make_experts(oracle, rng, experts, hidden, inter)
+    layer = ops.DecodeMoe([ops.ModelOptWeight.from_checkpoint(dev(p), dev(s), g) for p, s, g, _ in gu],
+                          [ops.ModelOptWeight.from_checkpoint(dev(p), dev(s), g) for p, s, g, _ in dn], top_k)
+    x, logits = rng.standard_normal(hidden).astype(np.float32), rng.standard_normal(experts).astype(np.float32)
+    shared, res = rng.standard_normal(hidden).astype(np.float32), rng.standard_normal(hidden).astype(np.float32)
+    gate = np.array([0.3], np.float32)
+    out = layer.run(dev(x), dev(logits), dev(gate), dev(shared), dev(res)).cpu().numpy()
+    idx, w = oracle.moe_topk(logits[None], top_k, True)
+    routed = np.zeros(hidden)
+    for slot in range(top_k):
+        e = int(idx[0, slot])
+        g_u = gu[e][3] @ x.astype(np.float64)
+        a = g_u[:inter] / (1 + np.exp(-g_u[:inter])) * g_u[inter:]
+        routed += (dn[e][3] @ a) * float(w[0, slot])
+    ref = res + routed + shared / (1 + np.exp(-0.3))
+    assert np.allclose(out, ref, rtol=1e-2, atol=1e-2)
+    assert np.array_equal(out, oracle.bf16_round(out))

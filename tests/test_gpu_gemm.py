@@ -210,3 +210,30 @@ def test_gemm_rejects_bad_arguments(ops):
     plan = lib.eider_b200_nvfp4_gemm_tn_create(128, 128, 128)
     assert lib.eider_b200_nvfp4_gemm_tn_on_stream(plan, None, None, None, None, None, None, 1.0, 0.0, None, 1, None) == 1
     lib.eider_b200_nvfp4_gemm_tn_destroy(plan)
+
+
+def test_dense_ffn_composition(ops, oracle):
+    # gate_up -> SiLU * up -> quantize -> down + residual -> bf16 (crates/infer/src/qwen3/qwen36.rs:7175-7280), stage by stage
+    # against the oracle, with the plan cache keyed by row count
+    import torch
+    hidden, inter = 1024, 768
+    rng = np.random.default_rng(4)
+    wgu = (rng.standard_normal((2 * inter, hidden)) * 0.02).astype(np.float32)
+    wdn = (rng.standard_normal((hidden, inter)) * 0.02).astype(np.float32)
+    gp, gs, gg = oracle.quantize_weight(wgu)
+    dp, ds, dg = oracle.quantize_weight(wdn)
+    in_scale = 0.015625
+    ffn = ops.DenseFfn(ops.ModelOptWeight.from_checkpoint(_dev(gp), _dev(gs), float(gg)),
+                       ops.ModelOptWeight.from_checkpoint(_dev(dp), _dev(ds), float(dg), input_scale=in_scale))
+    for rows in (300, 40, 300):
+        x = oracle.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32))
+        res = oracle.bf16_round(rng.standard_normal((rows, hidden)).astype(np.float32))
+        y = ffn.run(_dev(x, torch.bfloat16), _dev(res, torch.bfloat16))
+        torch.cuda.synchronize()
+        xp, xs, xr = oracle.quantize_nvfp4_rowscale(x)
+        gate_up = oracle.matmul_nt(oracle.dequantize_tiled(xp, xs), oracle.dequantize_weight(gp, gs), alpha=float(gg), row_scale=xr)
+        ap, as_ = oracle.silu_mul_halves_quantize_nvfp4(gate_up, in_scale)
+        ref = oracle.matmul_nt(oracle.dequantize_tiled(ap, as_), oracle.dequantize_weight(dp, ds), alpha=float(dg) * in_scale) + res
+        ok, stats = gemm_close(to_np(y), ref, rel=2e-2, abs_frac=2e-2)  # two quantized GEMMs in a row, bf16 output
+        assert ok, stats
+    assert sorted(ffn._plans) == [40, 300]  # one pair of plans per distinct row count, reused on the third call
