@@ -123,12 +123,12 @@ cudaError_t opt_in_smem(std::atomic<uint8_t> (&done)[kMaxDevices], Kernel kernel
     return st;
 }
 
-template <int KIND, int BLOCK_N, bool TRANSPOSED, int TERMS, bool GROUPED>
+template <int KIND, int BLOCK_N, bool TRANSPOSED, int TERMS, bool GROUPED, int EPI_WARPS = 4>
 cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, const Params& p, uint32_t work_items,
                    cudaStream_t stream) {
     constexpr int kStages = default_stages<KIND, BLOCK_N>();
     constexpr uint32_t kSmem = smem_bytes<KIND, BLOCK_N, kStages>();
-    auto kernel = gemm_kernel<KIND, BLOCK_N, kStages, TRANSPOSED, TERMS, GROUPED>;
+    auto kernel = gemm_kernel<KIND, BLOCK_N, kStages, TRANSPOSED, TERMS, GROUPED, EPI_WARPS>;
     static std::atomic<uint8_t> configured[kMaxDevices];
     if (cudaError_t st = opt_in_smem(configured, kernel, kSmem); st != cudaSuccess) return st;
     uint32_t grid = static_cast<uint32_t>(sm_count());
@@ -138,7 +138,7 @@ cudaError_t launch(const CUtensorMap& map_rows, const CUtensorMap& map_cols, con
     // tail of the kernel before it; everything that kernel wrote is read only after griddepcontrol.wait.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kNumThreads);
+    cfg.blockDim = dim3(64 + 32 * EPI_WARPS);
     cfg.dynamicSmemBytes = kSmem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -488,9 +488,11 @@ cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_
     const uint32_t max_row_tiles = (total_routes + kTileRows - 1) / kTileRows + plan.groups;
     if (plan.m % 256 == 0) {
         p.col_tiles = plan.m / 256;
+        if (act_packed) return launch<kNvf4, 256, false, 1, true, 8>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
         return launch<kNvf4, 256, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
     }
     p.col_tiles = plan.m / 128;
+    if (act_packed) return launch<kNvf4, 128, false, 1, true, 8>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
     return launch<kNvf4, 128, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
 }
 

@@ -294,8 +294,10 @@ __device__ __forceinline__ void silu_quantize_store64(const Params& p, const Til
 // KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
 // [col][row] (decode: rows are output features, columns are tokens).  TERMS: consecutive columns that
 // are summed (with their column scales) into one output column.  GROUPED: MoE schedule.
-template <int KIND, int BLOCK_N, int STAGES, bool TRANSPOSED, int TERMS, bool GROUPED>
-__global__ void __launch_bounds__(kNumThreads, 1)
+// EPI_WARPS: epilogue warps, 4 or 8.  Eight (two per tensor-memory lane quadrant, each taking half of the column steps)
+// are for the arithmetic-heavy SiLU * up -> NVFP4 epilogue, which four warps cannot finish in the time of a mainloop.
+template <int KIND, int BLOCK_N, int STAGES, bool TRANSPOSED, int TERMS, bool GROUPED, int EPI_WARPS = 4>
+__global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, const Params p) {
     using L = SmemLayout<BLOCK_N>;
     using T = TmemPlan<KIND, BLOCK_N>;
@@ -331,7 +333,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
         }
         for (uint32_t i = 0; i < kAcc; ++i) {
             umma::mbar_init(&acc_full[i], 1);
-            umma::mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+            umma::mbar_init(&acc_empty[i], EPI_WARPS);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         *last_flag = 0;
@@ -501,6 +503,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const uint32_t half = (warp - 2) >> 2;  // which half of the column steps (always 0 with four epilogue warps)
         umma::griddep_wait();            // scales / C written by the preceding kernel are read below
         uint32_t tile_count = 0;
         TileCoord t;
@@ -525,7 +528,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
                 wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
                        t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
-                if (GROUPED && p.act_packed) wide = true;  // (the host only sets it for whole tiles)
+            }
+            if constexpr (GROUPED && kWide) if (p.act_packed) {
+                // SiLU * up -> NVFP4 epilogue.  A rolled loop over the 64-column steps: the per-step body (32 activations and
+                // two block quantizations) is long, and unrolled copies of it beside the plain store path would not fit the
+                // instruction cache these warps have to themselves.  With eight warps each half takes half of the steps.
+                constexpr uint32_t kSteps = BLOCK_N / 64;
+                constexpr uint32_t kPer = kSteps / (EPI_WARPS / 4);
+                const uint32_t begin = half * kPer, end = begin + kPer;
+#pragma unroll 1
+                for (uint32_t step = begin; step < end; ++step) {
+                    const uint32_t c = (T::kOverlap && buf == 0) ? (BLOCK_N - 64 - step * 64) : step * 64;
+                    uint32_t raw[64];
+                    umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+                    umma::tmem_load_32x32(taddr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+                    umma::tmem_load_wait();
+                    if (T::kOverlap ? (step == begin) : (step + 1 == end)) {
+                        // the columns the next tile's MMAs may overwrite (the shared ones are step 0, which the first half
+                        // has just read; the second half never touches them) are in registers
+                        umma::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+                    }
+                    if (row_ok && !empty_tile) silu_quantize_store64(p, t, row, c, raw, rs);
+                }
+                continue;
+            }
+            if constexpr (EPI_WARPS > 4) if (half != 0) {
+                // the second set of warps only works in the fused epilogue above; elsewhere it keeps the barrier count
+                umma::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
+                continue;
             }
             if constexpr (kWide) if (wide) {
                 constexpr uint32_t kSteps = BLOCK_N / 64;
@@ -548,13 +582,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                         __syncwarp();
                         if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
                     }
-                    if (row_ok) {
-                        if (GROUPED && p.act_packed)
-                            silu_quantize_store64(p, t, row, col_of(step), &raw[step & 1][0], rs);
-                        else
-                            store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs,
-                                            p.col_scale ? p.col_scale + (GROUPED ? t.group * p.group_cols : 0) + t.out_col0 + col_of(step) : nullptr);
-                    }
+                    if (row_ok)
+                        store_row64_all(p, row_offset + col_of(step), &raw[step & 1][0], rs,
+                                        p.col_scale ? p.col_scale + (GROUPED ? t.group * p.group_cols : 0) + t.out_col0 + col_of(step) : nullptr);
                 }
                 if (!T::kOverlap) {
                     umma::tmem_load_wait();
