@@ -8,11 +8,14 @@ N = 27648 (fused gate+up).  A step = quantize the bf16 activations to NVFP4 on t
 scale, per-16 E4M3 scales) + the block-scaled tcgen05 GEMM with bf16 output.  Inputs are synthetic
 (X ~ N(0,1) bf16, W ~ N(0, 0.02^2) quantized the ModelOpt way), seeded.
 
-Prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`), the same through the public
-API with host buffers (`e2e`), the roofline of the dominant kernel, and the reference's CPU path timed on
-the host cores (`cpu_baseline`).  With --gpus N > 1 (launched by torchrun) the weight is sharded over N
-column-wise; the bf16 column blocks are written into every rank's output by the GEMM epilogue (symmetric memory, --gather
-fused) or all-gathered over NCCL (--gather nccl); strong scaling of the same workload.
+Prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`: K steps replayed as one CUDA graph), the
+same through the public API with host buffers (`e2e`), the roofline of the dominant kernel, the parity of the timed
+weights against the host path (`parity`; a failure exits non-zero before anything is timed) and the reference's CPU path
+timed on the host cores (`cpu_baseline`).  With --gpus N > 1 (launched by torchrun) the weight is sharded over N
+column-wise and the bf16 column blocks are written into every rank's output by the GEMM epilogue over NVLink (one
+multimem.st per tile through the switch, or one TMA store per peer with --no-multicast) or all-gathered over NCCL
+(--gather nccl); strong scaling of the same workload, with `scaling_detail` and the expert-parallel MoE in `extra.moe_ep`.
+Other configs: --config decode | moe | fp8 | sweep, --tokens / --in-features / --out-features.
 """
 from __future__ import annotations
 
@@ -399,6 +402,45 @@ def config_moe(args):
         dist.destroy_process_group()
 
 
+def config_sweep(args):
+    """--config sweep: the large dense W4A4 sweep on one GPU, M in {128, 512, 2048, 8192, 16384} x {(K 5120, N 27648), (K 13824,
+    N 5120)}; a step = per-row-scale quantizer + GEMM, replayed as a CUDA graph; rotating weight copies larger than L2."""
+    import torch
+    from eider_b200 import ops
+    peaks = load_peaks()
+    cases = []
+    for (k, n) in [(5120, 27648), (13824, 5120)]:
+        copies = 4
+        ws = [ops.ModelOptWeight.quantize(torch.randn(n, k, device="cuda") * 0.02) for _ in range(copies)]
+        for m in (128, 512, 2048, 8192, 16384):
+            x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+            xq = ops.Nvfp4Matrix.zeros(m, k, "cuda", row_scales=True)
+            y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            plan = ops.Fp4TnMatmulPlan(m, n, k)
+
+            def step(i):
+                ops.quantize_nvfp4_rowscale(x, out=xq)
+                plan.run(xq, ws[i % copies], out=y)
+
+            iters = max(4, min(args.steps, int(4000 / max(1.0, m / 64))))
+            us_step = _graph_time_us(torch, step, iters, reps=3)
+            us_gemm = _graph_time_us(torch, lambda i: plan.run(xq, ws[i % copies], out=y), iters, reps=3)
+            assert plan.status() == 0
+            fl = 2.0 * m * n * k
+            nbytes = n * k * 9 / 16 + m * k * 9 / 16 + 2.0 * m * n
+            cases.append({"M": m, "K": k, "N": n, "tile_code": plan.block_n, "step_us": us_step, "gemm_us": us_gemm,
+                          "gemm_tflops": fl / us_gemm / 1e6, "step_tflops": fl / us_step / 1e6,
+                          "gemm_frac_of_nominal_9pf": fl / us_gemm / 1e6 / NOMINAL_NVFP4_TFLOPS,
+                          "gemm_frac_of_4x_measured_bf16": fl / us_gemm / 1e6 / (4.0 * peaks["bf16_tflops"]),
+                          "gemm_gbs_at_min_bytes": nbytes / us_gemm / 1e3,
+                          "bound": "hbm" if m < 512 else "tensor"})
+            del x, xq, y, plan
+        del ws
+    print(json.dumps({"metric": METRIC, "unit": UNIT, "n_gpus": 1, "data": "synthetic", "config": {"workload": "dense NVFP4 W4A4 sweep"},
+                      "timing": "CUDA-graph replay, best of 3, 4 rotating weight copies", "peak_hbm_gbs": peaks["hbm_gbs"],
+                      "peak_source": peaks["source"], "cases": cases}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -410,7 +452,7 @@ def main():
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: how the column blocks become [M, N] on every rank: GEMM epilogue stores into every "
                          "rank's output (symmetric memory) or NCCL all-gather + re-assembly; auto = fused on 2, 4 and 8 ranks")
-    ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe", "fp8"],
+    ap.add_argument("--config", default="prefill", choices=["prefill", "decode", "moe", "fp8", "sweep"],
                     help="prefill (default, the contract line), or the single-GPU decode / MoE / FP8 GEMM configs")
     ap.add_argument("--tokens", type=int, default=0, help="prefill only: M instead of 512 (the larger-chunk configs)")
     ap.add_argument("--no-multicast", action="store_true", help="N > 1: one store per peer instead of one multimem.st per tile")
@@ -433,6 +475,8 @@ def main():
         return config_moe(args)
     if args.impl != "reference" and args.config == "fp8":
         return config_fp8_gemm(args)
+    if args.impl != "reference" and args.config == "sweep":
+        return config_sweep(args)
 
     if args.impl == "reference":
         reference_arm(args)
