@@ -136,6 +136,8 @@ SIGNATURES = {
     "infer_qwen36_ffn_finalize_routed_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _P]),
     "infer_qwen36_ffn_finalize_routed_batch_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "infer_nvfp4_w4a16_top1_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _P, _P, _U32, _U32, _F, _U32, _P]),
+    "infer_deepseek4_block_fp8_linear_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_block_fp8_f32_scale_linear_f32_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "eider_b200_peer_barrier_on_stream": (_I, [_P, _U32, _U32, _U32, _P, C.c_uint64, _P]),
 }
 

@@ -234,6 +234,94 @@ cudaError_t launch_fp8_simt(const uint8_t* xq, const float* s_x, const uint8_t* 
     return cudaSuccess;
 }
 
+// Block-scaled FP8 linear for a few tokens (crates/eider-cuda/native/deepseek4.cu:86-115, 117-170): weights [N][K] E4M3 with
+// one scale per 128 x 128 block, either an E8M0 byte or an f32; y[b][n] = sum_k x[b][k] * e4m3(w[n][k]) * scale[n/128][k/128]
+// with f32 activations (no activation quantization).  Same streaming shape as the kernels above: one warp per output row,
+// 128-bit weight loads (16 weights, always inside one scale block), activations of up to four tokens staged in shared
+// memory, so the weight matrix is read once per four tokens.
+template <int B, typename ScaleT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) block_fp8_linear_kernel(const float* __restrict__ x, const uint8_t* __restrict__ w,
+                                                                               const ScaleT* __restrict__ scales, float* __restrict__ y,
+                                                                               uint32_t n, uint32_t k) {
+    extern __shared__ float xs[];  // [B][k], 32-element chunks swizzled
+    for (uint32_t i = threadIdx.x; i < B * k; i += blockDim.x) {
+        const uint32_t b = i / k, e = i % k;
+        xs[b * k + xs_index(e / 32, e % 32)] = __ldg(x + static_cast<size_t>(b) * k + e);
+    }
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const uint8_t* wrow = w + static_cast<size_t>(row) * k;
+    const ScaleT* srow = scales + static_cast<size_t>(row / 128) * (k / 128);
+    float acc[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+    for (uint32_t h = lane; h < k / 16; h += 32) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(wrow + h * 16));
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+        float scale;
+        if constexpr (sizeof(ScaleT) == 1) {
+            const uint32_t code = __ldg(reinterpret_cast<const uint8_t*>(srow) + h / 8);
+            scale = code == 255 ? __int_as_float(0x7fc00000) : (code == 0 ? __int_as_float(0x00400000) : __int_as_float(code << 23));  // 2^(code - 127)
+        } else {
+            scale = __ldg(reinterpret_cast<const float*>(srow) + h / 8);
+        }
+        const uint32_t c = h / 2, e0 = (h & 1) * 16;
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const float* xb = xs + b * k;
+            float part = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 a = *reinterpret_cast<const float4*>(xb + xs_index(c, e0 + 4 * j));
+                part = fmaf(e4m3_value(static_cast<uint8_t>(ww[j])), a.x, part);
+                part = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 8)), a.y, part);
+                part = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 16)), a.z, part);
+                part = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 24)), a.w, part);
+            }
+            acc[b] = fmaf(scale, part, acc[b]);
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+        const float v = warp_sum(acc[b]);
+        if (lane == 0) y[static_cast<size_t>(b) * n + row] = v;
+    }
+}
+
+template <typename ScaleT>
+cudaError_t launch_block_fp8(const float* x, const uint8_t* w, const ScaleT* scales, float* y, uint32_t batch, uint32_t n, uint32_t k,
+                             cudaStream_t stream) {
+    if (!x || !w || !scales || !y || batch == 0 || n == 0 || k == 0 || n % 128 != 0 || k % 128 != 0) return cudaErrorInvalidValue;
+    const uint32_t grid = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    uint32_t done = 0;
+    while (done < batch) {
+        const uint32_t b = batch - done >= 4 ? 4 : (batch - done >= 2 ? 2 : 1);
+        const size_t smem = static_cast<size_t>(b) * k * sizeof(float);
+        if (smem > 200 * 1024) return cudaErrorNotSupported;
+        const float* xb = x + static_cast<size_t>(done) * k;
+        float* yb = y + static_cast<size_t>(done) * n;
+        cudaError_t st = cudaSuccess;
+#define EIDER_LAUNCH_BLOCK_FP8(BB)                                                                                             \
+    do {                                                                                                                       \
+        if (smem > 48 * 1024)                                                                                                  \
+            st = cudaFuncSetAttribute(block_fp8_linear_kernel<BB, ScaleT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                      static_cast<int>(smem));                                                                 \
+        if (st == cudaSuccess) block_fp8_linear_kernel<BB, ScaleT><<<grid, kWarpsPerBlock * 32, smem, stream>>>(xb, w, scales, yb, n, k); \
+    } while (0)
+        if (b == 4) EIDER_LAUNCH_BLOCK_FP8(4);
+        else if (b == 2) EIDER_LAUNCH_BLOCK_FP8(2);
+        else EIDER_LAUNCH_BLOCK_FP8(1);
+#undef EIDER_LAUNCH_BLOCK_FP8
+        if (st != cudaSuccess) return st;
+        st = cudaGetLastError();
+        if (st != cudaSuccess) return st;
+        done += b;
+    }
+    return cudaSuccess;
+}
+
 }  // namespace
 }  // namespace eider
 
@@ -277,6 +365,16 @@ cudaError_t eider_b200_fp8_linear_prequantized_simt_on_stream(const uint8_t* xq,
                                          static_cast<uint16_t*>(output), tokens, out_features, in_features, stream);
     return launch_fp8_simt<float>(xq, input_scales, weight, channel_scale, weight_scale, static_cast<float*>(output),
                                   tokens, out_features, in_features, stream);
+}
+
+cudaError_t infer_deepseek4_block_fp8_linear_f32_on_stream(const float* input, const uint8_t* weight, const uint8_t* scales, float* output,
+                                                           uint32_t batch_rows, uint32_t rows, uint32_t cols, cudaStream_t stream) {
+    return launch_block_fp8<uint8_t>(input, weight, scales, output, batch_rows, rows, cols, stream);
+}
+
+cudaError_t infer_block_fp8_f32_scale_linear_f32_on_stream(const float* input, const uint8_t* weight, const float* scales, float* output,
+                                                           uint32_t batch_rows, uint32_t rows, uint32_t cols, cudaStream_t stream) {
+    return launch_block_fp8<float>(input, weight, scales, output, batch_rows, rows, cols, stream);
 }
 
 }  // extern "C"

@@ -221,6 +221,18 @@ EIDER_B200_API cudaError_t eider_b200_fp8_linear_prequantized_simt_on_stream(
     const uint8_t* xq, const float* input_scales, const uint8_t* weight, const float* channel_scale, float weight_scale,
     void* output, int output_is_bf16, uint32_t tokens, uint32_t out_features, uint32_t in_features, cudaStream_t stream);
 
+/* Block-scaled FP8 linears (crates/eider-cuda/native/deepseek4.cu:1457-1495; weights of
+ * crates/eider-format/src/modelopt.rs:390-443): weight [rows][cols] E4M3, one scale per 128 x 128 block as an E8M0 byte
+ * (first form) or an f32 (second form), f32 activations [batch_rows][cols], f32 output [batch_rows][rows];
+ * rows % 128 == 0 and cols % 128 == 0 as in the reference.  CUDA-core streaming kernels: the weight matrix is read once per
+ * four tokens. */
+EIDER_B200_API cudaError_t infer_deepseek4_block_fp8_linear_f32_on_stream(const float* input, const uint8_t* weight,
+                                                                          const uint8_t* scales, float* output, uint32_t batch_rows,
+                                                                          uint32_t rows, uint32_t cols, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_block_fp8_f32_scale_linear_f32_on_stream(const float* input, const uint8_t* weight,
+                                                                          const float* scales, float* output, uint32_t batch_rows,
+                                                                          uint32_t rows, uint32_t cols, cudaStream_t stream);
+
 /* ---- dense GEMM on tcgen05 -------------------------------------------------------------------- */
 
 /* Supersedes cublasLtMatmul behind Fp4TnMatmulPlan (crates/eider-cuda/src/cublaslt/fp4_tn.rs:264-796,

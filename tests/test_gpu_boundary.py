@@ -286,3 +286,29 @@ def test_reference_fp8_linear_shims(lib, oracle):
     ok, stats = gemm_close(y3.cpu().numpy(), ref3, rel=1e-3, abs_frac=1e-3)
     assert ok, stats
     assert lib.infer_fp8_linear_w8a8_f32_on_stream(xd.data_ptr(), wd.data_ptr(), y3.data_ptr(), n, k, 0.5, 0.0, None) == 1
+
+
+@pytest.mark.parametrize("batch", [1, 7])
+def test_block_scaled_fp8_linears(lib, oracle, batch):
+    # crates/eider-cuda/native/deepseek4.cu:86-170: f32 activations x E4M3 weights x one scale per 128 x 128 block
+    import torch
+    n, k = 512, 1024
+    rng = np.random.default_rng(batch)
+    codes = rng.integers(0, 256, (n, k)).astype(np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x30
+    e8 = rng.integers(118, 131, (n // 128, k // 128)).astype(np.uint8)
+    f32s = rng.uniform(0.01, 2.0, (n // 128, k // 128)).astype(np.float32)
+    x = rng.standard_normal((batch, k)).astype(np.float32)
+    wv = oracle.e4m3_decode(codes).astype(np.float64)
+    xd, wd = dev(x), dev(codes)
+    for name, scales, dense in (("infer_deepseek4_block_fp8_linear_f32_on_stream", e8,
+                                 np.array([[oracle.e8m0_value(int(c)) for c in r] for r in e8], np.float64)),
+                                ("infer_block_fp8_f32_scale_linear_f32_on_stream", f32s, f32s.astype(np.float64))):
+        y = torch.full((batch, n + 4), -77.0, device="cuda")[:, :n].contiguous()
+        sd = dev(scales)
+        assert getattr(lib, name)(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), y.data_ptr(), batch, n, k, None) == 0
+        torch.cuda.synchronize()
+        ref = x.astype(np.float64) @ (wv * np.kron(dense, np.ones((128, 128)))).T
+        ok, stats = gemm_close(y.cpu().numpy(), ref, rel=1e-4, abs_frac=1e-4)
+        assert ok, (name, stats)
+        assert getattr(lib, name)(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), y.data_ptr(), batch, n + 64, k, None) == 1
