@@ -456,6 +456,7 @@ def main():
                     help="prefill (default, the contract line), or the single-GPU decode / MoE / FP8 GEMM configs")
     ap.add_argument("--tokens", type=int, default=0, help="prefill only: M instead of 512 (the larger-chunk configs)")
     ap.add_argument("--no-multicast", action="store_true", help="N > 1: one store per peer instead of one multimem.st per tile")
+    ap.add_argument("--multicast", action="store_true", help="N > 1: one multimem.st per tile also below eight ranks")
     ap.add_argument("--no-extra", action="store_true", help="skip the short decode / larger-chunk measurements of the default line")
     ap.add_argument("--in-features", type=int, default=0, help="prefill only: K instead of 5120 (13824 with --out-features 5120 = the down projection)")
     ap.add_argument("--out-features", type=int, default=0, help="prefill only: N instead of 27648")
@@ -556,7 +557,9 @@ def run_prefill(args):
                     q.set_block_n(args.block_n)
                 elif M > 128:
                     q.set_block_n(512)  # the CTA-pair kernel stages whole tiles for the stores that leave the GPU
-            sharded.fuse_into(fused_plans, M, multicast=not args.no_multicast)
+            # one multimem.st per tile pays from eight ranks on (measured: one TMA store per peer is faster on two and four)
+            use_multicast = (not args.no_multicast) and (world >= 8 or args.multicast)
+            sharded.fuse_into(fused_plans, M, multicast=use_multicast)
             gather = "fused-multicast" if sharded.multicast else "fused"
         except Exception as exc:  # symmetric memory is not available on this box: keep the NCCL path
             if rank == 0:

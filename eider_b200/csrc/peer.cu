@@ -172,28 +172,53 @@ __global__ void __launch_bounds__(256) ep_expand_experts_kernel(const uint32_t* 
     sorted_experts[row] = lo;
 }
 
-// One warp per received row: the bf16 result row goes back to the route's source rank, at the route's own index.
-__global__ void __launch_bounds__(kDispatchWarps * 32) ep_return_rows_kernel(const uint16_t* __restrict__ rows,
-                                                                            const uint32_t* __restrict__ origin,
-                                                                            const uint32_t* __restrict__ recv_total, ByteTable ret,
-                                                                            uint32_t capacity, uint32_t n) {
-    const uint32_t row = blockIdx.x * kDispatchWarps + (threadIdx.x >> 5);
-    const uint32_t lane = threadIdx.x & 31;
-    if (row >= capacity || row >= recv_total[0]) return;
-    const uint32_t o = origin[row];
-    const uint32_t src_rank = o >> 24, route = o & 0xffffffu;
-    const uint4* s4 = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(row) * n);
-    uint4* d4 = reinterpret_cast<uint4*>(ret.p[src_rank] + static_cast<size_t>(route) * n * 2);
-    // four loads in flight per lane before the first store: the row leaves as whole 512-byte runs per warp instruction
-    uint32_t i = lane;
-    for (; i + 96 < n / 8; i += 128) {
-        const uint4 a = __ldg(s4 + i), b = __ldg(s4 + i + 32), c = __ldg(s4 + i + 64), d = __ldg(s4 + i + 96);
-        d4[i] = a;
-        d4[i + 32] = b;
-        d4[i + 64] = c;
-        d4[i + 96] = d;
+// The bf16 result rows go back to the source rank of their route, at the route's own index.  Each row is one contiguous
+// run of 2 * n bytes on both sides, so it travels as two bulk copies of the copy engine: global -> shared memory (completes
+// on an mbarrier), shared memory -> the peer's return buffer.  NVLink then carries whole rows in full-size packets, which
+// plain 16-byte stores per lane did not (about 390 GB/s).  One row per warp at a time, persistent warps; every wait is
+// bounded and a warp that gives up simply stops copying (the layer's status shows up as wrong rows in no case: the host
+// checks the barrier status, and the bound is a second).
+constexpr uint32_t kReturnWarps = 4;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__global__ void __launch_bounds__(kReturnWarps * 32) ep_return_rows_kernel(const uint16_t* __restrict__ rows,
+                                                                           const uint32_t* __restrict__ origin,
+                                                                           const uint32_t* __restrict__ recv_total, ByteTable ret,
+                                                                           uint32_t capacity, uint32_t n) {
+    extern __shared__ __align__(128) uint8_t stage[];  // [kReturnWarps][2 * n]
+    __shared__ __align__(8) uint64_t bars[kReturnWarps];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row_bytes = n * 2;
+    if (lane != 0) return;  // one thread per warp drives the copy engine
+    const uint32_t bar = smem_addr(&bars[warp]);
+    const uint32_t buf = smem_addr(stage + static_cast<size_t>(warp) * row_bytes);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const uint32_t total = min(capacity, recv_total[0]);
+    uint32_t phase = 0;
+    for (uint32_t row = blockIdx.x * kReturnWarps + warp; row < total; row += gridDim.x * kReturnWarps) {
+        // the store that last read this buffer has finished reading it
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(buf),
+                     "l"(rows + static_cast<size_t>(row) * n), "r"(row_bytes), "r"(bar)
+                     : "memory");
+        const long long start = clock64();
+        uint32_t done = 0;
+        while (!done) {
+            asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                         : "=r"(done) : "r"(bar), "r"(phase) : "memory");
+            if (!done && clock64() - start > 2000000000ll) return;
+        }
+        phase ^= 1;
+        const uint32_t o = origin[row];
+        uint8_t* dst = ret.p[o >> 24] + static_cast<size_t>(o & 0xffffffu) * row_bytes;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(buf), "r"(row_bytes) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
-    for (; i < n / 8; i += 32) d4[i] = __ldg(s4 + i);
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the rows have left before the kernel (and the barrier behind it) ends
 }
 
 }  // namespace
@@ -291,8 +316,16 @@ cudaError_t eider_b200_ep_return_rows_on_stream(const uint16_t* rows, const uint
     if (!rows || !recv_origin || !recv_total || capacity == 0 || out_features == 0 || out_features % 8 != 0 || world == 0 ||
         world > kMaxRanks || (reinterpret_cast<uintptr_t>(rows) & 15) != 0 || !fill_bytes(ret, return_rows, world, 15))
         return cudaErrorInvalidValue;
-    ep_return_rows_kernel<<<(capacity + kDispatchWarps - 1) / kDispatchWarps, kDispatchWarps * 32, 0, stream>>>(
-        rows, recv_origin, recv_total, ret, capacity, out_features);
+    const size_t smem = static_cast<size_t>(kReturnWarps) * out_features * 2;
+    if (smem > 160 * 1024) return cudaErrorNotSupported;
+    if (smem > 48 * 1024) {
+        cudaError_t st = cudaFuncSetAttribute(ep_return_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (st != cudaSuccess) return st;
+    }
+    // persistent warps: enough CTAs to fill the machine, never more than there are rows
+    uint32_t grid = (capacity + kReturnWarps - 1) / kReturnWarps;
+    if (grid > 148 * 8) grid = 148 * 8;
+    ep_return_rows_kernel<<<grid, kReturnWarps * 32, smem, stream>>>(rows, recv_origin, recv_total, ret, capacity, out_features);
     return cudaGetLastError();
 }
 
