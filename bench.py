@@ -602,41 +602,55 @@ def run_prefill(args):
         return best
 
     # ---- parity gate: the timed weights, checked against the host path before anything is timed ---------------
-    with torch.cuda.stream(stream):
-        step(0, x_dev)
-        torch.cuda.synchronize()
-        y_check = result["y"].float().cpu().numpy()
-    parity, cpu_line = None, None
-    if rank == 0:
-        from oracle import oracle as o
-        xp, xs, xr = xq.packed.cpu().numpy(), xq.scales.cpu().numpy(), xq.row_scales.cpu().numpy()
-        a = o.dequantize_tiled(xp, xs) * xr[:, None]
-        if world == 1:
-            w0 = weights[0]
-            ref, seconds, cols = cpu_reference_product(a, w0.packed.cpu().numpy(), w0.scales_row_major.cpu().numpy(), w0.weight_scale_2,
-                                                       cols=None if not args.no_cpu_baseline else 1024)
-            parity = parity_report(y_check[:, :cols], ref)
-            sample = (f"the whole workload ({M} tokens x K={K} x {N} output features; unpack + f32 triple loop)" if cols == N else
-                      f"all {M} tokens x all K={K} x first {cols} of {N} output features (unpack + f32 triple loop)")
-            cpu_line = {"value": 2.0 * M * cols * K / seconds / 1e12, "unit": UNIT, "cores": o.max_threads(), "kind": "port",
-                        "sample": sample, "seconds": seconds}
-        else:
-            # the gathered [M, N] on rank 0: the first and last 128 columns of every rank's block, weights regenerated here
-            got, want = [], []
-            for shard in range(world):
-                ws_ = shard_weights(0, shard)
-                wp_h, ws_h = ws_.packed.cpu().numpy(), ws_.scales_row_major.cpu().numpy()
-                for c0 in (0, n_local - 128):
-                    ref, _, _ = cpu_reference_product(a, wp_h[c0:c0 + 128], ws_h[c0:c0 + 128], ws_.weight_scale_2, cols=128)
-                    want.append(ref)
-                    got.append(y_check[:, shard * n_local + c0: shard * n_local + c0 + 128])
-                del ws_
-            parity = parity_report(np.concatenate(got, axis=1), np.concatenate(want, axis=1))
-            parity["columns"] = "first and last 128 columns of every rank's block of the gathered output on rank 0"
-    ok = torch.tensor([1 if (parity is None or parity["bad"] == 0) else 0], device="cuda")
-    if world > 1:
-        dist.broadcast(ok, 0)
-    if int(ok.item()) == 0:
+    def check_parity():
+        """One step on weight copy 0 against the host product; -> (ok on every rank, parity dict on rank 0, cpu_baseline dict)."""
+        with torch.cuda.stream(stream):
+            step(0, x_dev)
+            torch.cuda.synchronize()
+            y_check = result["y"].float().cpu().numpy()
+        parity, cpu_line = None, None
+        if rank == 0:
+            from oracle import oracle as o
+            xp, xs, xr = xq.packed.cpu().numpy(), xq.scales.cpu().numpy(), xq.row_scales.cpu().numpy()
+            a = o.dequantize_tiled(xp, xs) * xr[:, None]
+            if world == 1:
+                w0 = weights[0]
+                ref, seconds, cols = cpu_reference_product(a, w0.packed.cpu().numpy(), w0.scales_row_major.cpu().numpy(), w0.weight_scale_2,
+                                                           cols=None if not args.no_cpu_baseline else 1024)
+                parity = parity_report(y_check[:, :cols], ref)
+                sample = (f"the whole workload ({M} tokens x K={K} x {N} output features; unpack + f32 triple loop)" if cols == N else
+                          f"all {M} tokens x all K={K} x first {cols} of {N} output features (unpack + f32 triple loop)")
+                cpu_line = {"value": 2.0 * M * cols * K / seconds / 1e12, "unit": UNIT, "cores": o.max_threads(), "kind": "port",
+                            "sample": sample, "seconds": seconds}
+            else:
+                # the gathered [M, N] on rank 0: the first and last 128 columns of every rank's block, weights regenerated here
+                got, want = [], []
+                for shard in range(world):
+                    ws_ = shard_weights(0, shard)
+                    wp_h, ws_h = ws_.packed.cpu().numpy(), ws_.scales_row_major.cpu().numpy()
+                    for c0 in (0, n_local - 128):
+                        ref, _, _ = cpu_reference_product(a, wp_h[c0:c0 + 128], ws_h[c0:c0 + 128], ws_.weight_scale_2, cols=128)
+                        want.append(ref)
+                        got.append(y_check[:, shard * n_local + c0: shard * n_local + c0 + 128])
+                    del ws_
+                parity = parity_report(np.concatenate(got, axis=1), np.concatenate(want, axis=1))
+                parity["columns"] = "first and last 128 columns of every rank's block of the gathered output on rank 0"
+        ok = torch.tensor([1 if (parity is None or parity["bad"] == 0) else 0], device="cuda")
+        if world > 1:
+            dist.broadcast(ok, 0)
+        return bool(int(ok.item())), parity, cpu_line
+
+    ok, parity, cpu_line = check_parity()
+    if not ok and gather == "fused-multicast":
+        # the multicast epilogue is the newest path: fall back to one store per peer rather than give up on the run
+        if rank == 0:
+            print(f"# multicast all-gather failed the parity check ({parity}); falling back to per-peer stores", file=sys.stderr)
+        for q in fused_plans:
+            q.set_output_multicast(0)
+        sharded.multicast = False
+        gather = "fused"
+        ok, parity, cpu_line = check_parity()
+    if not ok:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "error": "parity check failed, nothing was timed", "parity": parity}), flush=True)
         if dist:
