@@ -269,7 +269,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
                 umma::tmem_load_32x32(taddr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
             };
-            const bool wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && t.col0 + kPairN <= p.cols &&
+            const bool wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) &&
                               (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             const bool staged = p.out_maps != nullptr;  // (the host sets the maps only for plain bf16 output)
             const bool multicast = p.out_multicast != nullptr;  // (likewise, and only when the column count is a multiple of 8)
@@ -344,8 +344,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     }
                     continue;
                 }
-                if (!row_ok) continue;
-                if (wide) {
+                if (!row_ok || t.col0 + c >= p.cols) continue;
+                if (wide && t.col0 + c + 64 <= p.cols) {  // (a tile that hangs over the last column still stores its whole 64-column steps wide)
                     store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs,
                                     p.col_scale ? p.col_scale + t.col0 + c : nullptr);
                 } else {

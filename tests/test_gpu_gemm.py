@@ -101,7 +101,7 @@ def test_nvfp4_gemm_random(ops, oracle, m, n, k, block_n):
     _nvfp4_case(ops, oracle, x, w, block_n=block_n, rowscale=True, out_dtype="bf16")
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (130, 264, 1056), (384, 640, 288), (512, 1024, 5120), (1000, 2304, 2048)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (130, 264, 1056), (384, 640, 288), (512, 1024, 5120), (1000, 2304, 2048), (512, 3456, 512)])
 def test_nvfp4_gemm_cta_pairs(ops, oracle, m, n, k):
     # tile code 512: 256 x 256 tiles computed by clusters of two CTAs (tcgen05 cta_group::2); odd row-tile counts,
     # partial tiles in both directions and a K that is not a multiple of the stage depth are all in the list
