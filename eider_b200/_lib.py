@@ -80,6 +80,11 @@ SIGNATURES = {
     "eider_b200_decode_plan_set_path": (_I, [_P, _U32]),
     "eider_b200_nvfp4_w4a16_gemv_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _P, _F, _I, _P]),
     "eider_b200_fp8_linear_decode_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _I, _P]),
+    "eider_b200_fp8_linear_decode_quantized_on_stream": (_I, [_P, _P, _P, _U32, _P, _P, _F, _P, _I, _P]),
+    "eider_b200_nvfp4_decode_operand_create": (_P, [_U32, _U32]),
+    "eider_b200_nvfp4_decode_operand_destroy": (None, [_P]),
+    "eider_b200_nvfp4_decode_operand_expand_on_stream": (_I, [_P, _P, _I, _U32, _P]),
+    "eider_b200_nvfp4_w4a16_gemv_prepared_on_stream": (_I, [_P, _P, _P, _P, _F, _P, _P, _F, _I, _P]),
     "infer_moe_topk_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _I, _P]),
     "infer_moe_topk_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _I, _P]),
     "eider_b200_moe_sort_scratch_bytes": (_SZ, [_U32, _U32]),

@@ -63,6 +63,11 @@ __host__ __device__ inline float e4m3_value(uint8_t code) {
 #endif
 }
 
+// Residual NVFP4 expansion of activation rows (defined beside its kernel): scale bytes go to the 128 x 4 tiled layout of a GEMM
+// operand when operand_cols is 0, else to [64-element block][operand_cols rows][16 bytes].
+cudaError_t expand_nvfp4_terms_launch(const void* input, int input_is_bf16, uint8_t* packed, uint8_t* scales, float* col_scale,
+                                      uint32_t tokens, uint32_t in_features, uint32_t terms, uint32_t operand_cols, cudaStream_t stream);
+
 #ifdef __CUDACC__
 
 // E2M1 nibble -> f32 (crates/eider-cuda/src/format.rs:78-96).

@@ -46,6 +46,8 @@ struct Params {
     float* workspace;    // [splits][tokens][row_tiles * 128]
     uint32_t* counters;  // [row_tiles], self-resetting
     uint32_t* status;
+    const float* x_scale;  // quantized-activation kernel: [tokens] scales written by the activation quantizer
+    uint32_t defer_reduce; // quantized-activation kernel: leave the K splits' partial sums to splitk_reduce_kernel
 };
 
 template <typename XT> __device__ __forceinline__ void load8(const XT* p, float (&v)[8]);
@@ -247,22 +249,30 @@ __global__ void __launch_bounds__(kThreads, 3) fp8_decode_fused_kernel(const __g
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (*last_flag) {
                     __threadfence();
-                    if (row_ok)
-                        for (uint32_t m = 0; m < p.tokens; ++m) {
-                            // all partials are requested before any is used (one memory round trip), summed in split order
-                            float sum = 0.0f;
-                            for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
-                                float part[8];
+                    if (row_ok) {
+                        // the partials of every token and of eight splits at a time are requested before any is used (one
+                        // memory round trip per eight splits, not per token); each token is summed in split order
+                        float sum[kMaxTokens];
+#pragma unroll
+                        for (uint32_t m = 0; m < kMaxTokens; ++m) sum[m] = 0.0f;
+                        for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+                            float part[kMaxTokens][8];
+#pragma unroll
+                            for (uint32_t m = 0; m < kMaxTokens; ++m)
 #pragma unroll
                                 for (uint32_t u = 0; u < 8; ++u)
-                                    part[u] = (s0 + u < p.splits)
-                                                  ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.tokens + m) * padded_rows + row])
-                                                  : 0.0f;
+                                    part[m][u] = (m < p.tokens && s0 + u < p.splits)
+                                                     ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.tokens + m) * padded_rows + row])
+                                                     : 0.0f;
 #pragma unroll
-                                for (uint32_t u = 0; u < 8; ++u) sum += part[u];
-                            }
-                            emit(m, sum);
+                            for (uint32_t m = 0; m < kMaxTokens; ++m)
+#pragma unroll
+                                for (uint32_t u = 0; u < 8; ++u) sum[m] += part[m][u];
                         }
+#pragma unroll
+                        for (uint32_t m = 0; m < kMaxTokens; ++m)
+                            if (m < p.tokens) emit(m, sum[m]);
+                    }
                 }
             }
         }
@@ -273,6 +283,222 @@ __global__ void __launch_bounds__(kThreads, 3) fp8_decode_fused_kernel(const __g
         umma::tc_fence_after();
         umma::tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+// ---- activations already quantized (1..64 tokens) ---------------------------------------------------------------------
+// The per-token quantizer has run as its own kernel (the producer of x, or the reference's batch quantizer); this kernel is
+// the same one-item-per-CTA GEMV with nothing to compute before the MMAs: every ring slot holds a weight stage and the
+// matching stage of the activation codes (a tiled TMA load of COLS rows x 128 bytes, rows past `tokens` arrive as zeros),
+// the activation half being requested only once the kernel before this one has finished.
+__host__ __device__ inline uint32_t quantized_smem_bytes(uint32_t ring, uint32_t cols) { return kFixedBytes + ring * (kWeightTile + cols * kStageK); }
+
+template <int COLS>
+__global__ void __launch_bounds__(kThreads, 3) fp8_decode_quantized_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                          const __grid_constant__ CUtensorMap map_x, const Params p) {
+    constexpr uint32_t kAct = COLS * kStageK;
+    constexpr uint32_t kTmem = COLS < 32 ? 32 : COLS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t kRing = p.ring;
+    uint8_t* ring_w = smem;
+    uint8_t* ring_a = ring_w + kRing * kWeightTile;  // [ring][COLS rows][128 B], swizzled
+    uint8_t* tail = ring_a + kRing * kAct;
+    uint64_t* full = reinterpret_cast<uint64_t*>(tail);  // [kMaxRing]: two arrivals, the weight half and the activation half
+    uint64_t* empty = full + kMaxRing;                   // [kMaxRing]
+    uint64_t* acc_full = empty + kMaxRing;               // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* last_flag = tmem_slot + 2;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t split = blockIdx.x % p.splits, rt = blockIdx.x / p.splits;
+    const uint32_t stage0 = split * p.per, stage1 = min(p.k_stages, stage0 + p.per);
+    const uint32_t nstages = stage1 > stage0 ? stage1 - stage0 : 0;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < kMaxRing; ++i) {
+            umma::mbar_init(&full[i], 2);
+            umma::mbar_init(&empty[i], 1);
+        }
+        umma::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        umma::fence_barrier_init();
+        umma::prefetch_tensormap(&map_w);
+        umma::prefetch_tensormap(&map_x);
+    }
+    auto load_weights = [&](uint32_t s, uint32_t slot) {
+        umma::mbar_arrive_expect_tx(&full[slot], kWeightTile);
+        umma::tma_load_2d(ring_w + slot * kWeightTile, &map_w, &full[slot], static_cast<int32_t>(s * kStageK), static_cast<int32_t>(rt * kRows));
+    };
+    auto load_activation = [&](uint32_t s, uint32_t slot) {
+        umma::mbar_arrive_expect_tx(&full[slot], kAct);
+        umma::tma_load_2d(ring_a + slot * kAct, &map_x, &full[slot], static_cast<int32_t>(s * kStageK), 0);
+    };
+    // weights depend on nothing and every slot is free: the first ring is requested before the setup barrier
+    const uint32_t early = min(kRing, nstages);
+    if (threadIdx.x == 0)
+        for (uint32_t i = 0; i < early; ++i) load_weights(stage0 + i, i);
+    if (warp == 1) {
+        umma::tmem_alloc(tmem_slot, kTmem);
+        umma::tmem_relinquish();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) umma::griddep_launch_dependents();
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        const bool leader = umma::elect_one();
+        umma::griddep_wait();  // the activation codes are the output of the kernel before this one
+        if (leader)
+            for (uint32_t i = 0; i < early; ++i) load_activation(stage0 + i, i);
+        __syncwarp();
+        for (uint32_t it = early; it < nstages; ++it) {
+            const uint32_t slot = it % kRing, phase = (it / kRing) & 1;
+            if (!__all_sync(0xffffffffu, umma::mbar_wait(&empty[slot], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) break;
+            if (leader) {
+                load_weights(stage0 + it, slot);
+                load_activation(stage0 + it, slot);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        const bool leader = umma::elect_one();
+        constexpr uint32_t idesc = umma::idesc_f8(COLS);
+        const uint32_t w_lo0 = umma::desc_lo_sw128(umma::smem_u32(ring_w));
+        const uint32_t a_lo0 = umma::desc_lo_sw128(umma::smem_u32(ring_a));
+        bool ok = true;
+        for (uint32_t it = 0; ok && it < nstages; ++it) {
+            const uint32_t slot = it % kRing, phase = (it / kRing) & 1;
+            if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[slot], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
+            umma::tc_fence_after();
+            if (leader) {
+                const uint32_t w_lo = w_lo0 + slot * (kWeightTile >> 4), a_lo = a_lo0 + slot * (kAct >> 4);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j)  // K past the end is zero on both sides (TMA fill)
+                    umma::mma_f8(tmem_base, umma::make_desc(w_lo + j * 2, umma::kDescHiSw128), umma::make_desc(a_lo + j * 2, umma::kDescHiSw128),
+                                 idesc, (it > 0 || j > 0) ? 1u : 0u);
+                umma::tc_commit(&empty[slot]);
+            }
+            __syncwarp();
+        }
+        if (ok && leader) umma::tc_commit(acc_full);
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const uint32_t te = threadIdx.x - 64;  // 0..127
+        const uint32_t quad = warp & 3;
+        umma::griddep_wait();  // scratch, counters and the output are shared with the kernel before this one
+        bool ok = umma::mbar_wait(acc_full, 0, abort_flag, p.status, umma::kTimeoutTmemFull);
+        if (ok) {
+            umma::tc_fence_after();
+            const uint32_t row = rt * kRows + quad * 32 + lane;
+            const bool row_ok = row < p.n;
+            const uint32_t padded_rows = p.row_tiles * kRows;
+            const float rs = p.alpha * ((p.channel_scale && row_ok) ? p.channel_scale[row] : 1.0f);
+            auto emit = [&](uint32_t m, float sum) {
+                const size_t index = static_cast<size_t>(m) * p.ld_out + row;
+                const float v = sum * __ldg(p.x_scale + m) * rs;
+                if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(v);
+                else static_cast<float*>(p.out)[index] = v;
+            };
+            // sixteen tokens at a time: accumulator columns -> output, or -> this split's partial sums
+#pragma unroll 1
+            for (uint32_t m0 = 0; m0 < p.tokens; m0 += 16) {
+                uint32_t raw[16];
+                if (nstages > 0) {
+                    umma::tmem_load_32x16(tmem_base + ((quad * 32) << 16) + m0, raw);
+                    umma::tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) raw[i] = 0;
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const uint32_t m = m0 + i;
+                    if (m >= p.tokens) break;
+                    if (p.splits == 1) {
+                        if (row_ok) emit(m, __uint_as_float(raw[i]));
+                    } else {
+                        p.workspace[(static_cast<size_t>(split) * p.tokens + m) * padded_rows + row] = __uint_as_float(raw[i]);
+                    }
+                }
+            }
+            if (p.splits > 1 && !p.defer_reduce) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (te == 0) {
+                    const uint32_t prev = atomicAdd(&p.counters[rt], 1u);
+                    *last_flag = (prev == p.splits - 1) ? 1u : 0u;
+                    if (prev == p.splits - 1) p.counters[rt] = 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    if (row_ok) {
+                        // eight tokens x four splits are requested before any is used; each token is summed in split order
+#pragma unroll 1
+                        for (uint32_t m0 = 0; m0 < p.tokens; m0 += 8) {
+                            float sum[8];
+#pragma unroll
+                            for (uint32_t i = 0; i < 8; ++i) sum[i] = 0.0f;
+                            for (uint32_t s0 = 0; s0 < p.splits; s0 += 4) {
+                                float part[8][4];
+#pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i)
+#pragma unroll
+                                    for (uint32_t u = 0; u < 4; ++u)
+                                        part[i][u] = (m0 + i < p.tokens && s0 + u < p.splits)
+                                                         ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.tokens + m0 + i) * padded_rows + row])
+                                                         : 0.0f;
+#pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i)
+#pragma unroll
+                                    for (uint32_t u = 0; u < 4; ++u) sum[i] += part[i][u];
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < 8; ++i)
+                                if (m0 + i < p.tokens) emit(m0 + i, sum[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        umma::tc_fence_after();
+        umma::tmem_dealloc(tmem_base, kTmem);
+    }
+}
+
+// Sums the K splits' partial sums of fp8_decode_quantized_kernel when many tokens share the launch: the one CTA per row tile
+// that arrives last would need a memory round trip per eight tokens, this kernel spreads the same sums (in split order) over
+// the whole device.  One thread per (token, output row); launched as a programmatic dependent launch.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const Params p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t row = blockIdx.x * 256 + threadIdx.x, m = blockIdx.y;
+    if (row >= p.n) return;
+    const uint32_t padded_rows = p.row_tiles * kRows;
+    float sum = 0.0f;
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+        float part[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8; ++u)
+            part[u] = s0 + u < p.splits ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.tokens + m) * padded_rows + row]) : 0.0f;
+#pragma unroll
+        for (uint32_t u = 0; u < 8; ++u) sum += part[u];
+    }
+    const float v = sum * __ldg(p.x_scale + m) * p.alpha * (p.channel_scale ? p.channel_scale[row] : 1.0f);
+    const size_t index = static_cast<size_t>(m) * p.ld_out + row;
+    if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(v);
+    else static_cast<float*>(p.out)[index] = v;
 }
 
 }  // namespace decode_fp8

@@ -238,7 +238,19 @@ struct DecodePlan {
     uint8_t* act_scales;
     float* act_col_scale;
     uint32_t path;  // DecodePath: which kernel family serves one or two tokens
+    uint32_t ws_splits;  // K splits the scratch was sized for
     MapCache maps_x, maps_w;
+};
+
+// Activation of the decode GEMV in operand form: residual NVFP4 terms of up to eight tokens, written once by the producer
+// of x and read by every GEMV that consumes x.
+struct DecodeOperand {
+    uint32_t max_tokens, k;
+    uint32_t tokens, terms, cols;  // set by the last expansion: operand rows = tokens * terms, padded to cols = 16 or 32
+    uint8_t* packed;               // [32][k / 2]
+    uint8_t* sf;                   // [ceil(k / 64)][cols][16]
+    float* col_scale;              // [32]
+    CUtensorMap map16, map32;      // tiled views of `packed` with 16- and 32-row boxes
 };
 
 struct GroupedPlan {
@@ -664,9 +676,12 @@ void pick_fused_splits(uint32_t k_stages, uint32_t row_tiles, uint32_t* splits_o
 }
 
 // Shared memory the single-launch decode kernel needs for `ring` weight stages beside `per` resident activation stages.
-uint32_t fused_smem_bytes(uint32_t per, uint32_t ring) {
-    return decode::kFixedBytes + ring * (decode::kWeightTile + decode::kSfTile) + per * (decode::kActTile + decode::kActSfStage);
+uint32_t fused_smem_bytes(uint32_t per, uint32_t ring, uint32_t cols = decode::kCols) {
+    return decode::kFixedBytes + ring * (decode::kWeightTile + decode::kSfTile) +
+           per * (decode::act_tile_bytes(cols) + decode::act_sf_stage_bytes(cols));
 }
+// The prepared variant keeps the operand stages in the ring.
+uint32_t prepared_smem_bytes(uint32_t ring, uint32_t cols) { return fused_smem_bytes(ring, ring, cols); }
 
 // One (row tile, K split) item per CTA with three CTAs resident per SM: splits chosen so that the items just fill
 // 3 x SMs slots; every SM then interleaves the MMAs, activation expansion and epilogues of three independent items.
@@ -728,9 +743,30 @@ cudaError_t launch_fp8_fused_decode(const CUtensorMap& map_w, const decode_fp8::
 }  // extern "C++"
 
 extern "C++" {
-template <int TERMS, typename XT>
-cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, bool many, cudaStream_t stream) {
-    auto kernel = decode::nvfp4_decode_fused_kernel<TERMS, XT>;
+template <int COLS>
+cudaError_t launch_fp8_quantized_decode(const CUtensorMap& map_w, const CUtensorMap& map_x, const decode_fp8::Params& p, cudaStream_t stream) {
+    auto kernel = decode_fp8::fp8_decode_quantized_kernel<COLS>;
+    static std::atomic<uint8_t> configured[kMaxDevices];
+    if (cudaError_t st = opt_in_smem(configured, kernel, 76 * 1024); st != cudaSuccess) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.row_tiles * p.splits);
+    cfg.blockDim = dim3(decode_fp8::kThreads);
+    cfg.dynamicSmemBytes = decode_fp8::quantized_smem_bytes(p.ring, COLS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p);
+}
+}  // extern "C++"
+
+extern "C++" {
+template <int TERMS, typename XT, int COLS = decode::kCols, bool PREPARED = false>
+cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& p, bool many, cudaStream_t stream,
+                                const CUtensorMap* map_x = nullptr) {
+    auto kernel = decode::nvfp4_decode_fused_kernel<TERMS, XT, COLS, PREPARED>;
     static std::atomic<uint8_t> configured[kMaxDevices];
     if (cudaError_t st = opt_in_smem(configured, kernel, decode::kSmemBytes); st != cudaSuccess) return st;
     // Programmatic dependent launch: setup and the first weight requests of this kernel overlap the tail of the kernel
@@ -745,12 +781,12 @@ cudaError_t launch_fused_decode(const CUtensorMap& map_w, const decode::Params& 
     cfg.numAttrs = 1;
     if (many) {  // one item per CTA, small carve-out so that three CTAs share an SM
         cfg.gridDim = dim3(p.row_tiles * p.splits);
-        cfg.dynamicSmemBytes = fused_smem_bytes(p.per, p.ring);
+        cfg.dynamicSmemBytes = PREPARED ? prepared_smem_bytes(p.ring, COLS) : fused_smem_bytes(p.per, p.ring, COLS);
     } else {
         cfg.gridDim = dim3((static_cast<uint32_t>(sm_count()) / p.splits) * p.splits);
         cfg.dynamicSmemBytes = decode::kSmemBytes;
     }
-    return cudaLaunchKernelEx(&cfg, kernel, map_w, p);
+    return cudaLaunchKernelEx(&cfg, kernel, map_w, map_x ? *map_x : map_w, p);
 }
 }  // extern "C++"
 
@@ -773,6 +809,9 @@ DecodePlan* make_decode_plan(int kind, uint32_t max_tokens, uint32_t n, uint32_t
         pick_many_splits((k_bytes + kStageBytesK - 1) / kStageBytesK, row_tiles, &plan->many_splits, &plan->many_per, &plan->many_ring);
     uint32_t ws_splits = plan->splits > plan->fused_splits ? plan->splits : plan->fused_splits;
     if (plan->many_splits > ws_splits) ws_splits = plan->many_splits;
+    if (kind == kNvf4 && ws_splits < (k_bytes + kStageBytesK - 1) / kStageBytesK / decode::kMaxLocalStages + 1)
+        ws_splits = (k_bytes + kStageBytesK - 1) / kStageBytesK / decode::kMaxLocalStages + 1;
+    plan->ws_splits = ws_splits;
     const size_t ws = static_cast<size_t>(ws_splits) * row_tiles * kTileRows * max_tokens * sizeof(float);
     const uint32_t rows = max_tokens * plan->terms;
     bool ok = cudaMalloc(reinterpret_cast<void**>(&plan->workspace), ws) == cudaSuccess &&
@@ -905,6 +944,98 @@ cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* raw, const void* input, 
                       nullptr, c, d, weight_scale_2, beta, out_is_bf16, stream);
 }
 
+void* eider_b200_nvfp4_decode_operand_create(uint32_t max_tokens, uint32_t in_features) {
+    if (max_tokens == 0 || max_tokens > 8 || in_features == 0 || in_features % 32 != 0 || in_features / 8 > 4096) return nullptr;
+    auto* op = new DecodeOperand{};
+    op->max_tokens = max_tokens;
+    op->k = in_features;
+    const size_t packed_bytes = 32 * static_cast<size_t>(in_features / 2);
+    const size_t sf_bytes = static_cast<size_t>((in_features + 63) / 64) * 32 * 16;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&op->packed), packed_bytes) == cudaSuccess &&
+              cudaMemset(op->packed, 0, packed_bytes) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&op->sf), sf_bytes) == cudaSuccess &&
+              cudaMemset(op->sf, 0, sf_bytes) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&op->col_scale), 32 * sizeof(float)) == cudaSuccess &&
+              cudaMemset(op->col_scale, 0, 32 * sizeof(float)) == cudaSuccess &&
+              make_map(&op->map16, op->packed, 16, in_features / 2, in_features / 2, 16) == cudaSuccess &&
+              make_map(&op->map32, op->packed, 32, in_features / 2, in_features / 2, 32) == cudaSuccess;
+    if (!ok) {
+        cudaFree(op->packed); cudaFree(op->sf); cudaFree(op->col_scale);
+        delete op;
+        return nullptr;
+    }
+    return op;
+}
+
+void eider_b200_nvfp4_decode_operand_destroy(void* raw) {
+    auto* op = static_cast<DecodeOperand*>(raw);
+    if (!op) return;
+    cudaFree(op->packed); cudaFree(op->sf); cudaFree(op->col_scale);
+    delete op;
+}
+
+cudaError_t eider_b200_nvfp4_decode_operand_expand_on_stream(void* raw, const void* input, int input_is_bf16, uint32_t tokens,
+                                                             cudaStream_t stream) {
+    auto* op = static_cast<DecodeOperand*>(raw);
+    // bf16 activations carry 8 mantissa bits: four residual terms already sit below their rounding; f32 gets eight
+    const uint32_t terms = input_is_bf16 ? 4u : 8u;
+    if (!op || !input || tokens == 0 || tokens > op->max_tokens || tokens * terms > 32) return cudaErrorInvalidValue;
+    op->tokens = tokens;
+    op->terms = terms;
+    op->cols = tokens * terms <= 16 ? 16u : 32u;
+    return expand_nvfp4_terms_launch(input, input_is_bf16, op->packed, op->sf, op->col_scale, tokens, op->k, terms, op->cols, stream);
+}
+
+cudaError_t eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(void* raw, const void* operand, const uint8_t* w_values,
+                                                           const uint8_t* w_scales_tiled, float weight_scale_2, const void* c,
+                                                           void* d, float beta, int out_is_bf16, cudaStream_t stream) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    auto* op = static_cast<const DecodeOperand*>(operand);
+    if (!plan || plan->kind != kNvf4 || !op || op->tokens == 0 || op->k != plan->k || op->tokens > plan->max_tokens || !w_values ||
+        !w_scales_tiled || !d || (beta != 0.0f && !c))
+        return cudaErrorInvalidValue;
+    const CUtensorMap* map_w_p;
+    cudaError_t st = plan->maps_w.get(&map_w_p, w_values, plan->n, plan->k / 2, plan->k / 2, kTileRows);
+    if (st != cudaSuccess) return st;
+    decode::Params p{};
+    p.x_sf = op->sf;
+    p.x_col_scale = op->col_scale;
+    p.tokens = op->tokens;
+    p.n = plan->n;
+    p.k = plan->k;
+    p.k_stages = (plan->k / 2 + kStageBytesK - 1) / kStageBytesK;
+    // one (row tile, K split) item per CTA as in the expanding kernel; shapes too small for that split run unsplit or with
+    // just enough splits to keep a CTA's stage count in range (the grid may then take more than one wave)
+    p.splits = plan->many_splits ? plan->many_splits : 1;
+    p.per = (p.k_stages + p.splits - 1) / p.splits;
+    while (p.per > decode::kMaxLocalStages) {
+        ++p.splits;
+        p.per = (p.k_stages + p.splits - 1) / p.splits;
+    }
+    p.splits = (p.k_stages + p.per - 1) / p.per;  // no empty split
+    if (p.splits > plan->ws_splits) return cudaErrorInvalidValue;
+    p.ring = p.per < 4 ? p.per : 4;
+    while (p.ring > 2 && prepared_smem_bytes(p.ring, op->cols) > 74 * 1024) --p.ring;
+    p.expand_threads = 128;
+    p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
+    p.sf_w = w_scales_tiled;
+    p.sf_tile_stride = ((plan->k / 16 + 3) / 4 * 4) * 128;
+    p.out = d;
+    p.c_in = c;
+    p.ld_out = plan->n;
+    p.out_is_bf16 = out_is_bf16;
+    p.alpha = weight_scale_2;
+    p.beta = beta;
+    p.workspace = plan->workspace;
+    p.counters = plan->counters;
+    p.status = plan->status;
+    if (op->cols == 16)
+        return op->terms == 4 ? launch_fused_decode<4, uint16_t, 16, true>(*map_w_p, p, true, stream, &op->map16)
+                              : launch_fused_decode<8, uint16_t, 16, true>(*map_w_p, p, true, stream, &op->map16);
+    return op->terms == 4 ? launch_fused_decode<4, uint16_t, 32, true>(*map_w_p, p, true, stream, &op->map32)
+                          : launch_fused_decode<8, uint16_t, 32, true>(*map_w_p, p, true, stream, &op->map32);
+}
+
 /* FP8 W8A8 decode with per-token dynamic activation scales:
  * y[t][n] = (sum_k e4m3(xq[t][k]) * e4m3(w[n][k])) * s_x[t] * s_w[n] */
 cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input, int input_is_bf16, uint32_t tokens,
@@ -950,8 +1081,65 @@ cudaError_t eider_b200_fp8_linear_decode_on_stream(void* raw, const void* input,
         st = infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(static_cast<const float*>(input), plan->act_packed,
                                                                  plan->act_col_scale, tokens, plan->k, stream);
     if (st != cudaSuccess) return st;
-    return run_decode(*plan, 1, plan->act_packed, nullptr, plan->act_col_scale, tokens, weight, nullptr, channel_scale, nullptr,
-                      d, weight_scale, 0.0f, out_is_bf16, stream);
+    return eider_b200_fp8_linear_decode_quantized_on_stream(raw, plan->act_packed, plan->act_col_scale, tokens, weight, channel_scale,
+                                                            weight_scale, d, out_is_bf16, stream);
+}
+
+/* The same linear on activations that are already E4M3 codes with one scale per token (the output of the per-token
+ * quantizer, run by the producer of x or by the call above). */
+cudaError_t eider_b200_fp8_linear_decode_quantized_on_stream(void* raw, const uint8_t* x_codes, const float* x_scale, uint32_t tokens,
+                                                             const uint8_t* weight, const float* channel_scale, float weight_scale,
+                                                             void* d, int out_is_bf16, cudaStream_t stream) {
+    auto* plan = static_cast<DecodePlan*>(raw);
+    if (!plan || plan->kind != kFp8 || !x_codes || !x_scale || !weight || !d || tokens == 0 || tokens > plan->max_tokens)
+        return cudaErrorInvalidValue;
+    const uint32_t cols = tokens <= 16 ? 16u : tokens <= 32 ? 32u : 64u;
+    uint32_t ring = plan->many_per < 4 ? plan->many_per : 4;
+    while (ring > 2 && decode_fp8::quantized_smem_bytes(ring, cols) > 74 * 1024) --ring;
+    if (plan->many_splits == 0 || plan->path == kDecodeSplit || (reinterpret_cast<uintptr_t>(x_codes) & 15) != 0 || plan->k % 16 != 0 ||
+        decode_fp8::quantized_smem_bytes(ring, cols) > 74 * 1024)
+        // persistent split-K GEMM kernel in the decode orientation
+        return run_decode(*plan, 1, x_codes, nullptr, x_scale, tokens, weight, nullptr, channel_scale, nullptr, d, weight_scale, 0.0f,
+                          out_is_bf16, stream);
+    const CUtensorMap *map_w_p, *map_x_p;
+    cudaError_t st = plan->maps_w.get(&map_w_p, weight, plan->n, plan->k, plan->k, kTileRows);
+    if (st != cudaSuccess) return st;
+    st = plan->maps_x.get(&map_x_p, x_codes, tokens, plan->k, plan->k, cols);
+    if (st != cudaSuccess) return st;
+    decode_fp8::Params p{};
+    p.tokens = tokens;
+    p.n = plan->n;
+    p.k = plan->k;
+    p.k_stages = (plan->k + kStageBytesK - 1) / kStageBytesK;
+    p.splits = plan->many_splits;
+    p.per = plan->many_per;
+    p.ring = ring;
+    p.row_tiles = (plan->n + kTileRows - 1) / kTileRows;
+    p.channel_scale = channel_scale;
+    p.out = d;
+    p.ld_out = plan->n;
+    p.out_is_bf16 = out_is_bf16;
+    p.alpha = weight_scale;
+    p.workspace = plan->workspace;
+    p.counters = plan->counters;
+    p.status = plan->status;
+    p.x_scale = x_scale;
+    // more than sixteen tokens: the splits' partial sums are added up by a kernel of their own
+    p.defer_reduce = (tokens > 16 && p.splits > 1) ? 1u : 0u;
+    if (cols == 16) st = launch_fp8_quantized_decode<16>(*map_w_p, *map_x_p, p, stream);
+    else if (cols == 32) st = launch_fp8_quantized_decode<32>(*map_w_p, *map_x_p, p, stream);
+    else st = launch_fp8_quantized_decode<64>(*map_w_p, *map_x_p, p, stream);
+    if (st != cudaSuccess || !p.defer_reduce) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((plan->n + 255) / 256, tokens);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_fp8::splitk_reduce_kernel, p);
 }
 
 

@@ -325,8 +325,12 @@ __device__ __forceinline__ float2 decode_e2m1x2_fast(uint32_t byte) {
 template <typename T>
 __global__ void __launch_bounds__(kExpandThreads) expand_nvfp4_terms_kernel(const T* __restrict__ input, uint8_t* __restrict__ packed,
                                                                             uint8_t* __restrict__ scales, float* __restrict__ col_scale,
-                                                                            uint32_t k, uint32_t terms) {
+                                                                            uint32_t k, uint32_t terms, uint32_t operand_cols) {
     __shared__ float red[kExpandThreads / 32];
+    // launched as a programmatic dependent launch: the kernel after this one may start its own prologue now, and this one
+    // touches memory only after the kernel before it has finished
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t token = blockIdx.y;
     const T* src = input + static_cast<size_t>(token) * k;
     const uint32_t halves = k / 8;
@@ -386,7 +390,11 @@ __global__ void __launch_bounds__(kExpandThreads) expand_nvfp4_terms_kernel(cons
         }
         if (h < halves) {
             *reinterpret_cast<uint32_t*>(packed + static_cast<size_t>(row) * (k / 2) + h * 4) = w;
-            if ((h & 1) == 0) scales[tiled_scale_offset(row, h >> 1, k)] = sc;
+            // scale bytes: the 128 x 4 tiles of a GEMM operand, or (operand_cols != 0) the layout the single-launch decode
+            // kernel copies straight into shared memory: [64-element block][operand row][16 bytes], first four used
+            if ((h & 1) == 0)
+                scales[operand_cols ? ((static_cast<size_t>(h >> 3) * operand_cols + row) * 16 + ((h >> 1) & 3))
+                                    : tiled_scale_offset(row, h >> 1, k)] = sc;
         }
         g *= 0.25f;
         inv_g *= 4.0f;
@@ -519,22 +527,38 @@ __global__ void __launch_bounds__(256) quantize_fp8_kernel(const T* __restrict__
                                                            float* __restrict__ row_scale, uint32_t rows, uint32_t cols,
                                                            float static_scale) {
     __shared__ float red[8];
+    if (DYNAMIC) {
+        // (the dynamic quantizers are launched as programmatic dependent launches: the kernel after this one may start its
+        // prologue now, and this one touches memory only after the kernel before it has finished)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
     const uint32_t row = blockIdx.x;
     const T* src = input + static_cast<size_t>(row) * cols;
     float s = static_scale;
+    const bool vec_ok = (cols % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
     if (DYNAMIC) {
         float amax = 0.0f;
-        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-            float v = Loader<T>::load1(src + i);
-            if (isfinite(v)) amax = fmaxf(amax, fabsf(v));
+        if (vec_ok) {
+            for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+                float v[16];
+                Loader<T>::load16(src + b * 16, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (isfinite(v[i])) amax = fmaxf(amax, fabsf(v[i]));
+            }
+        } else {
+            for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+                float v = Loader<T>::load1(src + i);
+                if (isfinite(v)) amax = fmaxf(amax, fabsf(v));
+            }
         }
         amax = block_max(amax, red);
         s = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
         if (threadIdx.x == 0) row_scale[row] = s;
     }
     uint8_t* dst = q + static_cast<size_t>(row) * cols;
-    const bool vec_ok = (cols % 16 == 0) && ((reinterpret_cast<uintptr_t>(input) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
     if (vec_ok) {
         for (uint32_t b = threadIdx.x; b < cols / 16; b += blockDim.x) {
             float v[16];
@@ -567,7 +591,44 @@ __global__ void scales_to_tiled_kernel(const uint8_t* __restrict__ src, uint8_t*
 
 bool bad_scale(float s) { return !(s > 0.0f) || !isfinite(s); }
 
+template <typename Kernel, typename T>
+cudaError_t launch_dynamic_fp8(Kernel kernel, const T* input, uint8_t* q, float* row_scale, uint32_t rows, uint32_t cols, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, input, q, row_scale, rows, cols, 1.0f);
+}
+
 }  // namespace
+
+// Launcher shared with the decode plan's operand object (scale bytes in the tiled GEMM layout or, operand_cols = 16 / 32, in
+// the decode kernel's operand layout).
+cudaError_t expand_nvfp4_terms_launch(const void* input, int input_is_bf16, uint8_t* packed, uint8_t* scales, float* col_scale,
+                                      uint32_t tokens, uint32_t in_features, uint32_t terms, uint32_t operand_cols, cudaStream_t stream) {
+    if (!input || !packed || !scales || !col_scale || tokens == 0 || in_features == 0 || in_features % 16 != 0 ||
+        terms == 0 || terms > 16 || in_features / 8 > 4096 || (reinterpret_cast<uintptr_t>(input) & 15) != 0)
+        return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((in_features + kExpandChunk - 1) / kExpandChunk, tokens);
+    cfg.blockDim = dim3(kExpandThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (input_is_bf16)
+        return cudaLaunchKernelEx(&cfg, expand_nvfp4_terms_kernel<uint16_t>, static_cast<const uint16_t*>(input), packed, scales,
+                                  col_scale, in_features, terms, operand_cols);
+    return cudaLaunchKernelEx(&cfg, expand_nvfp4_terms_kernel<float>, static_cast<const float*>(input), packed, scales, col_scale,
+                              in_features, terms, operand_cols);
+}
 
 }  // namespace eider
 
@@ -635,20 +696,11 @@ cudaError_t eider_b200_nvfp4_scales_to_tiled_on_stream(const uint8_t* scales_row
 size_t eider_b200_nvfp4_scale_layout_len(size_t outer, size_t inner) { return scale_layout_len(outer, inner); }
 
 cudaError_t eider_b200_expand_nvfp4_terms_on_stream(const void* input, int input_is_bf16, uint8_t* packed,
-                                                    uint8_t* scales, float* col_scale, uint32_t tokens,
-                                                    uint32_t in_features, uint32_t terms, cudaStream_t stream) {
-    if (!input || !packed || !scales || !col_scale || tokens == 0 || in_features == 0 || in_features % 16 != 0 ||
-        terms == 0 || terms > 16 || in_features / 8 > 4096 || (reinterpret_cast<uintptr_t>(input) & 15) != 0)
-        return cudaErrorInvalidValue;
-    const dim3 grid((in_features + kExpandChunk - 1) / kExpandChunk, tokens);
-    if (input_is_bf16)
-        expand_nvfp4_terms_kernel<uint16_t><<<grid, kExpandThreads, 0, stream>>>(static_cast<const uint16_t*>(input), packed, scales,
-                                                                                 col_scale, in_features, terms);
-    else
-        expand_nvfp4_terms_kernel<float><<<grid, kExpandThreads, 0, stream>>>(static_cast<const float*>(input), packed, scales,
-                                                                              col_scale, in_features, terms);
-    return cudaGetLastError();
+                                                    uint8_t* scales, float* col_scale, uint32_t tokens, uint32_t in_features,
+                                                    uint32_t terms, cudaStream_t stream) {
+    return eider::expand_nvfp4_terms_launch(input, input_is_bf16, packed, scales, col_scale, tokens, in_features, terms, 0, stream);
 }
+
 
 cudaError_t infer_rms_norm_quantize_nvfp4_col_major_f32_on_stream(const float* input, const float* weight, uint8_t* packed,
                                                                   uint8_t* scales, uint32_t rows, uint32_t cols, float eps,
@@ -716,8 +768,7 @@ cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream(const float* inp
                                                                 float* input_scale, uint32_t rows, uint32_t cols,
                                                                 cudaStream_t stream) {
     if (!input || !quantized_input || !input_scale || rows == 0 || cols == 0) return cudaErrorInvalidValue;
-    quantize_fp8_kernel<float, true><<<rows, 256, 0, stream>>>(input, quantized_input, input_scale, rows, cols, 1.0f);
-    return cudaGetLastError();
+    return launch_dynamic_fp8(quantize_fp8_kernel<float, true>, input, quantized_input, input_scale, rows, cols, stream);
 }
 
 cudaError_t infer_quantize_fp8_e4m3_dynamic_f32_on_stream(const float* input, uint8_t* quantized_input,
@@ -729,8 +780,7 @@ cudaError_t eider_b200_quantize_fp8_e4m3_dynamic_bf16_batch_on_stream(const uint
                                                                       float* input_scale, uint32_t rows, uint32_t cols,
                                                                       cudaStream_t stream) {
     if (!input || !quantized_input || !input_scale || rows == 0 || cols == 0) return cudaErrorInvalidValue;
-    quantize_fp8_kernel<uint16_t, true><<<rows, 256, 0, stream>>>(input, quantized_input, input_scale, rows, cols, 1.0f);
-    return cudaGetLastError();
+    return launch_dynamic_fp8(quantize_fp8_kernel<uint16_t, true>, input, quantized_input, input_scale, rows, cols, stream);
 }
 
 cudaError_t infer_quantize_fp8_e4m3_f32_on_stream(const float* input, uint8_t* output, uint32_t len, float input_scale,

@@ -381,6 +381,43 @@ def fp8_linear_prequantized_simt(xq: torch.Tensor, s_x: torch.Tensor, wq: torch.
 
 
 # ---- tensor-core decode (1..64 tokens) ----------------------------------------------------------------
+class Nvfp4DecodeOperand:
+    """An activation in the operand form of the decode GEMV (residual NVFP4 terms), written once by the producer of x and read
+    by every decode linear that consumes x.  Up to eight bf16 tokens or four f32 tokens."""
+
+    def __init__(self, max_tokens: int, in_features: int):
+        lib = _lib.load()
+        self._lib = lib
+        self.max_tokens, self.k, self.tokens = max_tokens, in_features, 0
+        self._op = lib.eider_b200_nvfp4_decode_operand_create(max_tokens, in_features)
+        if not self._op:
+            raise ShapeError(f"unsupported decode operand tokens<={max_tokens} k={in_features}")
+
+    def expand(self, x: torch.Tensor) -> "Nvfp4DecodeOperand":
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        tokens, k = x.shape
+        if k != self.k or tokens > self.max_tokens or x.dtype not in (torch.float32, torch.bfloat16):
+            raise ShapeError("activation does not match the operand")
+        _need(x, x.dtype, "activation")
+        check("eider_b200_nvfp4_decode_operand_expand_on_stream",
+              self._lib.eider_b200_nvfp4_decode_operand_expand_on_stream(self._op, x.data_ptr(), int(x.dtype == torch.bfloat16),
+                                                                         tokens, _stream()))
+        self.tokens = tokens
+        return self
+
+    def close(self) -> None:
+        if self._op:
+            self._lib.eider_b200_nvfp4_decode_operand_destroy(self._op)
+            self._op = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Nvfp4DecodePlan:
     """W4A16 decode linear on tcgen05: y[t] = weight_scale_2 * W . x[t] for up to 64 tokens.  Plays the role of the
     reference's decode operators (LinearDecodeOp, crates/infer/src/qwen3/infer.rs:3385-3584; Nvfp4DeviceLinear::run_f32_into,
@@ -413,6 +450,23 @@ class Nvfp4DecodePlan:
                                                               w.packed.data_ptr(), w.scales_tiled.data_ptr(),
                                                               w.weight_scale_2, _ptr(c), out.data_ptr(), beta,
                                                               int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def run_prepared(self, operand: "Nvfp4DecodeOperand", w: ModelOptWeight, out: torch.Tensor | None = None, beta: float = 0.0,
+                     c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        """The same linear on an activation its producer has already expanded (Nvfp4DecodeOperand.expand): the GEMV only
+        copies its slice of the operand once the kernel before it has finished."""
+        if operand.k != self.k or w.in_features != self.k or w.out_features != self.n or not 0 < operand.tokens <= self.max_tokens:
+            raise ShapeError("operand shapes do not match the plan")
+        if out is None:
+            out = torch.empty(operand.tokens, self.n, dtype=out_dtype, device=w.packed.device)
+        if beta != 0.0 and c is None:
+            c = out
+        check("eider_b200_nvfp4_w4a16_gemv_prepared_on_stream",
+              self._lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(self._plan, operand._op, w.packed.data_ptr(),
+                                                                       w.scales_tiled.data_ptr(), w.weight_scale_2, _ptr(c),
+                                                                       out.data_ptr(), beta, int(out.dtype == torch.bfloat16),
+                                                                       _stream()))
         return out
 
     PATHS = {"auto": 0, "stream": 1, "fused": 2, "split": 3, "fused_many": 4}
@@ -470,6 +524,24 @@ class Fp8DecodePlan:
               self._lib.eider_b200_fp8_linear_decode_on_stream(self._plan, x.data_ptr(), int(x.dtype == torch.bfloat16), tokens,
                                                                wq.data_ptr(), _ptr(channel_scale), weight_scale,
                                                                out.data_ptr(), int(out.dtype == torch.bfloat16), _stream()))
+        return out
+
+    def run_quantized(self, x_codes: torch.Tensor, x_scale: torch.Tensor, wq: torch.Tensor, channel_scale: torch.Tensor | None,
+                      weight_scale: float = 1.0, out: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        """The same linear on activations their producer has already quantized (E4M3 codes [tokens, k] and one f32 scale per
+        token, e.g. from quantize_fp8_dynamic)."""
+        tokens, k = x_codes.shape
+        if k != self.k or wq.shape != (self.n, self.k) or tokens > self.max_tokens or x_scale.numel() < tokens:
+            raise ShapeError("operand shapes do not match the plan")
+        _need(x_codes, torch.uint8, "activation codes")
+        _need(x_scale, torch.float32, "activation scales")
+        _need(wq, torch.uint8, "weight")
+        if out is None:
+            out = torch.empty(tokens, self.n, dtype=out_dtype, device=x_codes.device)
+        check("eider_b200_fp8_linear_decode_quantized_on_stream",
+              self._lib.eider_b200_fp8_linear_decode_quantized_on_stream(self._plan, x_codes.data_ptr(), x_scale.data_ptr(), tokens,
+                                                                         wq.data_ptr(), _ptr(channel_scale), weight_scale,
+                                                                         out.data_ptr(), int(out.dtype == torch.bfloat16), _stream()))
         return out
 
     def status(self) -> int:

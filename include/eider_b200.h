@@ -270,6 +270,23 @@ EIDER_B200_API cudaError_t eider_b200_nvfp4_w4a16_gemv_on_stream(void* plan, con
                                                                  const uint8_t* w_scales_tiled, float weight_scale_2,
                                                                  const void* c, void* d, float beta, int out_is_bf16,
                                                                  cudaStream_t stream);
+/* The same GEMV with the residual expansion of x taken out of its dependency chain: the producer of x expands it once into
+ * an operand object (packed term rows, scale bytes and row scales in the layout the GEMV copies straight into shared
+ * memory), and every GEMV that consumes x (q/k/v, gate/up) only copies its K slice after the kernel before it has
+ * finished.  Up to eight bf16 tokens (four terms each) or four f32 tokens (eight terms) per operand.  No reference
+ * counterpart: the reference's W4A16 GEMV reads f32 x directly (crates/eider-cuda/src/ffi.rs:3285-3308).  The operand
+ * records the token count of its last expansion; expansion and the GEMVs that read it run in stream order. */
+EIDER_B200_API void* eider_b200_nvfp4_decode_operand_create(uint32_t max_tokens, uint32_t in_features);
+EIDER_B200_API void eider_b200_nvfp4_decode_operand_destroy(void* operand);
+EIDER_B200_API cudaError_t eider_b200_nvfp4_decode_operand_expand_on_stream(void* operand, const void* input,
+                                                                            int input_is_bf16, uint32_t tokens,
+                                                                            cudaStream_t stream);
+EIDER_B200_API cudaError_t eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(void* plan, const void* operand,
+                                                                          const uint8_t* w_values,
+                                                                          const uint8_t* w_scales_tiled,
+                                                                          float weight_scale_2, const void* c, void* d,
+                                                                          float beta, int out_is_bf16,
+                                                                          cudaStream_t stream);
 /* Supersedes infer_fp8_linear_channel_scaled_dynamic_f32_on_stream and its batch forms
  * (crates/eider-cuda/src/ffi.rs:3110-3162; kernels non_gemm.cu:9826-10011): per-token dynamic E4M3 activations,
  * per-channel (channel_scale != NULL) or per-tensor (weight_scale) weight scales. */
@@ -278,6 +295,15 @@ EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_on_stream(void* plan, co
                                                                   uint32_t tokens, const uint8_t* weight,
                                                                   const float* channel_scale, float weight_scale, void* d,
                                                                   int out_is_bf16, cudaStream_t stream);
+/* The same linear on activations that are already E4M3 codes [tokens][in_features] with one scale per token: the output
+ * of the per-token quantizer (infer_quantize_fp8_e4m3_dynamic_f32_batch_on_stream, crates/eider-cuda/src/ffi.rs:3206),
+ * run by the producer of x.  The call above is this one behind that quantizer.  No reference counterpart as an entry
+ * point: the reference's FP8 linears quantize inside (crates/eider-cuda/native/non_gemm.cu:9826-10011). */
+EIDER_B200_API cudaError_t eider_b200_fp8_linear_decode_quantized_on_stream(void* plan, const uint8_t* x_codes,
+                                                                            const float* x_scale, uint32_t tokens,
+                                                                            const uint8_t* weight, const float* channel_scale,
+                                                                            float weight_scale, void* d, int out_is_bf16,
+                                                                            cudaStream_t stream);
 EIDER_B200_API void eider_b200_decode_destroy(void* plan);
 EIDER_B200_API cudaError_t eider_b200_decode_plan_status(void* plan, uint32_t* host_status);
 /* Kernel family for a few tokens of an NVFP4 decode plan: 0 = automatic (the single-launch tcgen05 kernel, one work item

@@ -66,6 +66,41 @@ def test_nvfp4_w4a16_decode(ops, oracle, tokens, n, k, dtype):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("tokens,n,k", [(1, 128, 256), (1, 13824, 5120), (1, 5120, 13824), (2, 640, 1056), (3, 1000, 2048),
+                                        (4, 1024, 2080), (5, 5120, 13824), (8, 13824, 5120)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_nvfp4_w4a16_decode_on_prepared_operand(ops, oracle, tokens, n, k, dtype):
+    # the producer of x expands it once (operand object); the GEMV copies its slice instead of expanding it itself
+    import torch
+    if dtype == "f32" and tokens > 4:
+        pytest.skip("eight terms x more than four tokens do not fit the 32 operand rows")
+    rng = np.random.default_rng(tokens * 3 + n + k)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    packed, scales, g = oracle.quantize_weight(w)
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    wd = ops.ModelOptWeight.from_checkpoint(_dev(packed), _dev(scales), float(g))
+    plan = ops.Nvfp4DecodePlan(8, n, k)
+    operand = ops.Nvfp4DecodeOperand(8, k)
+    xd = _dev(x, torch.bfloat16 if dtype == "bf16" else None)
+    y = plan.run_prepared(operand.expand(xd), wd, out_dtype=torch.float32)
+    y2 = plan.run_prepared(operand, wd, out_dtype=torch.float32)  # the operand serves several GEMVs; counters self-reset
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    ref = oracle.nvfp4_linear_host(x, packed, scales, float(g))
+    tol = 2e-3 if dtype == "bf16" else 1e-4
+    ok, stats = gemm_close(to_np(y), ref, rel=tol, abs_frac=tol)
+    assert ok, stats
+    assert torch.equal(y, y2)
+    # a smaller batch through the same operand afterwards (rows of the earlier, larger batch are left behind it)
+    if tokens > 1:
+        y1 = plan.run_prepared(operand.expand(xd[:1].contiguous()), wd, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        ok, stats = gemm_close(to_np(y1), ref[:1], rel=tol, abs_frac=tol)
+        assert ok, stats
+
+
 def test_nvfp4_decode_terms_follow_the_call_not_the_plan(ops, oracle):
     # a plan made for 64 tokens still gives f32 activations eight residual terms when the call's tokens fit
     import torch
@@ -121,6 +156,34 @@ def test_fp8_decode_qkv(ops, oracle, tokens):
     ref = oracle.fp8_linear(xq, xs, wq, ws)
     ok, stats = gemm_close(to_np(y), ref)
     assert ok, stats
+
+
+@pytest.mark.parametrize("tokens,n,k", [(1, 7168, 5120), (5, 7168, 5120), (16, 1000, 528), (17, 7168, 5120), (33, 640, 2064), (64, 7168, 5120)])
+def test_fp8_decode_on_quantized_activations(ops, oracle, tokens, n, k):
+    # the producer of x runs the per-token quantizer; the GEMV takes its codes and scales (and equals the call that
+    # quantizes for itself, bit for bit, wherever that call takes the same route)
+    import torch
+    rng = np.random.default_rng(tokens * 5 + n)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = oracle.bf16_round(rng.standard_normal((tokens, k)).astype(np.float32))
+    wq, ws = oracle.quantize_fp8_weight(w)
+    xq_ref, xs_ref = oracle.quantize_fp8_dynamic(x)
+    xd = _dev(x, torch.bfloat16)
+    xq, xs = ops.quantize_fp8_dynamic(xd)
+    assert np.array_equal(to_np(xq), xq_ref) and np.array_equal(to_np(xs), xs_ref)
+    wqd, wsd = _dev(wq), _dev(ws)
+    plan = ops.Fp8DecodePlan(64, n, k)
+    y = plan.run_quantized(xq, xs, wqd, wsd, out_dtype=torch.float32)
+    y2 = plan.run_quantized(xq, xs, wqd, wsd, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert plan.status() == 0
+    ok, stats = gemm_close(to_np(y), oracle.fp8_linear(xq_ref, xs_ref, wq, ws), rel=1e-4, abs_frac=1e-4)
+    assert ok, stats
+    assert torch.equal(y, y2)
+    if tokens > 4:
+        y3 = plan.run(xd, wqd, wsd, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y3)
 
 
 def test_fp8_decode_small_and_scalar_scale(ops, oracle):
