@@ -740,12 +740,16 @@ def run_prefill(args):
             plan_full.run(xq, full_w[i % 4], out=y_full)
 
         single_ms = timed_graph(single_step, steps) / steps
+        single_gemm_ms = timed_graph(lambda i: plan_full.run(xq, full_w[i % 4], out=y_full), steps) / steps
         nvlink_bound_us = (world - 1) / world * 2.0 * M * N / 770e9 * 1e6
         detail = {"step_us": ms_per_step * 1e3, "gemm_us": gemm_ms * 1e3, "gemm_without_peer_stores_us": gemm_local_ms * 1e3,
                   "quantize_us": quant_ms * 1e3, "barrier_us": barrier_ms * 1e3,
                   "other_us": (ms_per_step - gemm_ms - quant_ms - barrier_ms) * 1e3,
                   "single_gpu_step_us": single_ms * 1e3,
                   "compute_only_speedup": single_ms / (gemm_local_ms + quant_ms),
+                  # the activation quantizer is replicated on every rank (each needs all of x); the GEMM alone:
+                  "single_gpu_gemm_us": single_gemm_ms * 1e3,
+                  "gemm_only_speedup": single_gemm_ms / gemm_local_ms,
                   "end_to_end_speedup": single_ms / ms_per_step,
                   "nvlink_bound_us": nvlink_bound_us,
                   "nvlink_bound_note": f"every rank receives (g-1)/g * 2MN = {(world - 1) / world * 2.0 * M * N / 1e6:.1f} MB per step; "
