@@ -257,6 +257,11 @@ struct GroupedPlan {
     uint32_t m, max_n, k, groups;  // reference naming: m = out features per expert, max_n = max tokens per expert
     uint32_t* status;
     MapCache maps_a, maps_w;
+    // pointer-table entry point: two host-encoded template maps, per-group maps patched on the device, row offsets
+    CUtensorMap* templates;   // [2] device copies: rows of a group (box 128 rows), weights of a group (box = column tile)
+    CUtensorMap* group_maps;  // [2 * groups]
+    uint32_t* offsets;        // [groups + 1] exclusive scan of the per-group row counts of the last call
+    CUtensorMap host_templates[2];
 };
 
 namespace {
@@ -455,6 +460,86 @@ cudaError_t run_decode(DecodePlan& plan, uint32_t terms, const uint8_t* x_values
         default: return EIDER_DECODE(kFp8, 256, 1);
     }
 #undef EIDER_DECODE
+}
+
+// Pointer-table form: one warp per group copies the two template maps into shared memory, replaces their addresses with
+// the group's table entries (and the row extent with the group's row count, so a row tile that hangs over the end reads
+// zeros instead of whatever lies behind the group's buffer) and publishes them; thread 0 of the grid writes the
+// exclusive scan of the row counts the GEMM walks.
+constexpr uint32_t kMapWarps = 8;
+__global__ void __launch_bounds__(kMapWarps * 32) grouped_maps_kernel(const CUtensorMap* __restrict__ templates, CUtensorMap* __restrict__ maps,
+                                                                    const uint8_t* const* __restrict__ row_values,
+                                                                    const uint8_t* const* __restrict__ col_values,
+                                                                    const uint32_t* __restrict__ rows_per_group, uint32_t* __restrict__ offsets,
+                                                                    uint32_t groups) {
+    __shared__ __align__(128) CUtensorMap staged[kMapWarps][2];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t g = blockIdx.x * kMapWarps + warp;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        uint32_t sum = 0;
+        for (uint32_t i = 0; i < groups; ++i) {
+            offsets[i] = sum;
+            sum += rows_per_group[i];
+        }
+        offsets[groups] = sum;
+    }
+    if (g >= groups) return;  // (warp-uniform)
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(templates);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&staged[warp][0]);
+    dst[lane] = src[lane];
+    dst[lane + 32] = src[lane + 32];
+    __syncwarp();
+    if (lane == 0) {
+        const uint32_t rows = rows_per_group[g];
+        umma::tensormap_replace_address(&staged[warp][0], row_values[g]);
+        umma::tensormap_replace_rows(&staged[warp][0], rows ? rows : 1u);
+        umma::tensormap_replace_address(&staged[warp][1], col_values[g]);
+    }
+    __syncwarp();
+    umma::tensormap_publish(maps + 2 * g, &staged[warp][0]);
+    umma::tensormap_publish(maps + 2 * g + 1, &staged[warp][1]);
+}
+
+cudaError_t run_grouped_tables(GroupedPlan& plan, const uint8_t* const* a_values, const uint8_t* const* a_scales,
+                               const uint8_t* const* b_values, const uint8_t* const* b_scales, uint16_t* const* output,
+                               const float* const* alpha, const uint32_t* tokens_per_expert, cudaStream_t stream) {
+    if (!a_values || !a_scales || !b_values || !b_scales || !output || !alpha || !tokens_per_expert || !plan.group_maps)
+        return cudaErrorInvalidValue;
+    grouped_maps_kernel<<<(plan.groups + kMapWarps - 1) / kMapWarps, kMapWarps * 32, 0, stream>>>(
+        plan.templates, plan.group_maps, a_values, b_values, tokens_per_expert, plan.offsets, plan.groups);
+    cudaError_t st = cudaGetLastError();
+    if (st != cudaSuccess) return st;
+    const uint32_t k_bytes = plan.k / 2;
+    Params p{};
+    p.rows = plan.groups * plan.max_n;
+    p.cols = plan.groups * plan.m;
+    p.k_bytes = k_bytes;
+    p.k_stages = (k_bytes + kStageBytesK - 1) / kStageBytesK;
+    p.sf_tile_stride = ((plan.k / 16 + 3) / 4 * 4) * 128;
+    p.out = nullptr;
+    p.ld_out = plan.m;
+    p.out_is_bf16 = 1;
+    p.alpha = 1.0f;
+    p.out_cols = plan.m;
+    p.splits = 1;
+    p.group_offsets = plan.offsets;
+    p.groups = plan.groups;
+    p.group_cols = plan.m;
+    p.status = plan.status;
+    p.group_maps = plan.group_maps;
+    p.tbl_row_scales = a_scales;
+    p.tbl_col_scales = b_scales;
+    p.tbl_out = output;
+    p.tbl_alpha = alpha;
+    // upper bound on work items: every group can hold max_n rows
+    const uint32_t max_row_tiles = plan.groups * ((plan.max_n + kTileRows - 1) / kTileRows);
+    // (the kernel's own map arguments are only prefetched on this path; it loads through the per-group maps)
+    if (plan.m % 256 == 0) {
+        p.col_tiles = plan.m / 256;
+        return launch<kNvf4, 256, false, 1, true>(plan.host_templates[0], plan.host_templates[1], p, max_row_tiles * p.col_tiles, stream);
+    }
+    p.col_tiles = plan.m / 128;
+    return launch<kNvf4, 128, false, 1, true>(plan.host_templates[0], plan.host_templates[1], p, max_row_tiles * p.col_tiles, stream);
 }
 
 cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
@@ -1243,7 +1328,7 @@ int eider_b200_nvfp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t
 
 void* eider_b200_nvfp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
     if (!eider_b200_nvfp4_grouped_gemm_supported(m, max_n, k, groups)) return nullptr;
-    auto* plan = new GroupedPlan{m, max_n, k, groups, nullptr, {}, {}};
+    auto* plan = new GroupedPlan{m, max_n, k, groups, nullptr, {}, {}, nullptr, nullptr, nullptr, {}};
     if (alloc_status(&plan->status) != cudaSuccess) {
         delete plan;
         return nullptr;
@@ -1251,10 +1336,51 @@ void* eider_b200_nvfp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t 
     return plan;
 }
 
+/* crates/eider-cuda/src/ffi.rs:643-667: the reference's grouped GEMM over device pointer tables.  The plan additionally owns
+ * the per-group tensor maps that a small kernel patches from the tables in front of every GEMM. */
+int infer_cutlass_fp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
+    return (eider_b200_nvfp4_grouped_gemm_supported(m, max_n, k, groups) && groups <= 4096) ? 1 : 0;
+}
+
+void* infer_cutlass_fp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups) {
+    if (!infer_cutlass_fp4_grouped_gemm_supported(m, max_n, k, groups)) return nullptr;
+    auto* plan = static_cast<GroupedPlan*>(eider_b200_nvfp4_grouped_gemm_create(m, max_n, k, groups));
+    if (!plan) return nullptr;
+    CUtensorMap* host_templates = plan->host_templates;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&plan->group_maps), 2 * static_cast<size_t>(groups) * sizeof(CUtensorMap)) == cudaSuccess &&
+              cudaMemset(plan->group_maps, 0, 2 * static_cast<size_t>(groups) * sizeof(CUtensorMap)) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&plan->templates), 2 * sizeof(CUtensorMap)) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&plan->offsets), (static_cast<size_t>(groups) + 1) * sizeof(uint32_t)) == cudaSuccess &&
+              // (any mapped, 16-byte aligned address encodes; every use replaces it)
+              make_map(&host_templates[0], plan->group_maps, max_n, k / 2, k / 2, kTileRows) == cudaSuccess &&
+              make_map(&host_templates[1], plan->group_maps, m, k / 2, k / 2, m % 256 == 0 ? 256 : 128) == cudaSuccess &&
+              cudaMemcpy(plan->templates, host_templates, 2 * sizeof(CUtensorMap), cudaMemcpyHostToDevice) == cudaSuccess;
+    if (!ok) {
+        eider_b200_nvfp4_grouped_gemm_destroy(plan);
+        return nullptr;
+    }
+    return plan;
+}
+
+void infer_cutlass_fp4_grouped_gemm_destroy(void* plan) { eider_b200_nvfp4_grouped_gemm_destroy(plan); }
+
+cudaError_t infer_cutlass_fp4_grouped_gemm_on_stream(void* raw, const uint8_t* const* a_values, const uint8_t* const* a_scales,
+                                                     const uint8_t* const* b_values, const uint8_t* const* b_scales,
+                                                     uint16_t* const* output, float* const* alpha, const uint32_t* tokens_per_expert,
+                                                     cudaStream_t stream) {
+    auto* plan = static_cast<GroupedPlan*>(raw);
+    if (!plan) return cudaErrorInvalidValue;
+    return run_grouped_tables(*plan, a_values, a_scales, b_values, b_scales, output, const_cast<const float* const*>(alpha),
+                              tokens_per_expert, stream);
+}
+
 void eider_b200_nvfp4_grouped_gemm_destroy(void* raw) {
     auto* plan = static_cast<GroupedPlan*>(raw);
     if (!plan) return;
     cudaFree(plan->status);
+    cudaFree(plan->group_maps);
+    cudaFree(plan->templates);
+    cudaFree(plan->offsets);
     delete plan;
 }
 

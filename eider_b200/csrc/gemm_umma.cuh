@@ -82,6 +82,14 @@ struct Params {
     uint8_t* act_packed;
     uint8_t* act_scales;
     uint32_t act_tile_bytes;
+    // Pointer-table form of the grouped GEMM (null: base pointers + offsets).  Every group has its own operand, scale,
+    // output and alpha pointers in device arrays; `group_maps` holds per-group tensor maps (rows of group g at [2g], its
+    // weights at [2g + 1]) whose addresses a preceding kernel has patched in from the tables.  `out` is null on this path.
+    const CUtensorMap* group_maps;
+    const uint8_t* const* tbl_row_scales;
+    const uint8_t* const* tbl_col_scales;
+    uint16_t* const* tbl_out;
+    const float* const* tbl_alpha;
 };
 
 // Calls f(base) for every output buffer of the launch.
@@ -362,7 +370,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             TileCoord t;
             bool ok = true;
             bool dep_waited = false;
+            uint32_t maps_group = 0xffffffffu;  // pointer tables: the group whose tensor maps this thread has acquired
             for (uint32_t item = blockIdx.x; ok && get_tile<BLOCK_N, TERMS, GROUPED>(p, item, walker, t); item += gridDim.x) {
+                // scale tiles past the end of the column operand do not exist in memory: their rows are
+                // zero-filled by the TMA and their outputs are never stored, so the copy is skipped
+                const uint32_t sf_col_tiles = (p.cols + kTileRows - 1) / kTileRows;
+                const uint32_t sf_col_tile0 = t.col0 / kTileRows;
+                bool second_sf = BLOCK_N > 128 && (sf_col_tile0 + 1 < sf_col_tiles);
+                const CUtensorMap* mrow = &map_rows;
+                const CUtensorMap* mcol = &map_cols;
+                int32_t row_coord = static_cast<int32_t>(t.row0), col_coord = static_cast<int32_t>(t.col0);
+                const uint8_t* sf_row_ptr = kNv ? p.sf_rows + static_cast<size_t>(t.sf_row_tile) * p.sf_tile_stride : nullptr;
+                const uint8_t* sf_col_ptr = kNv ? p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride : nullptr;
+                if constexpr (GROUPED) if (p.group_maps) {
+                    // pointer tables: the group's own tensors, coordinates relative to them
+                    mrow = p.group_maps + 2 * t.group;
+                    mcol = mrow + 1;
+                    row_coord = static_cast<int32_t>(t.row0 - t.group_row0);
+                    col_coord = static_cast<int32_t>(t.out_col0);
+                    sf_row_ptr = p.tbl_row_scales[t.group] + static_cast<size_t>((t.row0 - t.group_row0) / kTileRows) * p.sf_tile_stride;
+                    sf_col_ptr = p.tbl_col_scales[t.group] + static_cast<size_t>(t.out_col0 / kTileRows) * p.sf_tile_stride;
+                    second_sf = BLOCK_N > 128 && (t.out_col0 / kTileRows + 1 < p.group_cols / kTileRows);
+                    if (leader && maps_group != t.group) {
+                        // the maps were written by another kernel through the tensor-map proxy
+                        umma::tensormap_fence_acquire(mrow);
+                        umma::tensormap_fence_acquire(mcol);
+                        maps_group = t.group;
+                    }
+                }
                 for (uint32_t s = t.k_stage0; s < t.k_stage1; ++s, ++it) {
                     const uint32_t stage = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
@@ -370,11 +405,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     if (!leader) continue;
                     const uint32_t kb = min(4u, (p.k_bytes - s * kStageBytesK + 31) / 32);  // MMAs in this stage
                     uint32_t bytes = L::kA + L::kB;
-                    // scale tiles past the end of the column operand do not exist in memory: their rows are
-                    // zero-filled by the TMA and their outputs are never stored, so the copy is skipped
-                    const uint32_t sf_col_tiles = (p.cols + kTileRows - 1) / kTileRows;
-                    const uint32_t sf_col_tile0 = t.col0 / kTileRows;
-                    const bool second_sf = BLOCK_N > 128 && (sf_col_tile0 + 1 < sf_col_tiles);
                     if (kNv) bytes += kb * kScaleTileBytes * (2 + (second_sf ? 1 : 0));
                     umma::mbar_arrive_expect_tx(&full[stage], bytes);
                     const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
@@ -382,23 +412,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     // quantizer): under a programmatic dependent launch the weight side of the first stage is
                     // requested before the dependency is awaited.
                     auto load_rows = [&]() {
-                        umma::tma_load_2d(smem_a + stage * L::kA, &map_rows, &full[stage], static_cast<int32_t>(s * kStageBytesK),
-                                          static_cast<int32_t>(t.row0));
-                        if (kNv)
-                            umma::bulk_load_1d(smem_sfa + stage * L::kSfA,
-                                               p.sf_rows + static_cast<size_t>(t.sf_row_tile) * p.sf_tile_stride + k_off,
-                                               kb * kScaleTileBytes, &full[stage]);
+                        umma::tma_load_2d(smem_a + stage * L::kA, mrow, &full[stage], static_cast<int32_t>(s * kStageBytesK), row_coord);
+                        if (kNv) umma::bulk_load_1d(smem_sfa + stage * L::kSfA, sf_row_ptr + k_off, kb * kScaleTileBytes, &full[stage]);
                     };
                     auto load_cols = [&]() {
-                        umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
-                                          static_cast<int32_t>(t.col0));
+                        umma::tma_load_2d(smem_b + stage * L::kB, mcol, &full[stage], static_cast<int32_t>(s * kStageBytesK), col_coord);
                         if (kNv) {
-                            umma::bulk_load_1d(smem_sfb + stage * L::kSfB,
-                                               p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
-                                               kb * kScaleTileBytes, &full[stage]);
+                            umma::bulk_load_1d(smem_sfb + stage * L::kSfB, sf_col_ptr + k_off, kb * kScaleTileBytes, &full[stage]);
                             if (second_sf)
-                                umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes,
-                                                   p.sf_cols + static_cast<size_t>(sf_col_tile0 + 1) * p.sf_tile_stride + k_off,
+                                umma::bulk_load_1d(smem_sfb + stage * L::kSfB + 4 * kScaleTileBytes, sf_col_ptr + p.sf_tile_stride + k_off,
                                                    kb * kScaleTileBytes, &full[stage]);
                         }
                     };
@@ -518,6 +540,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             const bool row_ok = row < t.row_end;
             float rs = GROUPED ? (p.group_alpha ? p.group_alpha[t.group] : p.alpha) : p.alpha;
             if (p.row_scale && row_ok) rs *= p.row_scale[row];
+            size_t row_elems = static_cast<size_t>(row) * p.ld_out;  // element offset of this thread's output row from `out`
+            bool out_aligned32 = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+            if constexpr (GROUPED) if (p.group_maps) {
+                // pointer tables: the group's own output buffer and alpha; `out` is null, so the offset carries the address
+                const uintptr_t base = reinterpret_cast<uintptr_t>(p.tbl_out[t.group]);
+                row_elems = base / 2 + static_cast<size_t>(row - t.group_row0) * p.ld_out;
+                out_aligned32 = (base & 31) == 0;
+                rs = *p.tbl_alpha[t.group];
+            }
             const uint32_t buf = T::kOverlap ? (tile_count & 1) : acc;
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * T::kAccStride;
             // Fast path (warp-uniform test): a full-width bf16 tile with no column scale and no C input.  64 columns
@@ -527,7 +558,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             if constexpr (kWide) {
                 const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
                 wide = p.out_is_bf16 && (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0 && !(p.beta != 0.0f && p.c_in) && !empty_tile &&
-                       t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
+                       t.out_col0 + BLOCK_N <= ncols && (p.ld_out % 16) == 0 && out_aligned32;
             }
             if constexpr (GROUPED && kWide) if (p.act_packed) {
                 // SiLU * up -> NVFP4 epilogue.  A rolled loop over the 64-column steps: the per-step body (32 activations and
@@ -563,7 +594,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             }
             if constexpr (kWide) if (wide) {
                 constexpr uint32_t kSteps = BLOCK_N / 64;
-                const size_t row_offset = static_cast<size_t>(row) * p.ld_out + t.out_col0;
+                const size_t row_offset = row_elems + t.out_col0;
                 uint32_t raw[2][64];
                 auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (BLOCK_N - 64 - step * 64) : step * 64; };
                 auto issue = [&](uint32_t step, uint32_t (&r)[64]) {
@@ -630,7 +661,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     const uint32_t ncols = GROUPED ? p.group_cols : p.cols;
                     const uint32_t col0 = t.out_col0 + c;
                     if (row_ok && col0 < ncols) {
-                        const size_t index = static_cast<size_t>(row) * p.ld_out + col0;
+                        const size_t index = row_elems + col0;
                         const bool full_chunk = (col0 + 32 <= ncols) && (kChunk == 32);
                         const bool aligned = p.out_is_bf16 ? ((index % 8) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
                                                            : ((index % 4) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0);

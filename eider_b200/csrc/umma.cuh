@@ -86,6 +86,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---- TMA ------------------------------------------------------------------------------------
+// ---- tensor maps patched on the device ---------------------------------------------------------------------------
+// A tensor map encoded on the host can have its global address (and extents) replaced in a shared-memory copy, which is
+// then published to global memory through the tensor-map proxy; a thread that later hands that global copy to the TMA
+// first acquires it.
+__device__ __forceinline__ void tensormap_replace_address(void* smem_map, const void* address) {
+    asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(smem_u32(smem_map)),
+                 "l"(reinterpret_cast<uint64_t>(address))
+                 : "memory");
+}
+__device__ __forceinline__ void tensormap_replace_rows(void* smem_map, uint32_t rows) {  // extent of dimension 1 of a 2-D map
+    asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 1, %1;" ::"r"(smem_u32(smem_map)), "r"(rows) : "memory");
+}
+// (executed by a whole warp)
+__device__ __forceinline__ void tensormap_publish(void* global_map, void* smem_map) {
+    asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;" ::"l"(
+                     reinterpret_cast<uint64_t>(global_map)),
+                 "r"(smem_u32(smem_map))
+                 : "memory");
+}
+__device__ __forceinline__ void tensormap_fence_acquire(const void* global_map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(global_map)) : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

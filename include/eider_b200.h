@@ -446,6 +446,20 @@ EIDER_B200_API cudaError_t eider_b200_nvfp4_grouped_gemm_silu_quantize_on_stream
     void* plan, const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values_interleaved,
     const uint8_t* w_scales_tiled_interleaved, const float* alpha, const uint32_t* expert_offsets, uint32_t total_routes,
     uint8_t* packed, uint8_t* scales, uint32_t scale_tile_bytes, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:643-667 (CutlassFp4GroupedGemmPlan, crates/eider-cuda/src/cublaslt/fp4_tn.rs:1160-1278): the
+ * same grouped GEMM over device arrays of device pointers, one entry per group: packed rows and their 128 x 4 scale tiles,
+ * packed weights [m][k / 2] and their scale tiles, bf16 output [rows of the group][m], a pointer to the group's alpha, and
+ * the row count of every group (at most max_n).  In front of the GEMM a small kernel patches one tensor map per group and
+ * operand from the tables (tensormap.replace), so nothing is read back to the host and the call can be captured. */
+EIDER_B200_API int infer_cutlass_fp4_grouped_gemm_supported(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups);
+EIDER_B200_API void* infer_cutlass_fp4_grouped_gemm_create(uint32_t m, uint32_t max_n, uint32_t k, uint32_t groups);
+EIDER_B200_API void infer_cutlass_fp4_grouped_gemm_destroy(void* plan);
+EIDER_B200_API cudaError_t infer_cutlass_fp4_grouped_gemm_on_stream(void* plan, const uint8_t* const* a_values,
+                                                                    const uint8_t* const* a_scales,
+                                                                    const uint8_t* const* b_values,
+                                                                    const uint8_t* const* b_scales, uint16_t* const* output,
+                                                                    float* const* alpha, const uint32_t* tokens_per_expert,
+                                                                    cudaStream_t stream);
 EIDER_B200_API cudaError_t eider_b200_grouped_plan_status(void* plan, uint32_t* host_status);
 /* crates/eider-cuda/src/ffi.rs:1931 (kernel non_gemm.cu:3735-3780): un-permute + weighted sum, f32 [rows][len]. */
 EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream(

@@ -222,6 +222,59 @@ def test_grouped_pointer_tables(lib):
                                                           tables[1].data_ptr(), tables[2].data_ptr(), experts, k, n, tile, None) == 1
 
 
+@pytest.mark.parametrize("tokens,experts,top_k,hidden,out_features", [(64, 6, 2, 256, 384), (300, 16, 4, 512, 256), (1024, 32, 8, 2048, 1536)])
+def test_reference_grouped_gemm_over_pointer_tables(lib, oracle, tokens, experts, top_k, hidden, out_features):
+    # crates/eider-cuda/src/ffi.rs:643-667 (CutlassFp4GroupedGemmPlan::run_on_stream, cublaslt/fp4_tn.rs:1218-1262): seven
+    # device arrays of per-expert pointers and counts.  The row / scale / output tables come from the reference's own
+    # table kernel, the weight tables from the stacked checkpoint tensors; the result must equal the base-pointer form of
+    # the same GEMM bit for bit, and sampled experts are checked against the host product.
+    import torch
+    from eider_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(tokens + experts)
+    x = torch.randn(tokens, hidden, device="cuda", generator=g)
+    logits = torch.randn(tokens, experts, device="cuda", generator=g)
+    logits[:, 1] = -50.0  # an expert that receives nothing
+    w = ops.GroupedNvfp4Weights.quantize(torch.randn(experts, out_features, hidden, device="cuda", generator=g) * 0.02)
+    idx, _ = ops.moe_topk(logits, top_k, True)
+    routes = ops.MoeSortedRoutes(tokens * top_k, experts)
+    routes.sort(idx.reshape(-1))
+    rows = ops.MoeSortedNvfp4Rows(tokens * top_k, experts, hidden, tokens)
+    rows.gather_quantize(x, routes, top_k)
+    plan = ops.Fp4GroupedGemmPlan(out_features, tokens * top_k, hidden, experts)
+    want = plan.run(rows, w, routes)
+    torch.cuda.synchronize()
+
+    n_routes = tokens * top_k
+    got = torch.full((n_routes, out_features), 7.0, dtype=torch.bfloat16, device="cuda")
+    z = lambda: torch.zeros(experts, dtype=torch.int64, device="cuda")
+    a_tbl, as_tbl, out_tbl = z(), z(), z()
+    assert lib.infer_moe_grouped_pointer_tables_on_stream(routes.expert_offsets.data_ptr(), rows.packed.data_ptr(), rows.scales.data_ptr(),
+                                                          got.data_ptr(), a_tbl.data_ptr(), as_tbl.data_ptr(), out_tbl.data_ptr(), experts,
+                                                          hidden, out_features, rows.tile_bytes, None) == 0
+    sf_per_expert = (out_features // 128) * 128 * ((hidden // 16 + 3) // 4 * 4)
+    e_ids = torch.arange(experts, device="cuda", dtype=torch.int64)
+    b_tbl = w.packed.data_ptr() + e_ids * (out_features * hidden // 2)
+    bs_tbl = w.scales_tiled.data_ptr() + e_ids * sf_per_expert
+    alpha_tbl = w.alpha.data_ptr() + e_ids * 4
+    counts = routes.expert_counts
+    assert lib.infer_cutlass_fp4_grouped_gemm_supported(out_features, n_routes, hidden, experts) == 1
+    tplan = lib.infer_cutlass_fp4_grouped_gemm_create(out_features, n_routes, hidden, experts)
+    assert tplan
+    try:
+        for _ in range(2):  # the per-group maps are rewritten by every call
+            st = lib.infer_cutlass_fp4_grouped_gemm_on_stream(tplan, a_tbl.data_ptr(), as_tbl.data_ptr(), b_tbl.data_ptr(), bs_tbl.data_ptr(),
+                                                              out_tbl.data_ptr(), alpha_tbl.data_ptr(), counts.data_ptr(), None)
+            assert st == 0
+        torch.cuda.synchronize()
+        status = ctypes.c_uint32(1)
+        assert lib.eider_b200_grouped_plan_status(tplan, ctypes.byref(status)) == 0 and status.value == 0
+    finally:
+        lib.infer_cutlass_fp4_grouped_gemm_destroy(tplan)
+    assert torch.equal(got, want)
+    assert lib.infer_cutlass_fp4_grouped_gemm_on_stream(None, a_tbl.data_ptr(), as_tbl.data_ptr(), b_tbl.data_ptr(), bs_tbl.data_ptr(),
+                                                        out_tbl.data_ptr(), alpha_tbl.data_ptr(), counts.data_ptr(), None) == 1
+
+
 @pytest.mark.parametrize("m,k", [(13824, 5120), (5120, 13824), (300, 96)])
 def test_reference_w4a4_gemv_f32(lib, oracle, m, k):
     # crates/eider-cuda/src/ffi.rs:576-588 (test crates/eider-cuda/src/cublaslt/fp4_tn.rs:1652-1712): both operands NVFP4,
