@@ -81,6 +81,8 @@ SIGNATURES = {
     "eider_b200_nvfp4_w4a16_gemv_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _P, _F, _I, _P]),
     "eider_b200_fp8_linear_decode_on_stream": (_I, [_P, _P, _I, _U32, _P, _P, _F, _P, _I, _P]),
     "eider_b200_fp8_linear_decode_quantized_on_stream": (_I, [_P, _P, _P, _U32, _P, _P, _F, _P, _I, _P]),
+    "infer_nvfp4_w4a16_matvec_f32_warp_rows_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _U32, _P]),
+    "infer_nvfp4_w4a16_reuse_matvec_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
     "infer_cutlass_fp4_grouped_gemm_supported": (_I, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_create": (_P, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_destroy": (None, [_P]),

@@ -52,6 +52,7 @@ struct GroupedArgs {
     float* const* y_table;            // [groups] outputs [n] (null: y_flat + g * n)
     float* y_flat;
     uint32_t table_len, groups, n, k;
+    const uint32_t* route_ids = nullptr;  // kTableF32: when set, slot g reads input (and writes output) route_ids[g] of the tables
 };
 
 // grid = (ceil(n / kWarps), groups); k % 32 == 0.
@@ -72,7 +73,8 @@ __global__ void __launch_bounds__(kWarps * 32) grouped_gemv_kernel(const Grouped
             xs[xs_index(e / 32, e % 32 + 1)] = __fmul_rn(e2m1_value(byte >> 4), s);
         }
     } else {
-        const float* x = XMODE == kTableF32 ? static_cast<const float* const*>(a.x)[group] : static_cast<const float*>(a.x);
+        const uint32_t x_slot = (XMODE == kTableF32 && a.route_ids) ? __ldg(a.route_ids + group) : group;
+        const float* x = XMODE == kTableF32 ? static_cast<const float* const*>(a.x)[x_slot] : static_cast<const float*>(a.x);
         for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) xs[xs_index(i / 32, i % 32)] = __ldg(x + i);
     }
     __syncthreads();
@@ -97,7 +99,8 @@ __global__ void __launch_bounds__(kWarps * 32) grouped_gemv_kernel(const Grouped
     }
     acc = warp_sum(acc);
     if (lane == 0) {
-        float* y = a.y_table ? a.y_table[group] : a.y_flat + static_cast<size_t>(group) * a.n;
+        const uint32_t y_slot = (XMODE == kTableF32 && a.route_ids) ? __ldg(a.route_ids + group) : group;
+        float* y = a.y_table ? a.y_table[y_slot] : a.y_flat + static_cast<size_t>(y_slot) * a.n;
         y[row] = __fmul_rn(acc, a.alpha_table ? __ldg(a.alpha_table + expert) : a.alpha);
     }
 }
@@ -303,6 +306,24 @@ cudaError_t infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream(const uint32_t
         return cudaErrorInvalidValue;
     GroupedArgs a{indices, input_table, nullptr, packed_weight_table, weight_scale_table, weight_scale_2_table, 1.0f, output_table,
                   nullptr, table_len, groups, out_features, in_features};
+    return launch_grouped<kTableF32, false>(a, stream);
+}
+
+// crates/eider-cuda/src/ffi.rs:3333 (kernel non_gemm.cu:13640-13724): routes sorted by expert, every route with its own input
+// and output vector found through the tables by its route id.  The reference shares each decoded weight among four routes
+// of one expert; here every route's rows stream its expert's matrix with 128-bit loads (consecutive routes of one expert
+// find it in L2), the products are the same exact f32 products and only the order of the additions differs.  `offsets` is
+// required non-null as in the reference and is not read.
+cudaError_t infer_nvfp4_w4a16_reuse_matvec_f32_on_stream(const uint32_t* sorted_routes, const uint32_t* sorted_experts,
+                                                         const uint32_t* offsets, const float* const* inputs,
+                                                         const uint8_t* const* weights, const uint8_t* const* scales,
+                                                         const float* globals, float* const* outputs, uint32_t routes,
+                                                         uint32_t experts, uint32_t out_features, uint32_t in_features,
+                                                         cudaStream_t stream) {
+    if (!sorted_routes || !sorted_experts || !offsets || !inputs || !weights || !scales || !globals || !outputs)
+        return cudaErrorInvalidValue;
+    GroupedArgs a{sorted_experts, inputs, nullptr, weights, scales, globals, 1.0f, outputs, nullptr, experts, routes, out_features, in_features};
+    a.route_ids = sorted_routes;
     return launch_grouped<kTableF32, false>(a, stream);
 }
 

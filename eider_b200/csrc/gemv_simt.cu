@@ -336,6 +336,14 @@ cudaError_t infer_nvfp4_w4a16_matvec_f32_on_stream(const float* input, const uin
                                       weight_scale_2, stream);
 }
 
+cudaError_t infer_nvfp4_w4a16_matvec_f32_warp_rows_on_stream(const float* input, const uint8_t* packed_weight,
+                                                             const uint8_t* weight_scale, float* output, uint32_t out_features,
+                                                             uint32_t in_features, float weight_scale_2, uint32_t warps_per_block,
+                                                             cudaStream_t stream) {
+    (void)warps_per_block;  // launch geometry is fixed here; kept for signature compatibility
+    return launch_w4a16<float, float>(input, packed_weight, weight_scale, output, 1, out_features, in_features, weight_scale_2, stream);
+}
+
 cudaError_t infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream(const float* input, const uint8_t* packed_weight,
                                                                    const uint8_t* weight_scale, float* output,
                                                                    uint32_t batch_size, uint32_t out_features,

@@ -204,6 +204,11 @@ EIDER_B200_API cudaError_t infer_nvfp4_w4a16_matvec_f32_on_stream(const float* i
                                                                   uint32_t out_features, uint32_t in_features,
                                                                   float weight_scale_2, cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:3308. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_matvec_f32_warp_rows_on_stream(const float* input, const uint8_t* packed_weight,
+                                                                            const uint8_t* weight_scale, float* output,
+                                                                            uint32_t out_features, uint32_t in_features,
+                                                                            float weight_scale_2, uint32_t warps_per_block,
+                                                                            cudaStream_t stream); /* ffi.rs:3296 */
 EIDER_B200_API cudaError_t infer_nvfp4_w4a16_matvec_f32_warp_rows_batch_on_stream(
     const float* input, const uint8_t* packed_weight, const uint8_t* weight_scale, float* output, uint32_t batch_size,
     uint32_t out_features, uint32_t in_features, float weight_scale_2, uint32_t warps_per_block, cudaStream_t stream);
@@ -515,6 +520,16 @@ EIDER_B200_API cudaError_t infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream
     const uint32_t* indices, const float* const* input_table, const uint8_t* const* packed_weight_table,
     const uint8_t* const* weight_scale_table, const float* weight_scale_2_table, float* const* output_table, uint32_t table_len,
     uint32_t groups, uint32_t out_features, uint32_t in_features, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3333 (kernel non_gemm.cu:13640-13724): routes sorted by expert; route r of the sorted order
+ * multiplies inputs[sorted_routes[r]] by the matrix of expert sorted_experts[r] into outputs[sorted_routes[r]], times
+ * globals[expert].  in_features % 32 == 0 here (the reference: % 16, at most 3072); `offsets` must be non-null and is not read. */
+EIDER_B200_API cudaError_t infer_nvfp4_w4a16_reuse_matvec_f32_on_stream(const uint32_t* sorted_routes,
+                                                                        const uint32_t* sorted_experts, const uint32_t* offsets,
+                                                                        const float* const* inputs, const uint8_t* const* weights,
+                                                                        const uint8_t* const* scales, const float* globals,
+                                                                        float* const* outputs, uint32_t routes, uint32_t experts,
+                                                                        uint32_t out_features, uint32_t in_features,
+                                                                        cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:589-642 (crates/eider-cuda/native/cutlass_gemv.cu:277-880): grouped W4A4 GEMV with F32 output;
  * a = expert weights with tiled scales (found through tables), b = one NVFP4 activation row with tiled scales (outer = 0).
  * indexed_a: d[g] = alpha * A[indices[g]] . b; ..._tiled_scales: per-expert alpha_table, c is not read (beta 0);

@@ -114,6 +114,51 @@ def test_decode_moe_layer(lib, oracle, tokens):
                                                               gate_up_t.data_ptr(), experts, top_k, 2 * inter, hidden, None) == 1
 
 
+def test_reuse_matvec_over_sorted_routes(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:3333: routes sorted by expert; every route has its own input and output vector, found
+    # through the tables by route id; equals the per-slot grouped-inputs GEMV on the same operands bit for bit
+    import torch
+    experts, routes, n, k = 6, 23, 200, 512
+    rng = np.random.default_rng(5)
+    ws = make_experts(oracle, rng, experts, n, k)
+    w_dev = [(dev(p), dev(s)) for p, s, _, _ in ws]
+    w_t, s_t = table([a for a, _ in w_dev]), table([b for _, b in w_dev])
+    g_d = dev(np.array([g for _, _, g, _ in ws], np.float32))
+    expert_of = rng.integers(0, experts, routes).astype(np.uint32)
+    expert_of[expert_of == 2] = 3  # one expert receives nothing
+    order = np.argsort(expert_of, kind="stable").astype(np.uint32)
+    sorted_experts = expert_of[order]
+    offsets = np.concatenate([[0], np.cumsum(np.bincount(expert_of, minlength=experts))]).astype(np.uint32)
+    x = rng.standard_normal((routes, k)).astype(np.float32)
+    xd = dev(x)
+    y = torch.zeros(routes, n, device="cuda")
+    x_t, y_t = table(list(xd)), table(list(y))
+    i32 = lambda a: dev(np.ascontiguousarray(a, np.uint32).view(np.int32))
+    sr, se, off = i32(order), i32(sorted_experts), i32(offsets)
+    assert lib.infer_nvfp4_w4a16_reuse_matvec_f32_on_stream(sr.data_ptr(), se.data_ptr(), off.data_ptr(), x_t.data_ptr(), w_t.data_ptr(),
+                                                            s_t.data_ptr(), g_d.data_ptr(), y_t.data_ptr(), routes, experts, n, k, None) == 0
+    y2 = torch.zeros(routes, n, device="cuda")
+    y2_t = table(list(y2))
+    eo = i32(expert_of)
+    assert lib.infer_nvfp4_w4a16_grouped_inputs_matvec_f32_on_stream(eo.data_ptr(), x_t.data_ptr(), w_t.data_ptr(), s_t.data_ptr(), g_d.data_ptr(),
+                                                                     y2_t.data_ptr(), experts, routes, n, k, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    for r in range(routes):
+        ok, stats = gemm_close(y[r].cpu().numpy(), ws[int(expert_of[r])][3] @ x[r].astype(np.float64), rel=1e-4, abs_frac=1e-4)
+        assert ok, (r, stats)
+    assert lib.infer_nvfp4_w4a16_reuse_matvec_f32_on_stream(sr.data_ptr(), se.data_ptr(), None, x_t.data_ptr(), w_t.data_ptr(), s_t.data_ptr(),
+                                                            g_d.data_ptr(), y_t.data_ptr(), routes, experts, n, k, None) == 1
+    # the single-token warp-rows form (ffi.rs:3296) is the batch form with one row
+    p, s_, g, deq = ws[0]
+    y1 = torch.zeros(n, device="cuda")
+    assert lib.infer_nvfp4_w4a16_matvec_f32_warp_rows_on_stream(xd[0].data_ptr(), w_dev[0][0].data_ptr(), w_dev[0][1].data_ptr(), y1.data_ptr(),
+                                                                n, k, g, 8, None) == 0
+    torch.cuda.synchronize()
+    ok, stats = gemm_close(y1.cpu().numpy(), deq @ x[0].astype(np.float64), rel=1e-4, abs_frac=1e-4)
+    assert ok, stats
+
+
 def test_decode_moe_w4a4_slots(lib, oracle):
     # the W4A4 decode variant: quantized activation row, indexed expert weights with tiled scales, per-expert alpha;
     # then SiLU * up -> NVFP4 with simple scales per slot, bit-exact against the host quantizer on the device's own values
