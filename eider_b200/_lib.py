@@ -83,6 +83,13 @@ SIGNATURES = {
     "eider_b200_fp8_linear_decode_quantized_on_stream": (_I, [_P, _P, _P, _U32, _P, _P, _F, _P, _I, _P]),
     "infer_nvfp4_w4a16_matvec_f32_warp_rows_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _F, _U32, _P]),
     "infer_nvfp4_w4a16_reuse_matvec_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
+    "infer_fp8_linear_f32_configured_on_stream": (_I, [_P, _P, _P, _U32, _U32, _F, _U32, _P]),
+    "infer_fp8_linear_f32_batch_on_stream": (_I, [_P, _P, _P, _U32, _U32, _U32, _F, _U32, _P]),
+    "infer_fp8_linear_pair_f32_configured_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _F, _F, _U32, _P]),
+    "infer_fp8_linear_triple_f32_configured_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _F, _F, _F, _U32, _P]),
+    "infer_fp8_linear_channel_scaled_f32_configured_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_fp8_linear_channel_scaled_f32_batch_configured_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _P]),
+    "infer_fp8_linear_channel_scaled_precomputed_dynamic_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _P]),
     "infer_cutlass_fp4_grouped_gemm_supported": (_I, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_create": (_P, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_destroy": (None, [_P]),

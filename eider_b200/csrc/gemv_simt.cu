@@ -322,12 +322,190 @@ cudaError_t launch_block_fp8(const float* x, const uint8_t* w, const ScaleT* sca
     return cudaSuccess;
 }
 
+// FP8 weight-only linear for a few tokens (crates/eider-cuda/native/non_gemm.cu:9642-9684): y[b][n] = scale(n) * sum_k x[b][k] *
+// e4m3(w[n][k]) with f32 activations and either one weight scale or one per output row.  QUANT_X is the "precomputed
+// dynamic" form (non_gemm.cu:9900-9925): the activation is replaced by e4m3(x / s_x) with the per-tensor s_x a preceding
+// kernel has written, and the result is multiplied by s_x.  Same streaming shape as the kernels above.
+template <int B, bool QUANT_X>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) fp8_weight_only_kernel(const float* __restrict__ x, const uint8_t* __restrict__ w,
+                                                                              const float* __restrict__ channel_scale, float weight_scale,
+                                                                              const float* __restrict__ x_scale, float* __restrict__ y,
+                                                                              uint32_t n, uint32_t k) {
+    extern __shared__ float xs[];  // [B][kpad], 32-element chunks swizzled
+    const uint32_t kpad = (k + 31) / 32 * 32;
+    const float sx = QUANT_X ? __ldg(x_scale) : 1.0f;
+    for (uint32_t i = threadIdx.x; i < B * k; i += blockDim.x) {
+        const uint32_t b = i / k, e = i % k;
+        float v = __ldg(x + static_cast<size_t>(b) * k + e);
+        if (QUANT_X) v = e4m3_value(e4m3_satfinite(__fdiv_rn(v, sx)));
+        xs[b * kpad + xs_index(e / 32, e % 32)] = v;
+    }
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const uint8_t* wrow = w + static_cast<size_t>(row) * k;
+    float acc[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+    for (uint32_t h = lane; h < k / 16; h += 32) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(wrow + h * 16));
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+        float wv[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            wv[4 * j] = e4m3_value(static_cast<uint8_t>(ww[j]));
+            wv[4 * j + 1] = e4m3_value(static_cast<uint8_t>(ww[j] >> 8));
+            wv[4 * j + 2] = e4m3_value(static_cast<uint8_t>(ww[j] >> 16));
+            wv[4 * j + 3] = e4m3_value(static_cast<uint8_t>(ww[j] >> 24));
+        }
+        const uint32_t c = h / 2, e0 = (h & 1) * 16;
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const float* xb = xs + b * kpad;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 a = *reinterpret_cast<const float4*>(xb + xs_index(c, e0 + 4 * j));
+                acc[b] = fmaf(wv[4 * j], a.x, acc[b]);
+                acc[b] = fmaf(wv[4 * j + 1], a.y, acc[b]);
+                acc[b] = fmaf(wv[4 * j + 2], a.z, acc[b]);
+                acc[b] = fmaf(wv[4 * j + 3], a.w, acc[b]);
+            }
+        }
+    }
+    const float scale = (channel_scale ? __ldg(channel_scale + row) : weight_scale) * sx;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+        const float v = warp_sum(acc[b]);
+        if (lane == 0) y[static_cast<size_t>(b) * n + row] = v * scale;
+    }
+}
+
+// amax / 448 of one activation row (1 when it is all zero), as the per-token quantizer computes it (non_gemm.cu:9880-9898)
+__global__ void __launch_bounds__(256) fp8_input_scale_kernel(const float* __restrict__ x, float* __restrict__ scale, uint32_t k) {
+    __shared__ float red[8];
+    float amax = 0.0f;
+    for (uint32_t i = threadIdx.x; i < k; i += 256) amax = fmaxf(amax, fabsf(__ldg(x + i)));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+        scale[0] = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+    }
+}
+
+template <bool QUANT_X>
+cudaError_t launch_fp8_weight_only(const float* x, const uint8_t* w, const float* channel_scale, float weight_scale, const float* x_scale,
+                                   float* y, uint32_t batch, uint32_t n, uint32_t k, cudaStream_t stream) {
+    if (!x || !w || !y || batch == 0 || n == 0 || k == 0 || k % 16 != 0 || !isfinite(weight_scale) ||
+        ((reinterpret_cast<uintptr_t>(w)) & 15) != 0)
+        return cudaErrorInvalidValue;
+    const uint32_t grid = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    uint32_t done = 0;
+    while (done < batch) {
+        const uint32_t b = batch - done >= 4 ? 4 : (batch - done >= 2 ? 2 : 1);
+        const size_t smem = static_cast<size_t>(b) * ((k + 31) / 32 * 32) * sizeof(float);
+        if (smem > 200 * 1024) return cudaErrorNotSupported;
+        const float* xb = x + static_cast<size_t>(done) * k;
+        float* yb = y + static_cast<size_t>(done) * n;
+        cudaError_t st = cudaSuccess;
+#define EIDER_LAUNCH_FP8_WO(BB)                                                                                                \
+    do {                                                                                                                       \
+        if (smem > 48 * 1024)                                                                                                  \
+            st = cudaFuncSetAttribute(fp8_weight_only_kernel<BB, QUANT_X>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                      static_cast<int>(smem));                                                                 \
+        if (st == cudaSuccess)                                                                                                 \
+            fp8_weight_only_kernel<BB, QUANT_X><<<grid, kWarpsPerBlock * 32, smem, stream>>>(xb, w, channel_scale, weight_scale, \
+                                                                                             x_scale, yb, n, k);               \
+    } while (0)
+        if (b == 4) EIDER_LAUNCH_FP8_WO(4);
+        else if (b == 2) EIDER_LAUNCH_FP8_WO(2);
+        else EIDER_LAUNCH_FP8_WO(1);
+#undef EIDER_LAUNCH_FP8_WO
+        if (st != cudaSuccess) return st;
+        st = cudaGetLastError();
+        if (st != cudaSuccess) return st;
+        done += b;
+    }
+    return cudaSuccess;
+}
+
+bool bad_threads(uint32_t threads) { return threads < 64 || threads > 512 || threads % 32 != 0; }  // (validated as the reference does; not used)
+
 }  // namespace
 }  // namespace eider
 
 using namespace eider;
 
 extern "C" {
+
+// ---- FP8 weight-only linears of the reference (crates/eider-cuda/src/ffi.rs:3056-3147; kernels non_gemm.cu:9642-9950) ------
+cudaError_t infer_fp8_linear_f32_batch_on_stream(const float* input, const uint8_t* weight, float* output, uint32_t batch_size,
+                                                 uint32_t rows, uint32_t cols, float weight_scale, uint32_t threads, cudaStream_t stream) {
+    if (bad_threads(threads)) return cudaErrorInvalidValue;
+    return launch_fp8_weight_only<false>(input, weight, nullptr, weight_scale, nullptr, output, batch_size, rows, cols, stream);
+}
+
+cudaError_t infer_fp8_linear_f32_configured_on_stream(const float* input, const uint8_t* weight, float* output, uint32_t rows,
+                                                      uint32_t cols, float weight_scale, uint32_t threads, cudaStream_t stream) {
+    return infer_fp8_linear_f32_batch_on_stream(input, weight, output, 1, rows, cols, weight_scale, threads, stream);
+}
+
+cudaError_t infer_fp8_linear_pair_f32_configured_on_stream(const float* input, const uint8_t* first_weight, const uint8_t* second_weight,
+                                                           float* first_output, float* second_output, uint32_t first_rows,
+                                                           uint32_t second_rows, uint32_t cols, float first_scale, float second_scale,
+                                                           uint32_t threads, cudaStream_t stream) {
+    if (!input || !first_weight || !second_weight || !first_output || !second_output || first_rows == 0 || second_rows == 0 ||
+        cols == 0 || !isfinite(first_scale) || !isfinite(second_scale) || bad_threads(threads))
+        return cudaErrorInvalidValue;
+    cudaError_t st = launch_fp8_weight_only<false>(input, first_weight, nullptr, first_scale, nullptr, first_output, 1, first_rows, cols, stream);
+    if (st != cudaSuccess) return st;
+    return launch_fp8_weight_only<false>(input, second_weight, nullptr, second_scale, nullptr, second_output, 1, second_rows, cols, stream);
+}
+
+cudaError_t infer_fp8_linear_triple_f32_configured_on_stream(const float* input, const uint8_t* first_weight, const uint8_t* second_weight,
+                                                             const uint8_t* third_weight, float* first_output, float* second_output,
+                                                             float* third_output, uint32_t first_rows, uint32_t second_rows,
+                                                             uint32_t third_rows, uint32_t cols, float first_scale, float second_scale,
+                                                             float third_scale, uint32_t threads, cudaStream_t stream) {
+    if (!third_weight || !third_output || third_rows == 0 || !isfinite(third_scale)) return cudaErrorInvalidValue;
+    cudaError_t st = infer_fp8_linear_pair_f32_configured_on_stream(input, first_weight, second_weight, first_output, second_output,
+                                                                    first_rows, second_rows, cols, first_scale, second_scale, threads, stream);
+    if (st != cudaSuccess) return st;
+    return launch_fp8_weight_only<false>(input, third_weight, nullptr, third_scale, nullptr, third_output, 1, third_rows, cols, stream);
+}
+
+cudaError_t infer_fp8_linear_channel_scaled_f32_batch_configured_on_stream(const float* input, const uint8_t* weight,
+                                                                           const float* channel_weight_scale, float* output,
+                                                                           uint32_t batch_size, uint32_t rows, uint32_t cols,
+                                                                           uint32_t threads, cudaStream_t stream) {
+    if (!channel_weight_scale || bad_threads(threads)) return cudaErrorInvalidValue;
+    return launch_fp8_weight_only<false>(input, weight, channel_weight_scale, 1.0f, nullptr, output, batch_size, rows, cols, stream);
+}
+
+cudaError_t infer_fp8_linear_channel_scaled_f32_configured_on_stream(const float* input, const uint8_t* weight,
+                                                                     const float* channel_weight_scale, float* output, uint32_t rows,
+                                                                     uint32_t cols, uint32_t threads, cudaStream_t stream) {
+    return infer_fp8_linear_channel_scaled_f32_batch_configured_on_stream(input, weight, channel_weight_scale, output, 1, rows, cols, threads,
+                                                                          stream);
+}
+
+cudaError_t infer_fp8_linear_channel_scaled_precomputed_dynamic_f32_on_stream(const float* input, const uint8_t* weight,
+                                                                              const float* channel_weight_scale, float* input_scale,
+                                                                              float* output, uint32_t rows, uint32_t cols,
+                                                                              cudaStream_t stream) {
+    if (!input || !weight || !channel_weight_scale || !input_scale || !output || rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    fp8_input_scale_kernel<<<1, 256, 0, stream>>>(input, input_scale, cols);
+    cudaError_t st = cudaGetLastError();
+    if (st != cudaSuccess) return st;
+    return launch_fp8_weight_only<true>(input, weight, channel_weight_scale, 1.0f, input_scale, output, 1, rows, cols, stream);
+}
+
 
 cudaError_t infer_nvfp4_w4a16_matvec_f32_on_stream(const float* input, const uint8_t* packed_weight,
                                                    const uint8_t* weight_scale, float* output, uint32_t out_features,

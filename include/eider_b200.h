@@ -337,6 +337,38 @@ EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_f32_on_stream
 EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream(
     const float* input, uint8_t* quantized_input, const uint8_t* weight, const float* channel_weight_scale, float* input_scale,
     float* output, uint32_t rows, uint32_t cols, uint32_t threads, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3056-3147 (kernels non_gemm.cu:9642-9950): FP8 weight-only linears, f32 activations times
+ * E4M3 weights [rows][cols], one weight scale or one per output row; `batch` forms take [batch][cols] inputs and write
+ * [batch][rows]; the pair / triple forms run two / three weights on one input.  The "precomputed dynamic" form first writes
+ * input_scale[0] = amax(input) / 448 (1 for an all-zero input) and then multiplies e4m3(input / input_scale) by the weights.
+ * cols % 16 == 0 and 16-byte aligned weights here; `threads` is validated as in the reference (64..512, multiple of 32)
+ * and otherwise unused. */
+EIDER_B200_API cudaError_t infer_fp8_linear_f32_configured_on_stream(const float* input, const uint8_t* weight, float* output,
+                                                                     uint32_t rows, uint32_t cols, float weight_scale,
+                                                                     uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_f32_batch_on_stream(const float* input, const uint8_t* weight, float* output,
+                                                                uint32_t batch_size, uint32_t rows, uint32_t cols,
+                                                                float weight_scale, uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_pair_f32_configured_on_stream(const float* input, const uint8_t* first_weight,
+                                                                          const uint8_t* second_weight, float* first_output,
+                                                                          float* second_output, uint32_t first_rows,
+                                                                          uint32_t second_rows, uint32_t cols, float first_scale,
+                                                                          float second_scale, uint32_t threads,
+                                                                          cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_triple_f32_configured_on_stream(
+    const float* input, const uint8_t* first_weight, const uint8_t* second_weight, const uint8_t* third_weight, float* first_output,
+    float* second_output, float* third_output, uint32_t first_rows, uint32_t second_rows, uint32_t third_rows, uint32_t cols,
+    float first_scale, float second_scale, float third_scale, uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_f32_configured_on_stream(const float* input, const uint8_t* weight,
+                                                                                    const float* channel_weight_scale,
+                                                                                    float* output, uint32_t rows, uint32_t cols,
+                                                                                    uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_f32_batch_configured_on_stream(
+    const float* input, const uint8_t* weight, const float* channel_weight_scale, float* output, uint32_t batch_size, uint32_t rows,
+    uint32_t cols, uint32_t threads, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_precomputed_dynamic_f32_on_stream(
+    const float* input, const uint8_t* weight, const float* channel_weight_scale, float* input_scale, float* output, uint32_t rows,
+    uint32_t cols, cudaStream_t stream);
 EIDER_B200_API cudaError_t infer_fp8_linear_w8a8_f32_on_stream(const float* input, const uint8_t* weight, float* output,
                                                                uint32_t rows, uint32_t cols, float weight_scale,
                                                                float input_scale, cudaStream_t stream);

@@ -33,6 +33,10 @@ def u32(t):
     return t.cpu().numpy().view(np.uint32)
 
 
+def deq_dot(matrix, vector):
+    return matrix @ vector
+
+
 def sort_on_device(lib, ind, experts):
     import torch
     routes = ind.size
@@ -339,6 +343,66 @@ def test_reference_fp8_linear_shims(lib, oracle):
     ok, stats = gemm_close(y3.cpu().numpy(), ref3, rel=1e-3, abs_frac=1e-3)
     assert ok, stats
     assert lib.infer_fp8_linear_w8a8_f32_on_stream(xd.data_ptr(), wd.data_ptr(), y3.data_ptr(), n, k, 0.5, 0.0, None) == 1
+
+
+def test_reference_fp8_weight_only_linears(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:3056-3147: f32 activations times E4M3 weights, scalar or per-row weight scale, single /
+    # batch / pair / triple forms, and the "precomputed dynamic" form that quantizes the activation per tensor first
+    import torch
+    n, n2, n3, k, batch = 1000, 264, 72, 2064, 5
+    rng = np.random.default_rng(17)
+    ws = [rng.integers(0, 256, (r, k)).astype(np.uint8) for r in (n, n2, n3)]
+    for w in ws:
+        w[(w & 0x7f) == 0x7f] = 0x30  # no NaN codes
+    deq = [oracle.e4m3_decode(w).astype(np.float64) for w in ws]
+    x = rng.standard_normal((batch, k)).astype(np.float32)
+    ch = (rng.random(n) * 0.01 + 0.001).astype(np.float32)
+    wd = [dev(w) for w in ws]
+    xd, chd = dev(x), dev(ch)
+    y = torch.full((batch, n), -5.0, device="cuda")
+    assert lib.infer_fp8_linear_f32_batch_on_stream(xd.data_ptr(), wd[0].data_ptr(), y.data_ptr(), batch, n, k, 0.25, 256, None) == 0
+    y1 = torch.zeros(n, device="cuda")
+    assert lib.infer_fp8_linear_f32_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), y1.data_ptr(), n, k, 0.25, 128, None) == 0
+    yc = torch.zeros(batch, n, device="cuda")
+    assert lib.infer_fp8_linear_channel_scaled_f32_batch_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), chd.data_ptr(), yc.data_ptr(),
+                                                                              batch, n, k, 256, None) == 0
+    yc1 = torch.zeros(n, device="cuda")
+    assert lib.infer_fp8_linear_channel_scaled_f32_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), chd.data_ptr(), yc1.data_ptr(), n, k,
+                                                                        256, None) == 0
+    o = [torch.zeros(r, device="cuda") for r in (n, n2, n3)]
+    assert lib.infer_fp8_linear_triple_f32_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), wd[1].data_ptr(), wd[2].data_ptr(),
+                                                                o[0].data_ptr(), o[1].data_ptr(), o[2].data_ptr(), n, n2, n3, k, 0.25, 0.5,
+                                                                2.0, 256, None) == 0
+    p = [torch.zeros(r, device="cuda") for r in (n, n2)]
+    assert lib.infer_fp8_linear_pair_f32_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), wd[1].data_ptr(), p[0].data_ptr(), p[1].data_ptr(),
+                                                              n, n2, k, 0.25, 0.5, 256, None) == 0
+    torch.cuda.synchronize()
+    xr = x.astype(np.float64)
+    for got, ref in ((y.cpu().numpy(), xr @ deq[0].T * 0.25), (yc.cpu().numpy(), xr @ deq[0].T * ch[None, :].astype(np.float64))):
+        ok, stats = gemm_close(got, ref, rel=1e-4, abs_frac=1e-4)
+        assert ok, stats
+    assert torch.equal(y1, y[0]) and torch.equal(yc1, yc[0])
+    for got, d, sc in ((o[0], deq[0], 0.25), (o[1], deq[1], 0.5), (o[2], deq[2], 2.0)):
+        ok, stats = gemm_close(got.cpu().numpy(), deq_dot(d, xr[0]) * sc, rel=1e-4, abs_frac=1e-4)
+        assert ok, stats
+    assert torch.equal(p[0], o[0]) and torch.equal(p[1], o[1])
+    # precomputed dynamic: input_scale[0] = amax / 448, then e4m3(x / scale) times the weights, times scale and the row scale
+    xq, sx = oracle.quantize_fp8_dynamic(x[:1])
+    s_out = torch.zeros(1, device="cuda")
+    yd = torch.zeros(n, device="cuda")
+    assert lib.infer_fp8_linear_channel_scaled_precomputed_dynamic_f32_on_stream(xd.data_ptr(), wd[0].data_ptr(), chd.data_ptr(),
+                                                                                 s_out.data_ptr(), yd.data_ptr(), n, k, None) == 0
+    torch.cuda.synchronize()
+    assert float(s_out.item()) == float(sx[0])
+    ref = (deq[0] @ oracle.e4m3_decode(xq[0]).astype(np.float64)) * float(sx[0]) * ch.astype(np.float64)
+    ok, stats = gemm_close(yd.cpu().numpy(), ref, rel=1e-4, abs_frac=1e-4)
+    assert ok, stats
+    # rejected before any launch: null pointers, a thread count outside the reference's range, a row length off the 16 grid
+    assert lib.infer_fp8_linear_f32_batch_on_stream(None, wd[0].data_ptr(), y.data_ptr(), batch, n, k, 0.25, 256, None) == 1
+    assert lib.infer_fp8_linear_f32_batch_on_stream(xd.data_ptr(), wd[0].data_ptr(), y.data_ptr(), batch, n, k, 0.25, 48, None) == 1
+    assert lib.infer_fp8_linear_f32_batch_on_stream(xd.data_ptr(), wd[0].data_ptr(), y.data_ptr(), batch, n, k - 8, 0.25, 256, None) == 1
+    assert lib.infer_fp8_linear_channel_scaled_f32_configured_on_stream(xd.data_ptr(), wd[0].data_ptr(), None, yc1.data_ptr(), n, k, 256,
+                                                                        None) == 1
 
 
 @pytest.mark.parametrize("batch", [1, 7])
