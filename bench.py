@@ -836,18 +836,27 @@ def single_gpu_extras(args, torch, ops, peaks):
             plan = ops.Nvfp4DecodePlan(tokens, n, k)
             us = _graph_time_us(torch, lambda i: plan.run(x, ws[i % copies], out=y), 50)
             nbytes = n * k // 2 + n * k // 16 + 2 * tokens * k + 2 * tokens * n + 4
+            # the same GEMV on an operand the producer of x has expanded once (shared by every linear that reads x)
+            operand = ops.Nvfp4DecodeOperand(8, k).expand(x)
+            prepared_us = _graph_time_us(torch, lambda i: plan.run_prepared(operand, ws[i % copies], out=y), 50)
         else:
             ws = [torch.randint(0, 120, (n, k), dtype=torch.uint8, device="cuda") for _ in range(copies)]
             sw = torch.rand(n, device="cuda") * 0.01
             plan = ops.Fp8DecodePlan(64, n, k)
             us = _graph_time_us(torch, lambda i: plan.run(x, ws[i % copies], sw, out=y), 50)
             nbytes = n * k + 4 * n + 2 * tokens * k + 2 * tokens * n
+            # the same linear on activations their producer has already quantized (codes + one scale per token)
+            xq, xs = ops.quantize_fp8_dynamic(x)
+            prepared_us = _graph_time_us(torch, lambda i: plan.run_quantized(xq, xs, ws[i % copies], sw, out=y), 50)
         assert plan.status() == 0
         cases.append({"op": op, "M": tokens, "K": k, "N": n, "us": us, "gbs": nbytes / us / 1e3,
-                      "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"]})
+                      "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"], "prepared_activation_us": prepared_us,
+                      "prepared_activation_frac_of_hbm_peak": nbytes / prepared_us / 1e3 / peaks["hbm_gbs"]})
         del ws
     extra["decode"] = {"unit": "GB/s of the algorithmic bytes", "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
-                       "timing": f"CUDA-graph replay of 50 calls, {copies} rotating weight copies", "cases": cases}
+                       "timing": f"CUDA-graph replay of 50 calls, {copies} rotating weight copies",
+                       "prepared_activation": "the same GEMV on an activation its producer has expanded (NVFP4) or quantized (FP8) once",
+                       "cases": cases}
     # the 4096-token chunk of the sweep
     m4 = 4096
     ws = [ops.ModelOptWeight.quantize(torch.randn(N, K, device="cuda") * 0.02) for _ in range(3)]
