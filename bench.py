@@ -381,6 +381,12 @@ def measure_moe(torch, dist, world, rank, steps, warmup, stages=True):
         torch.cuda.synchronize()
     total = timed(lambda: step(x, logits), steps)
     compute = timed(lambda: layer.run_experts_and_return(), steps)  # the owner's share: two grouped GEMMs, SiLU quantizer, return stores
+    # each phase replayed on its own (the buffers hold the last step's routes; peer stores included, no waiting in any of them)
+    phase_us = {"route_sort_publish": timed(lambda: layer.route_and_publish(x, logits), steps),
+                "offsets_quantize_dispatch": timed(lambda: layer.dispatch(), steps),
+                "experts_and_return": compute,
+                "combine": timed(lambda: layer.combine(), steps),
+                "barrier": timed(lambda: layer.barrier.arrive_and_wait(3), steps)}
     assert layer.status() == 0
     layer.barrier.check()
     received = torch.tensor([float(layer.recv_total.item())], device="cuda")
@@ -392,7 +398,7 @@ def measure_moe(torch, dist, world, rank, steps, warmup, stages=True):
         return None
     route_bytes_out, route_bytes_back = h * 9 // 16, 2 * h
     return {"metric": "moe_prefill_tflops", "value": flops / total / 1e6, "unit": "TFLOP/s", "n_gpus": world, "us_per_step": total,
-            "experts_and_return_us": compute, "most_routes_on_one_rank": int(most.item()), "routes": t * k8,
+            "experts_and_return_us": compute, "phase_us": phase_us, "most_routes_on_one_rank": int(most.item()), "routes": t * k8,
             "nvlink_bytes_per_rank": (world - 1) / world * tl * k8 * (route_bytes_out + route_bytes_back),
             "partition": f"experts split evenly x{world}, tokens sharded by rows, NVFP4 rows dispatched and bf16 rows returned by peer "
                          "stores over NVLink, counts resident on the device, four bounded device barriers per step",
