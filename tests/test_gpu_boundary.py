@@ -272,6 +272,18 @@ def test_reference_grouped_gemm_over_pointer_tables(lib, oracle, tokens, experts
         torch.cuda.synchronize()
         status = ctypes.c_uint32(1)
         assert lib.eider_b200_grouped_plan_status(tplan, ctypes.byref(status)) == 0 and status.value == 0
+        assert torch.equal(got, want)
+        # nothing is read back to the host and nothing is allocated: the call records into a CUDA graph and replays
+        got.fill_(3.0)
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                assert lib.infer_cutlass_fp4_grouped_gemm_on_stream(tplan, a_tbl.data_ptr(), as_tbl.data_ptr(), b_tbl.data_ptr(),
+                                                                    bs_tbl.data_ptr(), out_tbl.data_ptr(), alpha_tbl.data_ptr(),
+                                                                    counts.data_ptr(), side.cuda_stream) == 0
+            graph.replay()
+        torch.cuda.synchronize()
     finally:
         lib.infer_cutlass_fp4_grouped_gemm_destroy(tplan)
     assert torch.equal(got, want)
