@@ -83,7 +83,20 @@ def _worker(rank, world, port, result):
                                            combine_fn=parallel.device_combine(tl, top_k))
         torch.cuda.synchronize()
         ok_moe = bool(torch.allclose(out, ref[rows], rtol=1e-5, atol=1e-6))
-        result[rank] = (ok_dense, ok_moe)
+        # the same layer over peer memory: NVFP4 rows dispatched and bf16 rows returned by peer stores, counts on the device,
+        # bounded device barriers between the phases; equals the single-GPU pipeline bit for bit, step after step
+        local_gu = ops.GroupedNvfp4Weights.from_checkpoint(w_gu.packed[sl].contiguous(), w_gu.scales_row_major[sl].contiguous(), w_gu.alpha[sl])
+        local_dn = ops.GroupedNvfp4Weights.from_checkpoint(w_dn.packed[sl].contiguous(), w_dn.scales_row_major[sl].contiguous(), w_dn.alpha[sl])
+        layer, step = parallel.peer_expert_parallel_moe(None, tl, experts, top_k, hidden, inter, local_gu, local_dn)
+        ok_peer = True
+        x_local, logits_local = xs[rows].contiguous(), logits[rows].contiguous()
+        for _ in range(3):
+            got = step(x_local, logits_local).clone()
+            torch.cuda.synchronize()
+            ok_peer = ok_peer and bool(torch.equal(got, ref[rows]))
+        layer.barrier.check()
+        ok_peer = ok_peer and layer.status() == 0
+        result[rank] = (ok_dense, ok_moe, ok_peer)
     finally:
         dist.destroy_process_group()
 
@@ -110,7 +123,7 @@ def test_two_rank_partitioned_paths():
                 if p.is_alive():
                     p.kill()
     assert [p.exitcode for p in procs] == [0] * world
-    assert dict(result) == {0: (True, True), 1: (True, True)}
+    assert dict(result) == {0: (True, True, True), 1: (True, True, True)}
 
 
 def test_peer_barrier_gives_up_instead_of_spinning():
