@@ -401,7 +401,7 @@ def measure_moe(torch, dist, world, rank, steps, warmup, stages=True):
             "experts_and_return_us": compute, "phase_us": phase_us, "most_routes_on_one_rank": int(most.item()), "routes": t * k8,
             "nvlink_bytes_per_rank": (world - 1) / world * tl * k8 * (route_bytes_out + route_bytes_back),
             "partition": f"experts split evenly x{world}, tokens sharded by rows, NVFP4 rows dispatched and bf16 rows returned by peer "
-                         "stores over NVLink, counts resident on the device, four bounded device barriers per step",
+                         "stores over NVLink, counts resident on the device, three bounded device barriers per step (two alternating buffer sets)",
             "timing": f"{steps} steps replayed as one CUDA graph per rank, ranks aligned on the device, max over ranks, best of 3",
             "data": "synthetic", "config": {"workload": "nvfp4 routed moe prefill: 4096 tokens, 128 experts, top-8, H=2048, I=768",
                                             "n_shards": world}}

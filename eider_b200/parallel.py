@@ -400,40 +400,56 @@ class PeerExpertParallelMoe:
         return self.out
 
     def status(self) -> int:
-        return self.gate_up_plan.status() | self.down_plan.status()
+        st = 0
+        for one in getattr(self, "twins", [self]):
+            st |= one.gate_up_plan.status() | one.down_plan.status()
+        return st
 
 
-def peer_expert_parallel_moe(group, tokens_local, experts, top_k, hidden, intermediate, w_gate_up, w_down, capacity=None):
+def peer_expert_parallel_moe(group, tokens_local, experts, top_k, hidden, intermediate, w_gate_up, w_down, capacity=None,
+                             double_buffer=True):
     """The layer on real ranks: buffers in symmetric memory, the library's bounded barrier between the phases.
-    Returns (layer, step) where step(x, router_logits) -> [tokens_local, hidden] f32."""
+    Returns (layer, step) where step(x, router_logits) -> [tokens_local, hidden] f32.
+
+    With `double_buffer` consecutive steps alternate between two sets of buffers, which makes the meeting after the combine
+    unnecessary: a rank reuses a set only after it has passed the third barrier of the step in between, and every rank
+    reaches that barrier only after it has finished the step before (its combine included)."""
     import torch.distributed._symmetric_memory as symm_mem
     group = group if group is not None else dist.group.WORLD
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    handles = {}
 
     def alloc(shape, dtype):
         t = symm_mem.empty(*shape, dtype=dtype, device="cuda")
         t.zero_()
         return t
 
-    layer = PeerExpertParallelMoe(rank, world, tokens_local, experts, top_k, hidden, intermediate, w_gate_up, w_down, capacity, alloc)
-    for name in PeerExpertParallelMoe.PEER_BUFFERS:
-        handles[name] = symm_mem.rendezvous(layer.buffers[name], group)
-    layer.connect({name: list(h.buffer_ptrs) for name, h in handles.items()})
-    layer._handles = handles
+    layers = []
+    for _ in range(2 if double_buffer else 1):
+        one = PeerExpertParallelMoe(rank, world, tokens_local, experts, top_k, hidden, intermediate, w_gate_up, w_down, capacity, alloc)
+        handles = {name: symm_mem.rendezvous(one.buffers[name], group) for name in PeerExpertParallelMoe.PEER_BUFFERS}
+        one.connect({name: list(h.buffer_ptrs) for name, h in handles.items()})
+        one._handles = handles
+        layers.append(one)
+    layer = layers[0]
     barrier = PeerBarrier(group)
-    layer.barrier = barrier
+    for one in layers:
+        one.barrier = barrier
+    layer.twins = layers
+    calls = [0]
 
     def step(x, router_logits, norm_topk_prob=True):
-        layer.route_and_publish(x, router_logits, norm_topk_prob)
+        cur = layers[calls[0] % len(layers)]
+        calls[0] += 1
+        cur.route_and_publish(x, router_logits, norm_topk_prob)
         barrier.arrive_and_wait(4)
-        layer.dispatch()
+        cur.dispatch()
         barrier.arrive_and_wait(5)
-        layer.run_experts_and_return()
+        cur.run_experts_and_return()
         barrier.arrive_and_wait(6)
-        # (the next step's counts and rows land in the same buffers: a rank may start it only when every rank has combined)
-        out = layer.combine()
-        barrier.arrive_and_wait(7)
+        out = cur.combine()
+        if len(layers) == 1:
+            # (the next step's counts and rows land in the same buffers: a rank may start it only when every rank has combined)
+            barrier.arrive_and_wait(7)
         return out
 
     return layer, step
