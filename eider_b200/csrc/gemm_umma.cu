@@ -421,7 +421,10 @@ cudaError_t run_decode(DecodePlan& plan, uint32_t terms, const uint8_t* x_values
     p.counters = plan.counters;
     p.status = plan.status;
     const uint32_t items = p.row_tiles * p.splits;
+    // more than sixteen tokens: the splits' partial sums are added up by a kernel of their own
+    p.defer_reduce = (p.splits > 1 && tokens > 16) ? 1u : 0u;
 #define EIDER_DECODE(KIND, BN, TERMS) launch<KIND, BN, true, TERMS, false>(map_rows, map_cols, p, items, stream)
+    auto dispatch = [&]() -> cudaError_t {
     if (nv) {
         if (terms == 8) {
             switch (block_n) {
@@ -459,7 +462,20 @@ cudaError_t run_decode(DecodePlan& plan, uint32_t terms, const uint8_t* x_values
         case 128: return EIDER_DECODE(kFp8, 128, 1);
         default: return EIDER_DECODE(kFp8, 256, 1);
     }
+    };
 #undef EIDER_DECODE
+    st = dispatch();
+    if (st != cudaSuccess || !p.defer_reduce) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((plan.n + 255) / 256, tokens);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, p);
 }
 
 // Pointer-table form: one warp per group copies the two template maps into shared memory, replaces their addresses with

@@ -54,6 +54,7 @@ struct Params {
     uint32_t splits;         // K splits (1 = none)
     float* workspace;        // [splits][out_cols][row_tiles*128] fp32 partials
     uint32_t* counters;      // [row_tiles] arrival counters, self-resetting
+    uint32_t defer_reduce;   // split K: leave the partial sums in `workspace` for splitk_reduce_kernel (many output columns)
     // grouped (MoE): per-group row ranges of the row operand
     const uint32_t* group_offsets;  // [groups + 1] or null
     uint32_t groups;
@@ -725,7 +726,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                 if (lane == 0) umma::mbar_arrive(&acc_empty[acc]);
             }
 
-            if (TRANSPOSED && p.splits > 1) {
+            if (TRANSPOSED && p.splits > 1 && !p.defer_reduce) {
                 // split-K: the last CTA to finish a row tile sums the partials in split order.
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -782,6 +783,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
         umma::tc_fence_after();
         umma::tmem_dealloc(tmem_base, T::kAlloc);
     }
+}
+
+// Sums the K splits' partial sums of the decode orientation when many tokens share the launch: the one CTA per row tile that
+// arrives last needs a memory round trip per four tokens, this kernel spreads the same sums (in split order) over the whole
+// device.  One thread per (token, output row); a programmatic dependent launch.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const Params p) {
+    umma::griddep_launch_dependents();
+    umma::griddep_wait();
+    const uint32_t row = blockIdx.x * 256 + threadIdx.x, ocol = blockIdx.y;
+    if (row >= p.rows) return;
+    const size_t stride = static_cast<size_t>(p.row_tiles) * kTileRows;
+    float sum = 0.0f;
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+        float part[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8; ++u)
+            part[u] = s0 + u < p.splits ? __ldcg(&p.workspace[(static_cast<size_t>(s0 + u) * p.out_cols + ocol) * stride + row]) : 0.0f;
+#pragma unroll
+        for (uint32_t u = 0; u < 8; ++u) sum += part[u];
+    }
+    float x = sum * (p.row_scale ? p.alpha * p.row_scale[row] : p.alpha);
+    const size_t index = static_cast<size_t>(ocol) * p.ld_out + row;
+    if (p.beta != 0.0f && p.c_in)
+        x = fmaf(p.beta, p.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(p.c_in)[index]) : static_cast<const float*>(p.c_in)[index], x);
+    if (p.out_is_bf16) static_cast<uint16_t*>(p.out)[index] = float_to_bf16_bits(x);
+    else static_cast<float*>(p.out)[index] = x;
 }
 
 }  // namespace gemm
