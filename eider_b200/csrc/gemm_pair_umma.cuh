@@ -200,16 +200,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     const uint32_t sfb_lo = sfb_lo0 + stage * (L::kSfB >> 4);
                     const uint32_t nkb = (s + 1 < p.k_stages) ? 4u : tail_kb;
                     if (nkb == 4) {
-                        if (kNv) {
+                        // the scale copies of a 64-element step right in front of its MMA: the copies of step j + 1 then run
+                        // under the MMA of step j (measured 1.2 us of 33.9 against all twelve copies first)
 #pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            if (kNv) {
                                 umma::tc_copy_scales_pair(sfa_tmem + j * 4, umma::make_desc(sfa_lo + j * 32, umma::kDescHiScales));
                                 umma::tc_copy_scales_pair(sfb_tmem + j * 8, umma::make_desc(sfb_lo + j * 32, umma::kDescHiScales));
                                 umma::tc_copy_scales_pair(sfb_tmem + j * 8 + 4, umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
                             }
-                        }
-#pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j) {
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
                             const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
                             const uint32_t accumulate = (s > 0 || j > 0) ? 1u : 0u;
