@@ -474,7 +474,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                     if (!leader) {
                         // nothing to issue
                     } else if (s + 1 < p.k_stages || tail_kb == 4) {
-#ifndef EIDER_EXP_SKIP_SFCP
                         if (kNv) {
 #pragma unroll
                             for (uint32_t j = 0; j < 4; ++j) {
@@ -485,7 +484,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
                                                          umma::make_desc(sfb_lo + (4 + j) * 32, umma::kDescHiScales));
                             }
                         }
-#endif
 #pragma unroll
                         for (uint32_t j = 0; j < 4; ++j) {
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
