@@ -83,13 +83,18 @@ enum Act { kSiluHalves = 0, kGeluPair = 1 };
 // up arrays of `len` elements (non_gemm.cu:1226-1246), cols = len and rows = 1.
 template <int ACT>
 __global__ void __launch_bounds__(256) act_mul_f32_kernel(const float* __restrict__ gate, const float* __restrict__ up,
-                                                          float* __restrict__ output, uint32_t rows, uint32_t cols) {
+                                                          float* __restrict__ output, uint32_t rows, uint32_t cols, float limit) {
     const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<size_t>(rows) * cols) return;
     if (ACT == kSiluHalves) {
         const size_t row = idx / cols, col = idx - row * cols;
         const size_t base = row * cols * 2;
-        output[idx] = rowops::silu_div_mul(__ldg(gate + base + col), __ldg(gate + base + cols + col));
+        float g = __ldg(gate + base + col), u = __ldg(gate + base + cols + col);
+        if (limit > 0.0f) {  // clamped form (non_gemm.cu:1328-1338): gate from above, up from both sides
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+        }
+        output[idx] = rowops::silu_div_mul(g, u);
     } else {
         output[idx] = rowops::gelu_tanh_mul(__ldg(gate + idx), __ldg(up + idx));
     }
@@ -266,8 +271,21 @@ cudaError_t infer_silu_mul_halves_f32_batch_on_stream(const float* gate_up, floa
                                                       cudaStream_t stream) {
     if (!gate_up || !output || rows == 0 || cols == 0) return cudaErrorInvalidValue;
     const size_t len = static_cast<size_t>(rows) * cols;
-    act_mul_f32_kernel<kSiluHalves><<<static_cast<uint32_t>((len + 255) / 256), 256, 0, stream>>>(gate_up, nullptr, output, rows, cols);
+    act_mul_f32_kernel<kSiluHalves><<<static_cast<uint32_t>((len + 255) / 256), 256, 0, stream>>>(gate_up, nullptr, output, rows, cols, 0.0f);
     return cudaGetLastError();
+}
+
+cudaError_t infer_silu_mul_halves_clamped_f32_batch_on_stream(const float* gate_up, float* output, uint32_t rows, uint32_t cols,
+                                                              float limit, cudaStream_t stream) {
+    if (!gate_up || !output || rows == 0 || cols == 0 || !isfinite(limit) || limit <= 0.0f) return cudaErrorInvalidValue;
+    const size_t len = static_cast<size_t>(rows) * cols;
+    act_mul_f32_kernel<kSiluHalves><<<static_cast<uint32_t>((len + 255) / 256), 256, 0, stream>>>(gate_up, nullptr, output, rows, cols, limit);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_silu_mul_halves_clamped_f32_on_stream(const float* gate_up, float* output, uint32_t len, float limit,
+                                                        cudaStream_t stream) {
+    return infer_silu_mul_halves_clamped_f32_batch_on_stream(gate_up, output, 1, len, limit, stream);
 }
 
 cudaError_t infer_silu_mul_halves_f32_on_stream(const float* gate_up, float* output, uint32_t len, cudaStream_t stream) {
@@ -277,7 +295,7 @@ cudaError_t infer_silu_mul_halves_f32_on_stream(const float* gate_up, float* out
 cudaError_t infer_gelu_tanh_mul_f32_on_stream(const float* gate, const float* up, float* output, uint32_t len,
                                               cudaStream_t stream) {
     if (!gate || !up || !output || len == 0) return cudaErrorInvalidValue;
-    act_mul_f32_kernel<kGeluPair><<<(len + 255) / 256, 256, 0, stream>>>(gate, up, output, 1, len);
+    act_mul_f32_kernel<kGeluPair><<<(len + 255) / 256, 256, 0, stream>>>(gate, up, output, 1, len, 0.0f);
     return cudaGetLastError();
 }
 

@@ -127,6 +127,12 @@ EIDER_B200_API cudaError_t infer_silu_mul_halves_f32_on_stream(const float* gate
 EIDER_B200_API cudaError_t infer_silu_mul_halves_f32_batch_on_stream(const float* gate_up, float* output, uint32_t rows,
                                                                      uint32_t cols, cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:1492: tanh-approximated GELU(gate) * up over `len` elements. */
+/* crates/eider-cuda/src/ffi.rs:1512 and :1527 (kernel non_gemm.cu:1328-1338): the same with gate clamped from above and up
+ * clamped to [-limit, limit] first; limit finite and positive. */
+EIDER_B200_API cudaError_t infer_silu_mul_halves_clamped_f32_on_stream(const float* gate_up, float* output, uint32_t len,
+                                                                       float limit, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_silu_mul_halves_clamped_f32_batch_on_stream(const float* gate_up, float* output, uint32_t rows,
+                                                                             uint32_t cols, float limit, cudaStream_t stream);
 EIDER_B200_API cudaError_t infer_gelu_tanh_mul_f32_on_stream(const float* gate, const float* up, float* output, uint32_t len,
                                                              cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:2873 (kernel non_gemm.cu:8898-8915): attention output [heads][tokens][head_dim] ->

@@ -215,6 +215,32 @@ def test_fused_silu_quantize_against_staged(lib, oracle, tokens, k):
     assert np.allclose(act.cpu().numpy(), g64 / (1 + np.exp(-g64)) * u64, rtol=2e-6, atol=1e-7)
 
 
+def test_clamped_silu_halves(lib):
+    # crates/eider-cuda/src/ffi.rs:1512, :1527 (kernel non_gemm.cu:1328-1338): gate clamped from above, up from both sides;
+    # equals the unclamped kernel on inputs clamped beforehand, bit for bit
+    import torch
+    rng = np.random.default_rng(4)
+    rows, cols, limit = 7, 300, 1.5
+    gu = (rng.standard_normal((rows, 2 * cols)) * 3).astype(np.float32)
+    gud = dev(gu)
+    got = torch.empty(rows, cols, device="cuda")
+    assert lib.infer_silu_mul_halves_clamped_f32_batch_on_stream(gud.data_ptr(), got.data_ptr(), rows, cols, limit, None) == 0
+    pre = gu.copy()
+    pre[:, :cols] = np.minimum(pre[:, :cols], limit)
+    pre[:, cols:] = np.clip(pre[:, cols:], -limit, limit)
+    pred = dev(pre)
+    want = torch.empty(rows, cols, device="cuda")
+    assert lib.infer_silu_mul_halves_f32_batch_on_stream(pred.data_ptr(), want.data_ptr(), rows, cols, None) == 0
+    one = torch.empty(cols, device="cuda")
+    assert lib.infer_silu_mul_halves_clamped_f32_on_stream(gud.data_ptr(), one.data_ptr(), cols, limit, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(one, want[0])
+    g64, u64 = pre[:, :cols].astype(np.float64), pre[:, cols:].astype(np.float64)
+    assert np.allclose(got.cpu().numpy(), g64 / (1 + np.exp(-g64)) * u64, rtol=2e-6, atol=1e-7)
+    assert lib.infer_silu_mul_halves_clamped_f32_batch_on_stream(gud.data_ptr(), got.data_ptr(), rows, cols, 0.0, None) == 1
+    assert lib.infer_silu_mul_halves_clamped_f32_batch_on_stream(gud.data_ptr(), got.data_ptr(), rows, cols, float("inf"), None) == 1
+
+
 @pytest.mark.parametrize("rows", [16, 768, 1000, 5])
 def test_vector_simple_scales_matches_oracle(lib, oracle, rows):
     import torch
