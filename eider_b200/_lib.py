@@ -92,6 +92,9 @@ SIGNATURES = {
     "infer_fp8_linear_channel_scaled_precomputed_dynamic_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _U32, _U32, _P]),
     "infer_silu_mul_halves_clamped_f32_on_stream": (_I, [_P, _P, _U32, _F, _P]),
     "infer_silu_mul_halves_clamped_f32_batch_on_stream": (_I, [_P, _P, _U32, _U32, _F, _P]),
+    "infer_fp8_moe_grouped_gate_up_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
+    "infer_moe_silu_quantize_fp8_slots_f32_on_stream": (_I, [_P, _P, _P, _U32, _U32, _P]),
+    "infer_fp8_moe_grouped_down_f32_on_stream": (_I, [_P, _P, _P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "infer_cutlass_fp4_grouped_gemm_supported": (_I, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_create": (_P, [_U32, _U32, _U32, _U32]),
     "infer_cutlass_fp4_grouped_gemm_destroy": (None, [_P]),

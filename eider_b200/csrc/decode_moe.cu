@@ -276,12 +276,140 @@ __global__ void __launch_bounds__(256) top1_pass2_kernel(const float* __restrict
     }
 }
 
+// ---- FP8 W8A8 slots (crates/eider-cuda/native/non_gemm.cu:10156-10350) ------------------------------------------------------
+// One warp per output row, the slot's activation codes decoded once per CTA into shared memory, weights streamed with 128-bit
+// loads; every product of two E4M3 values is exact in f32.  GATE_UP: rows [0, n) come from the gate table and [n, 2n) from
+// the up table, one shared activation; otherwise one activation row per slot and one output vector per slot.
+template <bool GATE_UP>
+__global__ void __launch_bounds__(kWarps * 32) fp8_slot_gemv_kernel(const uint32_t* __restrict__ indices, const uint8_t* __restrict__ x_codes,
+                                                                    const float* __restrict__ x_scales, const uint8_t* const* w_table,
+                                                                    const float* const* s_table, const uint8_t* const* w2_table,
+                                                                    const float* const* s2_table, float* y_flat, float* const* y_table,
+                                                                    uint32_t n, uint32_t k) {
+    extern __shared__ float xs[];  // [k], swizzled
+    const uint32_t slot = blockIdx.y;
+    const uint32_t expert = __ldg(indices + slot);
+    const uint8_t* x = GATE_UP ? x_codes : x_codes + static_cast<size_t>(slot) * k;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) xs[xs_index(i / 32, i % 32)] = e4m3_value(__ldg(x + i));
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t total = GATE_UP ? 2 * n : n;
+    if (row >= total) return;
+    const bool second = GATE_UP && row >= n;
+    const uint32_t r = second ? row - n : row;
+    const uint8_t* wrow = (second ? w2_table[expert] : w_table[expert]) + static_cast<size_t>(r) * k;
+    float acc = 0.0f;
+    for (uint32_t h = lane; h < k / 16; h += 32) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(wrow + h * 16));
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+        const uint32_t c = h / 2, e0 = (h & 1) * 16;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 a = *reinterpret_cast<const float4*>(xs + xs_index(c, e0 + 4 * j));
+            acc = fmaf(e4m3_value(static_cast<uint8_t>(ww[j])), a.x, acc);
+            acc = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 8)), a.y, acc);
+            acc = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 16)), a.z, acc);
+            acc = fmaf(e4m3_value(static_cast<uint8_t>(ww[j] >> 24)), a.w, acc);
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        const float sx = GATE_UP ? __ldg(x_scales) : __ldg(x_scales + slot);
+        const float sw = __ldg((second ? s2_table[expert] : s_table[expert]) + r);
+        const float v = __fmul_rn(__fmul_rn(acc, sx), sw);
+        if (GATE_UP) y_flat[static_cast<size_t>(slot) * 2 * n + row] = v;
+        else y_table[slot][row] = v;
+    }
+}
+
+// Per slot: SiLU(gate) * up of the slot's [gate | up] row, one dynamic scale amax / 448 per slot (1 for an all-zero slot;
+// non-finite values do not enter the maximum), E4M3 codes (non_gemm.cu:10241-10270).  One CTA per slot.
+__global__ void __launch_bounds__(256) silu_quantize_fp8_slots_kernel(const float* __restrict__ gate_up, uint8_t* __restrict__ quantized,
+                                                                      float* __restrict__ scales, uint32_t rows) {
+    __shared__ float red[8];
+    __shared__ float scale_sh;
+    const uint32_t slot = blockIdx.x;
+    const float* gate = gate_up + static_cast<size_t>(slot) * rows * 2;
+    const float* up = gate + rows;
+    float amax = 0.0f;
+    for (uint32_t i = threadIdx.x; i < rows; i += 256) {
+        const float g = __ldg(gate + i);
+        const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), __ldg(up + i));
+        if (isfinite(v)) amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+        const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 448.0f);
+        scales[slot] = sc;
+        scale_sh = sc;
+    }
+    __syncthreads();
+    const float sc = scale_sh;
+    for (uint32_t i = threadIdx.x; i < rows; i += 256) {
+        const float g = __ldg(gate + i);
+        const float v = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), __ldg(up + i));
+        quantized[static_cast<size_t>(slot) * rows + i] = e4m3_satfinite(__fdiv_rn(v, sc));
+    }
+}
+
+template <bool GATE_UP>
+cudaError_t launch_fp8_slots(const uint32_t* indices, const uint8_t* x, const float* x_scales, const uint8_t* const* w, const float* const* s,
+                             const uint8_t* const* w2, const float* const* s2, float* y_flat, float* const* y_table, uint32_t n, uint32_t k,
+                             uint32_t slots, cudaStream_t stream) {
+    if (k % 16 != 0) return cudaErrorInvalidValue;
+    const size_t smem = static_cast<size_t>((k + 31) / 32 * 32) * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorNotSupported;
+    if (smem > 48 * 1024) {
+        cudaError_t st = cudaFuncSetAttribute(fp8_slot_gemv_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (st != cudaSuccess) return st;
+    }
+    const uint32_t total = GATE_UP ? 2 * n : n;
+    fp8_slot_gemv_kernel<GATE_UP><<<dim3((total + kWarps - 1) / kWarps, slots), kWarps * 32, smem, stream>>>(indices, x, x_scales, w, s, w2, s2,
+                                                                                                              y_flat, y_table, n, k);
+    return cudaGetLastError();
+}
+
 }  // namespace
 }  // namespace eider
 
 using namespace eider;
 
 extern "C" {
+
+// ---- FP8 W8A8 decode-side MoE slots (crates/eider-cuda/src/ffi.rs:3163-3196) ----------------------------------------------
+cudaError_t infer_fp8_moe_grouped_gate_up_f32_on_stream(const uint32_t* indices, const uint8_t* input, const float* input_scale,
+                                                        const uint8_t* const* gate_weights, const float* const* gate_scales,
+                                                        const uint8_t* const* up_weights, const float* const* up_scales, float* output,
+                                                        uint32_t rows, uint32_t cols, uint32_t slots, cudaStream_t stream) {
+    if (!indices || !input || !input_scale || !gate_weights || !gate_scales || !up_weights || !up_scales || !output || rows == 0 ||
+        cols == 0 || slots == 0)
+        return cudaErrorInvalidValue;
+    return launch_fp8_slots<true>(indices, input, input_scale, gate_weights, gate_scales, up_weights, up_scales, output, nullptr, rows, cols,
+                                  slots, stream);
+}
+
+cudaError_t infer_moe_silu_quantize_fp8_slots_f32_on_stream(const float* gate_up, uint8_t* quantized, float* scales, uint32_t rows,
+                                                            uint32_t slots, cudaStream_t stream) {
+    if (!gate_up || !quantized || !scales || rows == 0 || slots == 0) return cudaErrorInvalidValue;
+    silu_quantize_fp8_slots_kernel<<<slots, 256, 0, stream>>>(gate_up, quantized, scales, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t infer_fp8_moe_grouped_down_f32_on_stream(const uint32_t* indices, const uint8_t* inputs, const float* input_scales,
+                                                     const uint8_t* const* weights, const float* const* weight_scales,
+                                                     float* const* outputs, uint32_t rows, uint32_t cols, uint32_t slots,
+                                                     cudaStream_t stream) {
+    if (!indices || !inputs || !input_scales || !weights || !weight_scales || !outputs || rows == 0 || cols == 0 || slots == 0)
+        return cudaErrorInvalidValue;
+    return launch_fp8_slots<false>(indices, inputs, input_scales, weights, weight_scales, nullptr, nullptr, nullptr, outputs, rows, cols,
+                                   slots, stream);
+}
+
 
 cudaError_t infer_nvfp4_w4a16_grouped_matvec_f32_on_stream(const uint32_t* indices, const float* input,
                                                            const uint8_t* const* packed_weight_table,

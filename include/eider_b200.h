@@ -343,6 +343,24 @@ EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_f32_on_stream
 EIDER_B200_API cudaError_t infer_fp8_linear_channel_scaled_dynamic_quantized_f32_configured_on_stream(
     const float* input, uint8_t* quantized_input, const uint8_t* weight, const float* channel_weight_scale, float* input_scale,
     float* output, uint32_t rows, uint32_t cols, uint32_t threads, cudaStream_t stream);
+/* crates/eider-cuda/src/ffi.rs:3163, :3177 and :3185 (kernels non_gemm.cu:10156-10350): the decode-side routed MoE on FP8
+ * experts.  gate_up: every slot multiplies the one E4M3 activation row (scale input_scale[0]) by its expert's gate and up
+ * matrices [rows][cols] (per-row scales) into output[slot][gate rows | up rows]; silu_quantize: SiLU(gate) * up per slot with
+ * one dynamic scale per slot (amax / 448) into E4M3 codes [slots][rows]; down: every slot multiplies its own code row
+ * (scale input_scales[slot]) by its expert's matrix into outputs[slot].  cols % 16 == 0 and 16-byte aligned weights here. */
+EIDER_B200_API cudaError_t infer_fp8_moe_grouped_gate_up_f32_on_stream(const uint32_t* indices, const uint8_t* input,
+                                                                       const float* input_scale, const uint8_t* const* gate_weights,
+                                                                       const float* const* gate_scales,
+                                                                       const uint8_t* const* up_weights, const float* const* up_scales,
+                                                                       float* output, uint32_t rows, uint32_t cols, uint32_t slots,
+                                                                       cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_moe_silu_quantize_fp8_slots_f32_on_stream(const float* gate_up, uint8_t* quantized, float* scales,
+                                                                           uint32_t rows, uint32_t slots, cudaStream_t stream);
+EIDER_B200_API cudaError_t infer_fp8_moe_grouped_down_f32_on_stream(const uint32_t* indices, const uint8_t* inputs,
+                                                                    const float* input_scales, const uint8_t* const* weights,
+                                                                    const float* const* weight_scales, float* const* outputs,
+                                                                    uint32_t rows, uint32_t cols, uint32_t slots,
+                                                                    cudaStream_t stream);
 /* crates/eider-cuda/src/ffi.rs:3056-3147 (kernels non_gemm.cu:9642-9950): FP8 weight-only linears, f32 activations times
  * E4M3 weights [rows][cols], one weight scale or one per output row; `batch` forms take [batch][cols] inputs and write
  * [batch][rows]; the pair / triple forms run two / three weights on one input.  The "precomputed dynamic" form first writes

@@ -159,6 +159,64 @@ def test_reuse_matvec_over_sorted_routes(lib, oracle):
     assert ok, stats
 
 
+def test_fp8_moe_slots(lib, oracle):
+    # crates/eider-cuda/src/ffi.rs:3163-3196: gate/up GEMV over a shared FP8 activation, SiLU * up -> per-slot dynamic FP8,
+    # down GEMV over per-slot activations; against a host evaluation of the same codes (every product is exact)
+    import torch
+    experts, slots, hidden, inter = 5, 3, 528, 272
+    rng = np.random.default_rng(23)
+
+    def codes(shape):
+        c = rng.integers(0, 256, shape).astype(np.uint8)
+        c[(c & 0x7f) == 0x7f] = 0x31
+        return c
+
+    gate = [codes((inter, hidden)) for _ in range(experts)]
+    up = [codes((inter, hidden)) for _ in range(experts)]
+    down = [codes((hidden, inter)) for _ in range(experts)]
+    gs = [(rng.random(inter) * 0.01 + 1e-3).astype(np.float32) for _ in range(experts)]
+    us = [(rng.random(inter) * 0.01 + 1e-3).astype(np.float32) for _ in range(experts)]
+    ds = [(rng.random(hidden) * 0.01 + 1e-3).astype(np.float32) for _ in range(experts)]
+    x = codes(hidden)
+    idx = np.array([4, 0, 2], np.uint32)
+    dv = lambda arrs: [dev(a) for a in arrs]
+    gate_d, up_d, down_d, gs_d, us_d, ds_d = dv(gate), dv(up), dv(down), dv(gs), dv(us), dv(ds)
+    xd, xs = dev(x), dev(np.array([0.0625], np.float32))
+    idx_d = dev(idx.view(np.int32))
+    gu = torch.zeros(slots, 2 * inter, device="cuda")
+    assert lib.infer_fp8_moe_grouped_gate_up_f32_on_stream(idx_d.data_ptr(), xd.data_ptr(), xs.data_ptr(), table(gate_d).data_ptr(),
+                                                           table(gs_d).data_ptr(), table(up_d).data_ptr(), table(us_d).data_ptr(),
+                                                           gu.data_ptr(), inter, hidden, slots, None) == 0
+    q = torch.zeros(slots, inter, dtype=torch.uint8, device="cuda")
+    qs = torch.zeros(slots, device="cuda")
+    assert lib.infer_moe_silu_quantize_fp8_slots_f32_on_stream(gu.data_ptr(), q.data_ptr(), qs.data_ptr(), inter, slots, None) == 0
+    out = torch.zeros(slots, hidden, device="cuda")
+    assert lib.infer_fp8_moe_grouped_down_f32_on_stream(idx_d.data_ptr(), q.data_ptr(), qs.data_ptr(), table(down_d).data_ptr(),
+                                                        table(ds_d).data_ptr(), table(list(out)).data_ptr(), hidden, inter, slots, None) == 0
+    torch.cuda.synchronize()
+    xv = oracle.e4m3_decode(x).astype(np.float64)
+    for s_, e in enumerate(idx):
+        g_ref = oracle.e4m3_decode(gate[e]).astype(np.float64) @ xv * 0.0625 * gs[e]
+        u_ref = oracle.e4m3_decode(up[e]).astype(np.float64) @ xv * 0.0625 * us[e]
+        got = gu[s_].cpu().numpy()
+        ok, stats = gemm_close(got, np.concatenate([g_ref, u_ref]), rel=1e-4, abs_frac=1e-4)
+        assert ok, stats
+        # the quantizer on the device's own gate/up values: scale and codes follow the reference's formula
+        g32, u32 = got[:inter], got[inter:]
+        with np.errstate(over="ignore"):
+            act = (g32 / (np.float32(1.0) + np.exp(-g32.astype(np.float32)))).astype(np.float32) * u32
+        scale = np.float32(np.abs(act).max()) / np.float32(448.0)
+        assert abs(float(qs[s_].item()) - float(scale)) <= 1e-6 * float(scale)
+        deq = oracle.e4m3_decode(q[s_].cpu().numpy()).astype(np.float64) * float(qs[s_].item())
+        assert np.all(np.abs(deq - act) <= 0.07 * np.abs(act) + 2e-3 * float(scale) * 448)
+        d_ref = oracle.e4m3_decode(down[e]).astype(np.float64) @ oracle.e4m3_decode(q[s_].cpu().numpy()).astype(np.float64) * float(qs[s_].item()) * ds[e]
+        ok, stats = gemm_close(out[s_].cpu().numpy(), d_ref, rel=1e-4, abs_frac=1e-4)
+        assert ok, stats
+    assert lib.infer_moe_silu_quantize_fp8_slots_f32_on_stream(None, q.data_ptr(), qs.data_ptr(), inter, slots, None) == 1
+    assert lib.infer_fp8_moe_grouped_down_f32_on_stream(idx_d.data_ptr(), q.data_ptr(), qs.data_ptr(), table(down_d).data_ptr(),
+                                                        table(ds_d).data_ptr(), table(list(out)).data_ptr(), hidden, inter + 8, slots, None) == 1
+
+
 def test_decode_moe_w4a4_slots(lib, oracle):
     # the W4A4 decode variant: quantized activation row, indexed expert weights with tiled scales, per-expert alpha;
     # then SiLU * up -> NVFP4 with simple scales per slot, bit-exact against the host quantizer on the device's own values
