@@ -232,3 +232,50 @@ def test_decode_rejects_bad_arguments(ops):
     plan = lib.eider_b200_nvfp4_decode_create(4, 128, 128)
     assert lib.eider_b200_nvfp4_w4a16_gemv_on_stream(plan, None, 1, 1, None, None, 1.0, None, None, 0.0, 1, None) == 1
     lib.eider_b200_decode_destroy(plan)
+
+
+def test_prepared_activation_entry_points_reject_bad_arguments(ops):
+    # argument checks of the operand object and of the GEMVs on prepared activations, all before any launch
+    import torch
+    from eider_b200 import _lib
+    lib = _lib.load()
+    assert not lib.eider_b200_nvfp4_decode_operand_create(9, 256)   # at most eight tokens
+    assert not lib.eider_b200_nvfp4_decode_operand_create(1, 48)    # K in multiples of 32
+    op = lib.eider_b200_nvfp4_decode_operand_create(8, 256)
+    plan = lib.eider_b200_nvfp4_decode_create(8, 128, 256)
+    other = lib.eider_b200_nvfp4_decode_create(8, 128, 512)
+    assert op and plan and other
+    x = torch.randn(8, 256, device="cuda")
+    w = torch.zeros(128, 128, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(128 * 16, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(8, 128, dtype=torch.bfloat16, device="cuda")
+    try:
+        # nothing expanded yet: the operand holds no tokens
+        assert lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(plan, op, w.data_ptr(), s.data_ptr(), 1.0, None, y.data_ptr(), 0.0, 1, None) == 1
+        # eight terms x five f32 tokens do not fit the 32 operand rows; nine tokens exceed the operand
+        assert lib.eider_b200_nvfp4_decode_operand_expand_on_stream(op, x.data_ptr(), 0, 5, None) == 1
+        assert lib.eider_b200_nvfp4_decode_operand_expand_on_stream(op, x.data_ptr(), 1, 9, None) == 1
+        assert lib.eider_b200_nvfp4_decode_operand_expand_on_stream(op, None, 1, 1, None) == 1
+        assert lib.eider_b200_nvfp4_decode_operand_expand_on_stream(op, x.data_ptr(), 0, 4, None) == 0
+        # a plan of another K, a missing weight, beta without C
+        assert lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(other, op, w.data_ptr(), s.data_ptr(), 1.0, None, y.data_ptr(), 0.0, 1, None) == 1
+        assert lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(plan, op, None, s.data_ptr(), 1.0, None, y.data_ptr(), 0.0, 1, None) == 1
+        assert lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(plan, op, w.data_ptr(), s.data_ptr(), 1.0, None, y.data_ptr(), 0.5, 1, None) == 1
+        assert lib.eider_b200_nvfp4_w4a16_gemv_prepared_on_stream(plan, op, w.data_ptr(), s.data_ptr(), 1.0, None, y.data_ptr(), 0.0, 1, None) == 0
+        torch.cuda.synchronize()
+        fplan = lib.eider_b200_fp8_decode_create(64, 128, 256)
+        codes = torch.zeros(8, 256, dtype=torch.uint8, device="cuda")
+        scales = torch.ones(8, device="cuda")
+        w8 = torch.zeros(128, 256, dtype=torch.uint8, device="cuda")
+        assert lib.eider_b200_fp8_linear_decode_quantized_on_stream(fplan, None, scales.data_ptr(), 8, w8.data_ptr(), None, 1.0, y.data_ptr(), 1, None) == 1
+        assert lib.eider_b200_fp8_linear_decode_quantized_on_stream(fplan, codes.data_ptr(), None, 8, w8.data_ptr(), None, 1.0, y.data_ptr(), 1, None) == 1
+        assert lib.eider_b200_fp8_linear_decode_quantized_on_stream(fplan, codes.data_ptr(), scales.data_ptr(), 65, w8.data_ptr(), None, 1.0, y.data_ptr(), 1, None) == 1
+        assert lib.eider_b200_fp8_linear_decode_quantized_on_stream(plan, codes.data_ptr(), scales.data_ptr(), 8, w8.data_ptr(), None, 1.0, y.data_ptr(), 1, None) == 1
+        assert lib.eider_b200_fp8_linear_decode_quantized_on_stream(fplan, codes.data_ptr(), scales.data_ptr(), 8, w8.data_ptr(), None, 1.0, y.data_ptr(), 1, None) == 0
+        torch.cuda.synchronize()
+        assert torch.all(y == 0)
+        lib.eider_b200_decode_destroy(fplan)
+    finally:
+        lib.eider_b200_decode_destroy(plan)
+        lib.eider_b200_decode_destroy(other)
+        lib.eider_b200_nvfp4_decode_operand_destroy(op)
