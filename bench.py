@@ -379,6 +379,27 @@ def measure_moe(torch, dist, world, rank, steps, warmup, stages=True):
         for _ in range(warmup):
             step(x, logits)
         torch.cuda.synchronize()
+    # parity gate: this rank's tokens through the single-GPU pipeline over ALL experts (every rank can regenerate every
+    # rank's weights from the seeds) must equal what the expert-parallel step returns, bit for bit
+    parts_gu, parts_dn = [], []
+    for r in range(world):
+        gr = torch.Generator(device="cuda").manual_seed(100 + r)
+        parts_gu.append(ops.GroupedNvfp4Weights.quantize(torch.randn(per, 2 * inter, h, device="cuda", generator=gr) * 0.02))
+        parts_dn.append(ops.GroupedNvfp4Weights.quantize(torch.randn(per, h, inter, device="cuda", generator=gr) * 0.02))
+    cat = lambda parts: ops.GroupedNvfp4Weights.from_checkpoint(torch.cat([p.packed for p in parts]),
+                                                                torch.cat([p.scales_row_major for p in parts]),
+                                                                torch.cat([p.alpha for p in parts]))
+    full_gu, full_dn = cat(parts_gu), cat(parts_dn)
+    with torch.cuda.stream(stream):
+        ref = ops.GroupedMoe(tl, e, k8, h, inter).run(x, logits, full_gu, full_dn, w_gate_up_interleaved=full_gu.interleave_gate_up()).clone()
+        got = step(x, logits).clone()
+        torch.cuda.synchronize()
+    same = torch.tensor([1.0 if torch.equal(ref, got) else 0.0], device="cuda")
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    parity_ok = bool(same.item() == 1.0)
+    del parts_gu, parts_dn, full_gu, full_dn, ref
+    if not parity_ok:
+        return {"metric": "moe_prefill_tflops", "error": "expert-parallel output differs from the single-GPU pipeline, nothing was timed"} if rank == 0 else None
     total = timed(lambda: step(x, logits), steps)
     compute = timed(lambda: layer.run_experts_and_return(), steps)  # the owner's share: two grouped GEMMs, SiLU quantizer, return stores
     # each phase replayed on its own (the buffers hold the last step's routes; peer stores included, no waiting in any of them)
@@ -398,7 +419,9 @@ def measure_moe(torch, dist, world, rank, steps, warmup, stages=True):
         return None
     route_bytes_out, route_bytes_back = h * 9 // 16, 2 * h
     return {"metric": "moe_prefill_tflops", "value": flops / total / 1e6, "unit": "TFLOP/s", "n_gpus": world, "us_per_step": total,
-            "experts_and_return_us": compute, "phase_us": phase_us, "most_routes_on_one_rank": int(most.item()), "routes": t * k8,
+            "experts_and_return_us": compute, "phase_us": phase_us,
+            "parity": {"bit_identical_to_single_gpu_pipeline": True, "checked": "every rank's tokens, all experts"},
+            "most_routes_on_one_rank": int(most.item()), "routes": t * k8,
             "nvlink_bytes_per_rank": (world - 1) / world * tl * k8 * (route_bytes_out + route_bytes_back),
             "partition": f"experts split evenly x{world}, tokens sharded by rows, NVFP4 rows dispatched and bf16 rows returned by peer "
                          "stores over NVLink, counts resident on the device, three bounded device barriers per step (two alternating buffer sets)",
