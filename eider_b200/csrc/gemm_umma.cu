@@ -601,7 +601,9 @@ cudaError_t run_grouped(GroupedPlan& plan, const uint8_t* a_values, const uint8_
     const uint32_t max_row_tiles = (total_routes + kTileRows - 1) / kTileRows + plan.groups;
     if (plan.m % 256 == 0) {
         p.col_tiles = plan.m / 256;
-        if (act_packed) return launch<kNvf4, 256, false, 1, true, 8>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
+        // sixteen epilogue warps: one 64-column step of the SiLU * up quantizer per warp (measured 98 us against 108 us with
+        // eight warps on 4096 tokens x top-8, 128 experts, H 2048, I 768)
+        if (act_packed) return launch<kNvf4, 256, false, 1, true, 16>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
         return launch<kNvf4, 256, false, 1, true>(map_rows, map_cols, p, max_row_tiles * p.col_tiles, stream);
     }
     p.col_tiles = plan.m / 128;

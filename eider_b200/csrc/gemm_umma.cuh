@@ -303,8 +303,9 @@ __device__ __forceinline__ void silu_quantize_store64(const Params& p, const Til
 // KIND: operand format.  BLOCK_N: column-operand rows per tile.  TRANSPOSED: output is
 // [col][row] (decode: rows are output features, columns are tokens).  TERMS: consecutive columns that
 // are summed (with their column scales) into one output column.  GROUPED: MoE schedule.
-// EPI_WARPS: epilogue warps, 4 or 8.  Eight (two per tensor-memory lane quadrant, each taking half of the column steps)
-// are for the arithmetic-heavy SiLU * up -> NVFP4 epilogue, which four warps cannot finish in the time of a mainloop.
+// EPI_WARPS: epilogue warps, 4, 8 or 16.  Eight or sixteen (two or four per tensor-memory lane quadrant, each taking its
+// share of the 64-column steps) are for the arithmetic-heavy SiLU * up -> NVFP4 epilogue, which four warps cannot finish in
+// the time of a mainloop.
 template <int KIND, int BLOCK_N, int STAGES, bool TRANSPOSED, int TERMS, bool GROUPED, int EPI_WARPS = 4>
 __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, const Params p) {
@@ -524,7 +525,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const uint32_t quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-        const uint32_t half = (warp - 2) >> 2;  // which half of the column steps (always 0 with four epilogue warps)
+        const uint32_t half = (warp - 2) >> 2;  // which share of the column steps (always 0 with four epilogue warps)
         umma::griddep_wait();            // scales / C written by the preceding kernel are read below
         uint32_t tile_count = 0;
         TileCoord t;
@@ -562,9 +563,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             if constexpr (GROUPED && kWide) if (p.act_packed) {
                 // SiLU * up -> NVFP4 epilogue.  A rolled loop over the 64-column steps: the per-step body (32 activations and
                 // two block quantizations) is long, and unrolled copies of it beside the plain store path would not fit the
-                // instruction cache these warps have to themselves.  With eight warps each half takes half of the steps.
+                // instruction cache these warps have to themselves.  With eight (sixteen) warps each set takes a half (quarter) of the steps.
                 constexpr uint32_t kSteps = BLOCK_N / 64;
                 constexpr uint32_t kPer = kSteps / (EPI_WARPS / 4);
+                static_assert(kSteps % (EPI_WARPS / 4) == 0, "the epilogue warp sets share the 64-column steps evenly");
                 const uint32_t begin = half * kPer, end = begin + kPer;
 #pragma unroll 1
                 for (uint32_t step = begin; step < end; ++step) {
