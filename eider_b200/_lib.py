@@ -122,6 +122,8 @@ SIGNATURES = {
     "infer_moe_weighted_accumulate_sorted_bf16_batch_on_stream": (_I, [_P, _P, _P, _P, _U32, _U32, _U32, _P]),
     "eider_b200_gemm_plan_set_block_n": (_I, [_P, _U32]),
     "eider_b200_gemm_plan_block_n": (_U32, [_P]),
+    "eider_b200_gemm_plan_set_k_splits": (_I, [_P, _U32]),
+    "eider_b200_gemm_plan_k_splits": (_U32, [_P]),
     "eider_b200_gemm_plan_set_output_peers": (_I, [_P, _P, _U32, _U32]),
     "eider_b200_gemm_plan_status": (_I, [_P, _P]),
     "eider_b200_gemm_plan_set_output_multicast": (_I, [_P, _P]),

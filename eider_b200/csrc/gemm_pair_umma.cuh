@@ -40,15 +40,22 @@ struct PairTile {
     uint32_t row_tile;  // this CTA's 128-row tile (may be one past the last when the row-tile count is odd)
     uint32_t row0;
     uint32_t col0;      // first weight row of the pair tile
+    uint32_t k0, k1;    // K stages of this work item (all of them unless K is split)
+    uint32_t split;
 };
 
 __device__ __forceinline__ bool pair_tile(const Params& p, uint32_t item, uint32_t rank, PairTile& t) {
     const uint32_t row_pairs = (p.row_tiles + 1) / 2;
-    if (item >= row_pairs * p.col_tiles) return false;
+    if (item >= row_pairs * p.col_tiles * p.splits) return false;
     const uint32_t rp = item % row_pairs;  // row pairs fastest: neighbouring pairs share the weight tile in L2
+    const uint32_t rest = item / row_pairs;
     t.row_tile = rp * 2 + rank;
     t.row0 = t.row_tile * kTileRows;
-    t.col0 = (item / row_pairs) * kPairN;
+    t.col0 = (rest % p.col_tiles) * kPairN;
+    t.split = rest / p.col_tiles;
+    const uint32_t per = (p.k_stages + p.splits - 1) / p.splits;
+    t.k0 = t.split * per;
+    t.k1 = min(p.k_stages, t.k0 + per);
     return true;
 }
 
@@ -118,7 +125,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             const bool row_sf = kNv && t.row_tile < p.row_tiles;
             const uint32_t sf_col_tile0 = t.col0 / kTileRows;
             const bool second_sf = sf_col_tile0 + 1 < sf_col_tiles;
-            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+            for (uint32_t s = t.k0; s < t.k1; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&empty[stage], phase ^ 1, abort_flag, p.status, umma::kTimeoutEmpty))) { ok = false; break; }
@@ -158,7 +165,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         PairTile t;
         bool ok = true;
         for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
-            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+            for (uint32_t s = t.k0; s < t.k1; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
@@ -188,7 +195,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
             umma::tc_fence_after();
             const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
-            for (uint32_t s = 0; s < p.k_stages; ++s, ++it) {
+            for (uint32_t s = t.k0; s < t.k1; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&full[stage], phase, abort_flag, p.status, umma::kTimeoutFull))) { ok = false; break; }
@@ -211,7 +218,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                             }
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
                             const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
-                            const uint32_t accumulate = (s > 0 || j > 0) ? 1u : 0u;
+                            const uint32_t accumulate = (s > t.k0 || j > 0) ? 1u : 0u;
                             if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
                             else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         }
@@ -226,7 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                         for (uint32_t j = 0; j < nkb; ++j) {
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
                             const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
-                            const uint32_t accumulate = (s > 0 || j > 0) ? 1u : 0u;
+                            const uint32_t accumulate = (s > t.k0 || j > 0) ? 1u : 0u;
                             if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
                             else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         }
@@ -344,6 +351,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                     continue;
                 }
                 if (!row_ok || t.col0 + c >= p.cols) continue;
+                if (p.split_stride != 0) {
+                    // split K: this split's unscaled fp32 partial sums (the host sets alpha 1 and no scales on this path)
+                    float* dst = static_cast<float*>(p.out) + static_cast<size_t>(t.split) * p.split_stride + static_cast<size_t>(row) * p.ld_out + t.col0 + c;
+                    if (t.col0 + c + 64 <= p.cols && (p.ld_out % 4) == 0) {
+#pragma unroll
+                        for (uint32_t q = 0; q < 16; ++q)
+                            reinterpret_cast<float4*>(dst)[q] = make_float4(__uint_as_float(raw[step & 1][4 * q]), __uint_as_float(raw[step & 1][4 * q + 1]),
+                                                                            __uint_as_float(raw[step & 1][4 * q + 2]), __uint_as_float(raw[step & 1][4 * q + 3]));
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 64; ++i)
+                            if (t.col0 + c + i < p.cols) dst[i] = __uint_as_float(raw[step & 1][i]);
+                    }
+                    continue;
+                }
                 if (wide && t.col0 + c + 64 <= p.cols) {  // (a tile that hangs over the last column still stores its whole 64-column steps wide)
                     store_row64_all(p, static_cast<size_t>(row) * p.ld_out + t.col0 + c, &raw[step & 1][0], rs,
                                     p.col_scale ? p.col_scale + t.col0 + c : nullptr);

@@ -220,6 +220,10 @@ struct DensePlan {
     CUtensorMap* peer_maps; // device array of n_peers bf16 tensor maps over the same column blocks (TMA-store epilogue)
     void* multicast;        // the same column block inside an NVLink multicast mapping of every rank's output (null = off)
     MapCache maps_x, maps_w;
+    // Row-major split K (few tiles, long K): 0 or 1 = off.  The workspace holds `splits` fp32 copies of the output.
+    uint32_t splits;
+    float* workspace;
+    size_t workspace_elems;
 };
 
 enum DecodePath : uint32_t { kDecodeAuto = 0, kDecodeStream = 1, kDecodeFused = 2, kDecodeSplit = 3, kDecodeFusedMany = 4 };
@@ -303,6 +307,60 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
     return best;
 }
 
+// Row-major split K.  A launch whose tiles fill only part of the device streams each tile's whole K through one SM at that
+// SM's load rate; splitting K over the idle SMs shortens that at the price of fp32 partial sums written by the GEMM and read
+// by a reduce kernel.  The partial sums cost more than the idle SMs give back as soon as there is more than one row tile
+// (measured, K 13824 -> N 5120: 64 tokens 19.2 -> 16.7 us and 128 tokens 19.0 -> 18.2 us with three splits, but 256 tokens
+// 20.0 -> 29.8 us with two and 512 tokens 24.7 -> 40.7 us with three), so a plan only chooses a split for a single row tile;
+// the count comes from a coarse model (0.6 us per 128-byte K stage and wave, partials written at 10 TB/s and read at 6 TB/s,
+// 2 us per extra launch, at least eight stages per split, a predicted gain of 15 %).
+uint32_t pick_k_splits(int kind, uint32_t m, uint32_t n, uint32_t k, uint32_t block_n) {
+    const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
+    if (row_tiles > 1) return 1;
+    const uint32_t stages = ((kind == kNvf4 ? k / 2 : k) + kStageBytesK - 1) / kStageBytesK;
+    const bool pair = block_n == kPairBlockCode;
+    const uint32_t slots = pair ? static_cast<uint32_t>(sm_count()) / 2 : static_cast<uint32_t>(sm_count());
+    const uint32_t items = pair ? ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN) : row_tiles * ((n + block_n - 1) / block_n);
+    if (slots == 0) return 1;
+    const float out_mb = static_cast<float>(m) * static_cast<float>(n) * 4.0f * 1e-6f;
+    auto cost = [&](uint32_t s) {
+        const uint32_t per = (stages + s - 1) / s;
+        float t = static_cast<float>((items * s + slots - 1) / slots) * static_cast<float>(per) * 0.6f;
+        if (s > 1) t += s * out_mb / 10.0f + 2.0f + (s * out_mb + 0.5f * out_mb) / 6.0f;
+        return t;
+    };
+    uint32_t best = 1;
+    float best_cost = cost(1) * 0.85f;
+    for (uint32_t s : {2u, 3u, 4u, 5u, 6u, 8u}) {
+        const uint32_t per = (stages + s - 1) / s;
+        if (per < 8 || (s - 1) * per >= stages) continue;
+        const float c = cost(s);
+        if (c < best_cost) {
+            best_cost = c;
+            best = s;
+        }
+    }
+    return best;
+}
+
+// Sets the plan's split count and makes sure the workspace can hold the partial sums (nothing changes on failure).
+cudaError_t set_k_splits(DensePlan& plan, uint32_t splits) {
+    const uint32_t stages = ((plan.kind == kNvf4 ? plan.k / 2 : plan.k) + kStageBytesK - 1) / kStageBytesK;
+    if (splits == 0 || splits > 16) return cudaErrorInvalidValue;
+    if (splits > 1 && (splits - 1) * ((stages + splits - 1) / splits) >= stages) return cudaErrorInvalidValue;  // an empty split
+    const size_t need = splits > 1 ? static_cast<size_t>(splits) * plan.m * plan.n : 0;
+    if (need > plan.workspace_elems) {
+        float* ws = nullptr;
+        cudaError_t st = cudaMalloc(reinterpret_cast<void**>(&ws), need * sizeof(float));
+        if (st != cudaSuccess) return st;
+        cudaFree(plan.workspace);
+        plan.workspace = ws;
+        plan.workspace_elems = need;
+    }
+    plan.splits = splits;
+    return cudaSuccess;
+}
+
 }  // namespace
 
 cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x_scales, const uint8_t* w_values,
@@ -355,15 +413,57 @@ cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x
             p.out_maps = nullptr;
         }
     }
+    // split K: the GEMM writes unscaled fp32 partial sums, one copy of the output per split, and a dependent launch sums,
+    // scales and converts them (not with the fused all-gather, whose tiles leave the GPU from the GEMM's epilogue)
+    const bool split = plan.splits > 1 && plan.n_peers == 0;
+    SplitRowsReduce red{};
+    if (split) {
+        red.workspace = plan.workspace;
+        red.split_stride = static_cast<size_t>(plan.m) * plan.n;
+        red.splits = plan.splits;
+        red.rows = plan.m;
+        red.cols = plan.n;
+        red.ld_out = plan.n;
+        red.alpha = alpha;
+        red.beta = beta;
+        red.row_scale = token_scale;
+        red.col_scale = channel_scale;
+        red.c_in = c;
+        red.out = d;
+        red.out_is_bf16 = out_is_bf16;
+        p.out = plan.workspace;
+        p.c_in = nullptr;
+        p.out_is_bf16 = 0;
+        p.alpha = 1.0f;
+        p.beta = 0.0f;
+        p.row_scale = nullptr;
+        p.col_scale = nullptr;
+        p.splits = plan.splits;
+        p.split_stride = red.split_stride;
+    }
+    auto reduce = [&](cudaError_t launched) {
+        if (!split || launched != cudaSuccess) return launched;
+        const size_t quads = static_cast<size_t>(plan.m) * ((plan.n + 3) / 4);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<uint32_t>(std::min<size_t>((quads + 255) / 256, static_cast<size_t>(sm_count()) * 8)));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, splitk_rows_reduce_kernel, red);
+    };
     if (plan.block_n == kPairBlockCode) {
         // 256 x 256 tiles on CTA pairs
         p.col_tiles = (plan.n + kPairN - 1) / kPairN;
-        const uint32_t pair_items = ((p.row_tiles + 1) / 2) * p.col_tiles;
-        return nv ? launch_pair<kNvf4>(map_rows, map_cols, p, pair_items, stream)
-                  : launch_pair<kFp8>(map_rows, map_cols, p, pair_items, stream);
+        const uint32_t pair_items = ((p.row_tiles + 1) / 2) * p.col_tiles * p.splits;
+        return reduce(nv ? launch_pair<kNvf4>(map_rows, map_cols, p, pair_items, stream)
+                         : launch_pair<kFp8>(map_rows, map_cols, p, pair_items, stream));
     }
-    const uint32_t items = p.row_tiles * p.col_tiles;
-#define EIDER_DENSE(KIND, BN) launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream)
+    const uint32_t items = p.row_tiles * p.col_tiles * p.splits;
+#define EIDER_DENSE(KIND, BN) reduce(launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream))
     if (nv) {
         if (plan.block_n == 256) return EIDER_DENSE(kNvf4, 256);
         if (plan.block_n == 192) return EIDER_DENSE(kNvf4, 192);
@@ -629,6 +729,7 @@ void* eider_b200_nvfp4_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
         delete plan;
         return nullptr;
     }
+    if (set_k_splits(*plan, pick_k_splits(kNvf4, m, n, k, plan->block_n)) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
     return plan;
 }
 
@@ -637,6 +738,7 @@ void eider_b200_nvfp4_gemm_tn_destroy(void* raw) {
     if (!plan) return;
     cudaFree(plan->status);
     cudaFree(plan->peer_maps);
+    cudaFree(plan->workspace);
     delete plan;
 }
 
@@ -654,7 +756,20 @@ int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     auto* plan = static_cast<DensePlan*>(raw);
     if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256 && block_n != kPairBlockCode)) return 0;
     plan->block_n = block_n;
+    // the split count goes with the tile shape
+    if (set_k_splits(*plan, pick_k_splits(plan->kind, plan->m, plan->n, plan->k, block_n)) != cudaSuccess) plan->splits = 1;
     return 1;
+}
+
+cudaError_t eider_b200_gemm_plan_set_k_splits(void* raw, uint32_t splits) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    if (!plan) return cudaErrorInvalidValue;
+    return set_k_splits(*plan, splits);
+}
+
+uint32_t eider_b200_gemm_plan_k_splits(void* raw) {
+    auto* plan = static_cast<DensePlan*>(raw);
+    return plan ? (plan->splits > 1 ? plan->splits : 1) : 0;
 }
 
 cudaError_t eider_b200_gemm_plan_set_output_peers(void* raw, void* const* peers, uint32_t count, uint32_t ld_out) {
@@ -716,6 +831,7 @@ void* eider_b200_fp8_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
         delete plan;
         return nullptr;
     }
+    if (set_k_splits(*plan, pick_k_splits(kFp8, m, n, k, plan->block_n)) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
     return plan;
 }
 

@@ -55,6 +55,9 @@ struct Params {
     float* workspace;        // [splits][out_cols][row_tiles*128] fp32 partials
     uint32_t* counters;      // [row_tiles] arrival counters, self-resetting
     uint32_t defer_reduce;   // split K: leave the partial sums in `workspace` for splitk_reduce_kernel (many output columns)
+    // Row-major split K (prefill with few tiles and a long K): `out` is an fp32 workspace, split s writes its unscaled
+    // partial sums at out + s * split_stride elements, and splitk_rows_reduce_kernel sums, scales and converts them.
+    size_t split_stride;     // 0 = not in use
     // grouped (MoE): per-group row ranges of the row operand
     const uint32_t* group_offsets;  // [groups + 1] or null
     uint32_t groups;
@@ -541,6 +544,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
             float rs = GROUPED ? (p.group_alpha ? p.group_alpha[t.group] : p.alpha) : p.alpha;
             if (p.row_scale && row_ok) rs *= p.row_scale[row];
             size_t row_elems = static_cast<size_t>(row) * p.ld_out;  // element offset of this thread's output row from `out`
+            if (!TRANSPOSED && !GROUPED) row_elems += static_cast<size_t>(t.split) * p.split_stride;
             bool out_aligned32 = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             if constexpr (GROUPED) if (p.group_maps) {
                 // pointer tables: the group's own output buffer and alpha; `out` is null, so the offset carries the address
@@ -782,6 +786,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant_
     if (warp == 1) {
         umma::tc_fence_after();
         umma::tmem_dealloc(tmem_base, T::kAlloc);
+    }
+}
+
+// Row-major split K: out[r][c] = (sum over splits, in split order, of workspace[s][r][c]) * alpha * row_scale[r] * col_scale[c]
+// (+ beta * c_in[r][c]), the operations of the GEMM epilogue in the same order.  Four columns per thread; a programmatic
+// dependent launch behind the GEMM.
+struct SplitRowsReduce {
+    const float* workspace;
+    size_t split_stride;
+    uint32_t splits, rows, cols, ld_out;
+    float alpha, beta;
+    const float* row_scale;
+    const float* col_scale;
+    const void* c_in;
+    void* out;
+    int out_is_bf16;
+};
+__global__ void __launch_bounds__(256) splitk_rows_reduce_kernel(const SplitRowsReduce a) {
+    umma::griddep_wait();
+    const uint32_t quads = (a.cols + 3) / 4;
+    const size_t total = static_cast<size_t>(a.rows) * quads;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t row = static_cast<uint32_t>(i / quads);
+        const uint32_t col = static_cast<uint32_t>(i % quads) * 4;
+        const size_t src = static_cast<size_t>(row) * a.cols + col;
+        const bool whole = col + 4 <= a.cols && (a.cols % 4) == 0;
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t sp = 0; sp < a.splits; ++sp) {
+            const float* part = a.workspace + sp * a.split_stride + src;
+            if (whole) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(part));
+                sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+            } else {
+                for (uint32_t j = 0; j < 4 && col + j < a.cols; ++j) sum[j] += __ldcg(part + j);
+            }
+        }
+        float rs = a.alpha;
+        if (a.row_scale) rs *= a.row_scale[row];
+        for (uint32_t j = 0; j < 4 && col + j < a.cols; ++j) {
+            const size_t index = static_cast<size_t>(row) * a.ld_out + col + j;
+            float x = sum[j] * rs;
+            if (a.col_scale) x *= a.col_scale[col + j];
+            if (a.beta != 0.0f && a.c_in)
+                x = fmaf(a.beta, a.out_is_bf16 ? bf16_bits_to_float(static_cast<const uint16_t*>(a.c_in)[index])
+                                               : static_cast<const float*>(a.c_in)[index], x);
+            if (a.out_is_bf16) static_cast<uint16_t*>(a.out)[index] = float_to_bf16_bits(x);
+            else static_cast<float*>(a.out)[index] = x;
+        }
     }
 }
 

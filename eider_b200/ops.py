@@ -190,6 +190,14 @@ class Fp4TnMatmulPlan:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
             raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
 
+    @property
+    def k_splits(self) -> int:
+        """K splits in use (1 = none); chosen by the plan for shapes with few tiles and a long K."""
+        return int(self._lib.eider_b200_gemm_plan_k_splits(self._plan))
+
+    def set_k_splits(self, splits: int) -> None:
+        check("eider_b200_gemm_plan_set_k_splits", self._lib.eider_b200_gemm_plan_set_k_splits(self._plan, splits))
+
     def run(self, x: Nvfp4Matrix, w: ModelOptWeight, out: torch.Tensor | None = None, alpha: float | None = None,
             beta: float = 0.0, c: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
         if x.rows != self.m or x.k != self.k or w.out_features != self.n or w.in_features != self.k:
@@ -260,6 +268,14 @@ class Fp8TnMatmulPlan:
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
             raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
+
+    @property
+    def k_splits(self) -> int:
+        """K splits in use (1 = none); chosen by the plan for shapes with few tiles and a long K."""
+        return int(self._lib.eider_b200_gemm_plan_k_splits(self._plan))
+
+    def set_k_splits(self, splits: int) -> None:
+        check("eider_b200_gemm_plan_set_k_splits", self._lib.eider_b200_gemm_plan_set_k_splits(self._plan, splits))
 
     def run(self, xq: torch.Tensor, wq: torch.Tensor, token_scale: torch.Tensor | None,
             channel_scale: torch.Tensor | None, out: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0,

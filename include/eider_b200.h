@@ -532,6 +532,16 @@ EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_st
  * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
 EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
 EIDER_B200_API uint32_t eider_b200_gemm_plan_block_n(void* plan); /* the tile code in use (0 for a null plan) */
+/* Split K of a dense plan (no reference counterpart; the reference's cuBLASLt heuristics choose theirs).  A shape with few
+ * output tiles and a long K (a 128..512-token chunk through a down projection) leaves most SMs idle while a few stream the
+ * whole K; with `splits` > 1 every tile's K range is divided over that many work items, which write fp32 partial sums into
+ * a workspace the plan owns (splits x tokens x out_features floats, allocated by this call or at creation), and a dependent
+ * launch sums them in split order and applies alpha, the scales, beta * C and the output conversion exactly as the
+ * unsplit epilogue does.  Plans choose a split count themselves at creation and when the tile shape is set; this call
+ * overrides it (1 = off; at most 16; cudaErrorInvalidValue when a split would be empty).  Ignored while the fused
+ * all-gather is on. */
+EIDER_B200_API cudaError_t eider_b200_gemm_plan_set_k_splits(void* plan, uint32_t splits);
+EIDER_B200_API uint32_t eider_b200_gemm_plan_k_splits(void* plan); /* the split count in use (0 for a null plan) */
 /* Fused all-gather for a column-sharded dense layer (no reference counterpart: the reference is single-GPU).  peers[q]
  * points at this rank's first output column inside rank q's full [tokens][ld_out] output (its own buffer included),
  * mapped into this process (CUDA IPC / symmetric memory), 32-byte aligned; count <= 8.  While set, the GEMM's epilogue

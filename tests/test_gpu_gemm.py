@@ -34,7 +34,7 @@ def _lcg(seed, count):
     return out
 
 
-def _nvfp4_case(ops, oracle, x, w, block_n=None, rowscale=False, out_dtype="f32", alpha=None, beta=0.0):
+def _nvfp4_case(ops, oracle, x, w, block_n=None, rowscale=False, out_dtype="f32", alpha=None, beta=0.0, splits=None):
     import torch
     m, k = x.shape
     n = w.shape[0]
@@ -52,6 +52,9 @@ def _nvfp4_case(ops, oracle, x, w, block_n=None, rowscale=False, out_dtype="f32"
     plan = ops.Fp4TnMatmulPlan(m, n, k)
     if block_n:
         plan.set_block_n(block_n)
+    if splits is not None:
+        plan.set_k_splits(splits)  # (after the tile shape: setting that one lets the plan choose its own split count again)
+        assert plan.k_splits == splits
     dt = torch.float32 if out_dtype == "f32" else torch.bfloat16
     a = float(g) if alpha is None else alpha
     rng = np.random.default_rng(1)
@@ -197,6 +200,52 @@ def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k):
     ref = oracle.fp8_linear(xq.cpu().numpy(), xs.cpu().numpy(), wq.cpu().numpy(), ws.cpu().numpy())
     ok, stats = gemm_close(to_np(y), ref)
     assert ok, stats
+
+
+@pytest.mark.parametrize("m,n,k,block_n,splits", [(128, 320, 4096, 128, 3), (100, 264, 2080, 64, 2), (128, 512, 4096, 256, 2),
+                                                   (256, 512, 4096, 512, 4), (300, 328, 2336, 512, 2), (40, 5120, 13824, 128, 3)])
+@pytest.mark.parametrize("out_dtype,beta,rowscale", [("bf16", 0.0, True), ("f32", 0.5, False)])
+def test_nvfp4_gemm_split_k(ops, oracle, m, n, k, block_n, splits, out_dtype, beta, rowscale):
+    # K divided over several work items per tile, fp32 partial sums summed by a second kernel: same criterion as unsplit
+    rng = np.random.default_rng(m + n + k + splits)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    _nvfp4_case(ops, oracle, x, w, block_n=block_n, rowscale=rowscale, out_dtype=out_dtype, beta=beta, splits=splits)
+
+
+@pytest.mark.parametrize("block_n,splits", [(128, 3), (512, 2)])
+def test_fp8_gemm_split_k(ops, oracle, block_n, splits):
+    import torch
+    m, n, k = 200, 328, 2064
+    rng = np.random.default_rng(7)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = oracle.bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    wq, ws = ops.quantize_fp8_weight(_dev(w))
+    xq, xs = ops.quantize_fp8_dynamic(_dev(x, torch.bfloat16))
+    plan = ops.Fp8TnMatmulPlan(m, n, k)
+    plan.set_block_n(block_n)
+    plan.set_k_splits(splits)
+    y = plan.run(xq, wq, xs, ws, out_dtype=torch.bfloat16)
+    assert plan.status() == 0
+    ref = oracle.fp8_linear(xq.cpu().numpy(), xs.cpu().numpy(), wq.cpu().numpy(), ws.cpu().numpy())
+    ok, stats = gemm_close(to_np(y), ref)
+    assert ok, stats
+
+
+def test_split_k_choice_and_argument_checks(ops):
+    from eider_b200._lib import CudaError
+    # few tiles and a long K: split; enough tiles, or a short K: not
+    assert ops.Fp4TnMatmulPlan(128, 5120, 13824).k_splits == 3
+    assert ops.Fp4TnMatmulPlan(512, 27648, 5120).k_splits == 1
+    assert ops.Fp4TnMatmulPlan(128, 27648, 5120).k_splits == 1
+    assert ops.Fp4TnMatmulPlan(4096, 5120, 13824).k_splits == 1
+    assert ops.Fp4TnMatmulPlan(256, 5120, 13824).k_splits == 1  # (more than one row tile: the partial sums cost more than they save)
+    plan = ops.Fp4TnMatmulPlan(128, 256, 512)  # two 128-byte K stages
+    for bad in (0, 17, 3):
+        with pytest.raises(CudaError):
+            plan.set_k_splits(bad)
+    plan.set_k_splits(2)
+    assert plan.k_splits == 2
 
 
 def test_gemm_rejects_bad_arguments(ops):
