@@ -127,6 +127,14 @@ __device__ __forceinline__ float div_rn(float x, const Divisor& D) {
     const float aq = fabsf(q0);
     return (aq == 0.0f || aq == __int_as_float(0x7f800000)) ? q0 : q;
 }
+// The same quotient for a finite x and a divisor in the fast range, without the two comparisons: x * r never overflows for
+// the quantizers' operands, an underflowed q0 = +-0 leaves q = RN(x r) = q0, and the only case where q and q0 differ in
+// more than the last place's correction is x = -0 (e = +0, q = +0), which the sign of x restores.  NaN stays NaN.
+__device__ __forceinline__ float div_rn_finite(float x, const Divisor& D) {
+    const float q0 = x * D.r;
+    const float e = fmaf(-q0, D.d, x);
+    return copysignf(fmaf(e, D.r, q0), x);
+}
 // Row scale of the on-the-fly quantizer: the smallest power of two g with amax / g <= 2688 (1 for amax == 0), so that
 // x / g is exact and the largest block scale still fits E4M3.  2688 = 1.3125 * 2^11.
 __device__ __forceinline__ float row_scale_pow2(float amax) {
@@ -162,6 +170,26 @@ __device__ __forceinline__ float moe_silu_mul(float g, float u) { return __fmul_
 // Quantize one 16-element block already divided by the input scale.  Returns the scale byte and
 // writes 8 packed bytes.  Order of operations: crates/eider-cuda/native/non_gemm.cu:120-153.
 __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32_t valid, uint2* packed_out) {
+    if (valid == 16) {
+        // Whole blocks without an infinity: one max per element (fmaxf drops NaNs as the maximum below does, an infinity
+        // shows in the result) and the quotient without its special-case comparisons.  Same bytes as the path below.
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+        if (m != __int_as_float(0x7f800000)) {
+            const uint8_t sc = m == 0.0f ? 0 : ue4m3_code(div6_rn(m));
+            const float s = e4m3_value(sc);
+            uint32_t w[2] = {0u, 0u};
+            if (s != 0.0f) {
+                const Divisor ds = make_divisor(s);  // (an E4M3 value: always inside the fast range)
+#pragma unroll
+                for (int i = 0; i < 16; i += 2)
+                    w[i / 8] |= static_cast<uint32_t>(e2m1x2_code(div_rn_finite(v[i], ds), div_rn_finite(v[i + 1], ds))) << ((i % 8) * 4);
+            }
+            *packed_out = make_uint2(w[0], w[1]);
+            return sc;
+        }
+    }
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i)

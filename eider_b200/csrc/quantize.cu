@@ -181,10 +181,19 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_rowscale_kernel(const T* 
     const uint32_t b = threadIdx.x;
     float v[16];
     float amax = 0.0f;
+    bool has_inf = false;
     if (b < blocks) {
         Loader<T>::load16(input + static_cast<size_t>(row) * k + b * 16, v);
+        // one max per element: fmaxf drops NaNs as the quantizer's maximum does; an infinity (which it must drop too) shows
+        // in the result and sends the block down the careful path
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, finite_abs(v[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        has_inf = amax == __int_as_float(0x7f800000);
+        if (has_inf) {
+            amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, finite_abs(v[i]));
+        }
     }
     float bmax = amax;  // maximum of this thread's block, before scaling
 #pragma unroll
@@ -207,11 +216,16 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_rowscale_kernel(const T* 
     const float sv = e4m3_value(sc);
     const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
     uint32_t w[2] = {0u, 0u};
+    if (sv == 0.0f) {
+        // an all-zero (or all non-finite) block: zero codes
+    } else if (!has_inf && ds.fast) {
 #pragma unroll
-    for (int i = 0; i < 16; i += 2) {
-        const float lo = sv == 0.0f ? 0.0f : div_rn(v[i] * inv_g, ds);
-        const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1] * inv_g, ds);
-        w[i / 8] |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << ((i % 8) * 4);
+        for (int i = 0; i < 16; i += 2)
+            w[i / 8] |= static_cast<uint32_t>(e2m1x2_code(div_rn_finite(v[i] * inv_g, ds), div_rn_finite(v[i + 1] * inv_g, ds))) << ((i % 8) * 4);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i += 2)
+            w[i / 8] |= static_cast<uint32_t>(e2m1x2_code(div_rn(v[i] * inv_g, ds), div_rn(v[i + 1] * inv_g, ds))) << ((i % 8) * 4);
     }
     *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (k / 2) + b * 8) = make_uint2(w[0], w[1]);
     if (TILED) scales[tiled_scale_offset(row, b, k)] = sc;

@@ -97,6 +97,34 @@ def test_rowscale(ops, oracle, tokens, k, dtype):
     assert np.array_equal(q.scales.cpu().numpy(), scales)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_rowscale_with_specials_everywhere(ops, oracle, dtype):
+    # signed zeros, infinities of both signs, NaNs, denormals and huge values sprinkled over random rows: blocks with an
+    # infinity take the kernel's careful path, all others the short one, and both must give the reference's bytes
+    import torch
+    rng = np.random.default_rng(11)
+    tokens, k = 96, 5120
+    x = rng.standard_normal((tokens, k)).astype(np.float32)
+    x[rng.random((tokens, k)) < 0.02] = 0.0
+    x[rng.random((tokens, k)) < 0.02] = -0.0
+    x[rng.random((tokens, k)) < 0.002] = np.inf
+    x[rng.random((tokens, k)) < 0.002] = -np.inf
+    x[rng.random((tokens, k)) < 0.002] = np.nan
+    x[rng.random((tokens, k)) < 0.01] *= 1e-30
+    x[5] *= 1e20
+    x[6] *= 1e-25
+    x[7, :] = 0.0
+    x[8, :16] = -0.0
+    x[9, 16:32] = [np.inf] * 8 + [-np.inf] * 8
+    if dtype == "bf16":
+        x = oracle.bf16_round(x)
+    q = ops.quantize_nvfp4_rowscale(_dev(x, torch.bfloat16 if dtype == "bf16" else None))
+    packed, scales, row = oracle.quantize_nvfp4_rowscale(x)
+    assert np.array_equal(q.row_scales.cpu().numpy(), row)
+    assert np.array_equal(q.scales.cpu().numpy(), scales)
+    assert np.array_equal(q.packed.cpu().numpy(), packed)
+
+
 def test_weight_quantize_and_repack(ops, oracle):
     rng = np.random.default_rng(3)
     w = (rng.standard_normal((384, 1024)) * 0.02).astype(np.float32)
