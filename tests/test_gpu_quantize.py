@@ -82,7 +82,8 @@ def test_all_zero_and_nonfinite_rows(ops, oracle):
 
 # (up to 16384 elements per row: one thread per 16-element block; up to 32768: one thread per 8 elements in up to four
 # passes; longer rows: the generic kernel)
-@pytest.mark.parametrize("tokens,k", [(1, 5120), (33, 2048), (512, 5120), (130, 13824), (3, 8208), (5, 32768), (2, 32784)])
+@pytest.mark.parametrize("tokens,k", [(1, 5120), (33, 2048), (512, 5120), (130, 13824), (3, 8208), (5, 32768), (2, 32784),
+                                      (1300, 13824)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_rowscale(ops, oracle, tokens, k, dtype):
     import torch
