@@ -468,7 +468,13 @@ def config_sweep(args):
                 plan.run(xq, ws[i % copies], out=y)
 
             iters = max(4, min(args.steps, int(4000 / max(1.0, m / 64))))
+            # the large cases run into the power cap and the SM clock takes about a second to come back: without a pause the
+            # case measured next inherits the lowered clock (measured: 35.4 us instead of 24.7 us for M = 512, K = 13824)
+            torch.cuda.synchronize()
+            time.sleep(2.0)
             us_step = _graph_time_us(torch, step, iters, reps=3)
+            torch.cuda.synchronize()
+            time.sleep(2.0)
             us_gemm = _graph_time_us(torch, lambda i: plan.run(xq, ws[i % copies], out=y), iters, reps=3)
             assert plan.status() == 0
             fl = 2.0 * m * n * k
@@ -482,7 +488,7 @@ def config_sweep(args):
             del x, xq, y, plan
         del ws
     print(json.dumps({"metric": METRIC, "unit": UNIT, "n_gpus": 1, "data": "synthetic", "config": {"workload": "dense NVFP4 W4A4 sweep"},
-                      "timing": "CUDA-graph replay, best of 3, 4 rotating weight copies", "peak_hbm_gbs": peaks["hbm_gbs"],
+                      "timing": "CUDA-graph replay, best of 3, 4 rotating weight copies, 2 s idle before every measurement (clock recovery after a power-capped case)", "peak_hbm_gbs": peaks["hbm_gbs"],
                       "peak_source": peaks["source"], "cases": cases}), flush=True)
 
 

@@ -46,8 +46,10 @@ def test_quantizers_stay_inside_their_outputs():
         assert not bool((packed == 0xAB).all().item())
 
 
-@pytest.mark.parametrize("m,n,k,block_n", [(130, 264, 1056, 0), (300, 328, 512, 512), (512, 1024, 1024, 512), (1, 144, 64, 0)])
-def test_dense_gemm_writes_exactly_its_output(m, n, k, block_n):
+# (the last two: K split over three work items per tile, fp32 partial sums summed by the reduce kernel)
+@pytest.mark.parametrize("m,n,k,block_n,splits", [(130, 264, 1056, 0, 0), (300, 328, 512, 512, 0), (512, 1024, 1024, 512, 0), (1, 144, 64, 0, 0),
+                                                  (100, 330, 4096, 128, 3), (300, 328, 3072, 512, 3)])
+def test_dense_gemm_writes_exactly_its_output(m, n, k, block_n, splits):
     torch = require_cuda()
     from eider_b200 import ops
     w = ops.ModelOptWeight.quantize(torch.randn(n, k, device="cuda") * 0.02)
@@ -58,6 +60,8 @@ def test_dense_gemm_writes_exactly_its_output(m, n, k, block_n):
         plan = ops.Fp4TnMatmulPlan(m, n, k)
         if block_n:
             plan.set_block_n(block_n)
+        if splits:
+            plan.set_k_splits(splits)
         plan.run(xq, w, out=out)
         torch.cuda.synchronize()
         assert plan.status() == 0 and intact()
