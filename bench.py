@@ -825,8 +825,8 @@ def run_prefill(args):
     nvfp4_peak = 4.0 * peaks["bf16_tflops"]
     roofline = {
         "bound": "tensor",
-        "kernel": ("gemm_pair_kernel<nvfp4> (tcgen05.mma cta_group::2 kind::mxf4nvf4.block_scale, 256x256 tiles on CTA pairs)"
-                   if active.block_n == 512 else
+        "kernel": (f"gemm_pair_kernel<nvfp4> (tcgen05.mma cta_group::2 kind::mxf4nvf4.block_scale, 256x{256 if active.block_n == 512 else 192} tiles on CTA pairs)"
+                   if active.block_n in (512, 384) else
                    f"gemm_kernel<nvfp4, {active.block_n}> (tcgen05.mma kind::mxf4nvf4.block_scale)"),
         "achieved": achieved, "peak": nvfp4_peak, "unit": "TFLOP/s", "frac": achieved / nvfp4_peak,
         "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TF/s); NVFP4 is not measured by the driver",

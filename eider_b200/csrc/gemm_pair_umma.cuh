@@ -21,11 +21,15 @@ namespace gemm {
 
 constexpr uint32_t kPairN = 256;      // weight rows per pair tile
 constexpr uint32_t kPairHalfN = 128;  // of which each CTA loads half
+// The narrow form, 256 x 192 tiles: two whole accumulators fit in tensor memory beside the scale columns (no shared columns
+// to hand over between tiles), and a weight matrix of few column tiles divides into more work items (5120 rows: 27 instead
+// of 20 for 74 SM pairs).  A tile that does not start on a 128-row scale tile starts two scale columns into it.
+constexpr uint32_t kPairNarrowN = 192;
 
-template <int KIND> struct PairSmem {
+template <int KIND, uint32_t PAIR_N = kPairN> struct PairSmem {
     static constexpr bool kNv = KIND == kNvf4;
     static constexpr uint32_t kA = kTileRows * kStageBytesK;          // this CTA's 128 rows
-    static constexpr uint32_t kB = kPairHalfN * kStageBytesK;         // this CTA's half of the weight rows
+    static constexpr uint32_t kB = (PAIR_N / 2) * kStageBytesK;       // this CTA's half of the weight rows
     static constexpr uint32_t kSfA = kNv ? 4 * kScaleTileBytes : 0;   // scales of this CTA's rows
     static constexpr uint32_t kSfB = kNv ? 8 * kScaleTileBytes : 0;   // scales of all 256 weight rows
     static constexpr uint32_t kStage = kA + kB + kSfA + kSfB;
@@ -44,6 +48,7 @@ struct PairTile {
     uint32_t split;
 };
 
+template <uint32_t PAIR_N = kPairN>
 __device__ __forceinline__ bool pair_tile(const Params& p, uint32_t item, uint32_t rank, PairTile& t) {
     const uint32_t row_pairs = (p.row_tiles + 1) / 2;
     if (item >= row_pairs * p.col_tiles * p.splits) return false;
@@ -51,7 +56,7 @@ __device__ __forceinline__ bool pair_tile(const Params& p, uint32_t item, uint32
     const uint32_t rest = item / row_pairs;
     t.row_tile = rp * 2 + rank;
     t.row0 = t.row_tile * kTileRows;
-    t.col0 = (rest % p.col_tiles) * kPairN;
+    t.col0 = (rest % p.col_tiles) * PAIR_N;
     t.split = rest / p.col_tiles;
     const uint32_t per = (p.k_stages + p.splits - 1) / p.splits;
     t.k0 = t.split * per;
@@ -59,11 +64,12 @@ __device__ __forceinline__ bool pair_tile(const Params& p, uint32_t item, uint32
     return true;
 }
 
-template <int KIND>
+template <int KIND, uint32_t PAIR_N = kPairN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, const Params p) {
-    using L = PairSmem<KIND>;
-    using T = TmemPlan<KIND, kPairN>;
+    static_assert(PAIR_N == kPairN || PAIR_N == kPairNarrowN, "pair tiles are 256 or 192 weight rows wide");
+    using L = PairSmem<KIND, PAIR_N>;
+    using T = TmemPlan<KIND, PAIR_N>;
     constexpr bool kNv = KIND == kNvf4;
     constexpr int STAGES = L::kStages;
     constexpr uint32_t kAcc = T::kAccStages;
@@ -121,7 +127,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         PairTile t;
         bool ok = true;
         bool dep_waited = false;
-        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
+        for (uint32_t item = pair; ok && pair_tile<PAIR_N>(p, item, rank, t); item += pairs) {
             const bool row_sf = kNv && t.row_tile < p.row_tiles;
             const uint32_t sf_col_tile0 = t.col0 / kTileRows;
             const bool second_sf = sf_col_tile0 + 1 < sf_col_tiles;
@@ -137,7 +143,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                 const size_t k_off = static_cast<size_t>(s) * 4 * kScaleTileBytes;
                 // weights first: they do not depend on the kernel that ran before this one
                 umma::tma_load_2d(smem_b + stage * L::kB, &map_cols, &full[stage], static_cast<int32_t>(s * kStageBytesK),
-                                  static_cast<int32_t>(t.col0 + rank * kPairHalfN));
+                                  static_cast<int32_t>(t.col0 + rank * (PAIR_N / 2)));
                 if (kNv) {
                     umma::bulk_load_1d(smem_sfb + stage * L::kSfB, p.sf_cols + static_cast<size_t>(sf_col_tile0) * p.sf_tile_stride + k_off,
                                        kb * kScaleTileBytes, &full[stage]);
@@ -164,7 +170,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         uint32_t it = 0;
         PairTile t;
         bool ok = true;
-        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs) {
+        for (uint32_t item = pair; ok && pair_tile<PAIR_N>(p, item, rank, t); item += pairs) {
             for (uint32_t s = t.k0; s < t.k1; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
@@ -176,7 +182,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------------ even CTA: MMA issuer for the pair
         const bool leader = umma::elect_one();
-        constexpr uint32_t idesc = kNv ? umma::idesc_nvf4_pair(kPairN) : umma::idesc_f8_pair(kPairN);
+        constexpr uint32_t idesc = kNv ? umma::idesc_nvf4_pair(PAIR_N) : umma::idesc_f8_pair(PAIR_N);
         const uint32_t a_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_a));
         const uint32_t b_lo0 = umma::desc_lo_sw128(umma::smem_u32(smem_b));
         const uint32_t sfa_lo0 = umma::desc_lo_scales(umma::smem_u32(smem_sfa));
@@ -189,12 +195,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         uint32_t it = 0, tile_count = 0;
         PairTile t;
         bool ok = true;
-        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
+        for (uint32_t item = pair; ok && pair_tile<PAIR_N>(p, item, rank, t); item += pairs, ++tile_count) {
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
             if (!__all_sync(0xffffffffu, umma::mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, umma::kTimeoutTmemEmpty))) { ok = false; break; }
             umma::tc_fence_after();
             const uint32_t d_tmem = tmem_base + (T::kOverlap ? (tile_count & 1) : acc) * T::kAccStride;
+            // a column tile that does not start on a 128-row scale tile starts (col0 % 128) / 32 scale columns into it
+            const uint32_t sfb_sub = (PAIR_N % kTileRows != 0) ? (t.col0 % kTileRows) / 32 : 0;
             for (uint32_t s = t.k0; s < t.k1; ++s, ++it) {
                 const uint32_t stage = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
@@ -219,7 +227,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
                             const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
                             const uint32_t accumulate = (s > t.k0 || j > 0) ? 1u : 0u;
-                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
+                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8 + sfb_sub, accumulate);
                             else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         }
                     } else {
@@ -234,7 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                             const uint64_t a_desc = umma::make_desc(a_lo + j * 2, umma::kDescHiSw128);
                             const uint64_t b_desc = umma::make_desc(b_lo + j * 2, umma::kDescHiSw128);
                             const uint32_t accumulate = (s > t.k0 || j > 0) ? 1u : 0u;
-                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8, accumulate);
+                            if (kNv) umma::mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4, sfb_tmem + j * 8 + sfb_sub, accumulate);
                             else umma::mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         }
                     }
@@ -257,7 +265,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
         uint32_t tile_count = 0;
         PairTile t;
         bool ok = true;
-        for (uint32_t item = pair; ok && pair_tile(p, item, rank, t); item += pairs, ++tile_count) {
+        for (uint32_t item = pair; ok && pair_tile<PAIR_N>(p, item, rank, t); item += pairs, ++tile_count) {
             const uint32_t acc = tile_count % kAcc;
             const uint32_t acc_phase = (tile_count / kAcc) & 1;
             if (!umma::mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, p.status, umma::kTimeoutTmemFull)) { ok = false; break; }
@@ -269,7 +277,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
             const uint32_t buf = T::kOverlap ? (tile_count & 1) : acc;
             const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * T::kAccStride;
             // overlapping buffers: buffer 0 shares its last 64 columns, buffer 1 its first ones; drain those first
-            auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (kPairN - 64 - step * 64) : step * 64; };
+            auto col_of = [&](uint32_t step) { return (T::kOverlap && buf == 0) ? (PAIR_N - 64 - step * 64) : step * 64; };
             auto issue = [&](uint32_t step, uint32_t (&r)[64]) {
                 const uint32_t c = col_of(step);
                 umma::tmem_load_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
@@ -279,7 +287,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_cons
                               (p.ld_out % 16) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;
             const bool staged = p.out_maps != nullptr;  // (the host sets the maps only for plain bf16 output)
             const bool multicast = p.out_multicast != nullptr;  // (likewise, and only when the column count is a multiple of 8)
-            constexpr uint32_t kSteps = kPairN / 64;
+            constexpr uint32_t kSteps = PAIR_N / 64;
             uint32_t raw[2][64];
             issue(0, raw[0]);
 #pragma unroll

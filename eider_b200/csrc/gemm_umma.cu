@@ -164,11 +164,11 @@ cudaError_t make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t c
 }
 
 // CTA-pair kernel: clusters of two along x, as many pairs as can be co-resident (one CTA per SM).
-template <int KIND>
+template <int KIND, uint32_t PAIR_N = kPairN>
 cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols, const Params& p, uint32_t pair_items,
                         cudaStream_t stream) {
-    using L = PairSmem<KIND>;
-    auto kernel = gemm_pair_kernel<KIND>;
+    using L = PairSmem<KIND, PAIR_N>;
+    auto kernel = gemm_pair_kernel<KIND, PAIR_N>;
     static std::atomic<int> max_pairs_of[kMaxDevices];
     const int dev = current_device();
     int max_pairs = max_pairs_of[dev].load(std::memory_order_acquire);
@@ -208,6 +208,8 @@ cudaError_t launch_pair(const CUtensorMap& map_rows, const CUtensorMap& map_cols
 
 // ------------------------------------------------------------------------------------ plans
 constexpr uint32_t kPairBlockCode = 512;  // DensePlan::block_n value that selects the CTA-pair kernel
+constexpr uint32_t kPairNarrowBlockCode = 384;  // ... and its 256 x 192 form
+inline bool is_pair_code(uint32_t block_n) { return block_n == kPairBlockCode || block_n == kPairNarrowBlockCode; }
 
 struct DensePlan {
     int kind;
@@ -301,8 +303,18 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
     // faster than one-CTA 256-wide tiles).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
     if (row_tiles >= 2 && (row_tiles % 2 == 0 || row_tiles >= 9)) {
         const uint32_t pair_items = ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN);
-        const float cost = static_cast<float>((pair_items + sms / 2 - 1) / (sms / 2)) * 128.0f * 0.93f;
-        if (cost <= best_cost) return kPairBlockCode;
+        const uint32_t waves = (pair_items + sms / 2 - 1) / (sms / 2);
+        const float cost = static_cast<float>(waves) * 128.0f * 0.93f;
+        if (cost <= best_cost) {
+            // 256 x 192 pair tiles when they need fewer (or, being smaller, no more) turns of the SM pairs: a 192-wide tile
+            // takes 0.81 - 0.95 of a 256-wide one (0.9 here), so it has to save a wave in most cases.  Measured with
+            // K 13824 -> N 5120 (20 against 27 column tiles for 74 pairs): 512 tokens 24.6 -> 22.5 us, 1024 tokens
+            // 41.6 -> 36.2 us, 2048 tokens 60.0 -> 57.0 us; N 27648 stays with 256 (512 tokens: 33.2 against 35.5 us).
+            const uint32_t narrow_items = ((row_tiles + 1) / 2) * ((n + kPairNarrowN - 1) / kPairNarrowN);
+            const uint32_t narrow_waves = (narrow_items + sms / 2 - 1) / (sms / 2);
+            if (static_cast<float>(narrow_waves) * 0.9f < static_cast<float>(waves) * 0.98f) return kPairNarrowBlockCode;
+            return kPairBlockCode;
+        }
     }
     return best;
 }
@@ -318,9 +330,10 @@ uint32_t pick_k_splits(int kind, uint32_t m, uint32_t n, uint32_t k, uint32_t bl
     const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
     if (row_tiles > 1) return 1;
     const uint32_t stages = ((kind == kNvf4 ? k / 2 : k) + kStageBytesK - 1) / kStageBytesK;
-    const bool pair = block_n == kPairBlockCode;
+    const bool pair = is_pair_code(block_n);
     const uint32_t slots = pair ? static_cast<uint32_t>(sm_count()) / 2 : static_cast<uint32_t>(sm_count());
-    const uint32_t items = pair ? ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN) : row_tiles * ((n + block_n - 1) / block_n);
+    const uint32_t pair_n = block_n == kPairNarrowBlockCode ? kPairNarrowN : kPairN;
+    const uint32_t items = pair ? ((row_tiles + 1) / 2) * ((n + pair_n - 1) / pair_n) : row_tiles * ((n + block_n - 1) / block_n);
     if (slots == 0) return 1;
     const float out_mb = static_cast<float>(m) * static_cast<float>(n) * 4.0f * 1e-6f;
     auto cost = [&](uint32_t s) {
@@ -374,7 +387,7 @@ cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x
     cudaError_t st = plan.maps_x.get(&map_rows_p, x_values, plan.m, k_bytes, k_bytes, kTileRows);
     if (st != cudaSuccess) return st;
     // (the CTA-pair kernel loads the weight tile in two 128-row halves)
-    st = plan.maps_w.get(&map_cols_p, w_values, plan.n, k_bytes, k_bytes, plan.block_n == kPairBlockCode ? kPairHalfN : plan.block_n);
+    st = plan.maps_w.get(&map_cols_p, w_values, plan.n, k_bytes, k_bytes, plan.block_n == kPairBlockCode ? kPairHalfN : plan.block_n == kPairNarrowBlockCode ? kPairNarrowN / 2 : plan.block_n);
     if (st != cudaSuccess) return st;
     const CUtensorMap& map_rows = *map_rows_p;
     const CUtensorMap& map_cols = *map_cols_p;
@@ -461,6 +474,13 @@ cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x
         const uint32_t pair_items = ((p.row_tiles + 1) / 2) * p.col_tiles * p.splits;
         return reduce(nv ? launch_pair<kNvf4>(map_rows, map_cols, p, pair_items, stream)
                          : launch_pair<kFp8>(map_rows, map_cols, p, pair_items, stream));
+    }
+    if (plan.block_n == kPairNarrowBlockCode) {
+        // 256 x 192 tiles on CTA pairs
+        p.col_tiles = (plan.n + kPairNarrowN - 1) / kPairNarrowN;
+        const uint32_t pair_items = ((p.row_tiles + 1) / 2) * p.col_tiles * p.splits;
+        return reduce(nv ? launch_pair<kNvf4, kPairNarrowN>(map_rows, map_cols, p, pair_items, stream)
+                         : launch_pair<kFp8, kPairNarrowN>(map_rows, map_cols, p, pair_items, stream));
     }
     const uint32_t items = p.row_tiles * p.col_tiles * p.splits;
 #define EIDER_DENSE(KIND, BN) reduce(launch<KIND, BN, false, 1, false>(map_rows, map_cols, p, items, stream))
@@ -754,7 +774,7 @@ cudaError_t eider_b200_nvfp4_gemm_tn_on_stream(void* raw, const uint8_t* x_value
 
 int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     auto* plan = static_cast<DensePlan*>(raw);
-    if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256 && block_n != kPairBlockCode)) return 0;
+    if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256 && !is_pair_code(block_n))) return 0;
     plan->block_n = block_n;
     // the split count goes with the tile shape
     if (set_k_splits(*plan, pick_k_splits(plan->kind, plan->m, plan->n, plan->k, block_n)) != cudaSuccess) plan->splits = 1;

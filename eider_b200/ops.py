@@ -188,7 +188,7 @@ class Fp4TnMatmulPlan:
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192, 256, 512 (CTA pairs, 256 x 256) or 384 (CTA pairs, 256 x 192), got {block_n}")
 
     @property
     def k_splits(self) -> int:
@@ -267,7 +267,7 @@ class Fp8TnMatmulPlan:
 
     def set_block_n(self, block_n: int) -> None:
         if not self._lib.eider_b200_gemm_plan_set_block_n(self._plan, block_n):
-            raise ShapeError(f"block_n must be 64, 128, 192, 256 or 512 (CTA pairs), got {block_n}")
+            raise ShapeError(f"block_n must be 64, 128, 192, 256, 512 (CTA pairs, 256 x 256) or 384 (CTA pairs, 256 x 192), got {block_n}")
 
     @property
     def k_splits(self) -> int:

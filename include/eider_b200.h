@@ -528,7 +528,7 @@ EIDER_B200_API cudaError_t infer_moe_weighted_accumulate_sorted_bf16_batch_on_st
     uint32_t len, uint32_t routes_per_row, cudaStream_t stream);
 
 /* Tile-shape override (64, 128, 192 or 256 weight rows per tile; 512 = 256 x 256 tiles computed by pairs of CTAs
- * with tcgen05 cta_group::2) and the kernel status word of a plan
+ * with tcgen05 cta_group::2, 384 = 256 x 192 tiles on such pairs) and the kernel status word of a plan
  * (0 = ok; non-zero = a bounded device wait expired, low byte = which). */
 EIDER_B200_API int eider_b200_gemm_plan_set_block_n(void* plan, uint32_t block_n);
 EIDER_B200_API uint32_t eider_b200_gemm_plan_block_n(void* plan); /* the tile code in use (0 for a null plan) */

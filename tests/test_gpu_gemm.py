@@ -104,14 +104,16 @@ def test_nvfp4_gemm_random(ops, oracle, m, n, k, block_n):
     _nvfp4_case(ops, oracle, x, w, block_n=block_n, rowscale=True, out_dtype="bf16")
 
 
+@pytest.mark.parametrize("block_n", [512, 384])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 256), (130, 264, 1056), (384, 640, 288), (512, 1024, 5120), (1000, 2304, 2048), (512, 3456, 512)])
-def test_nvfp4_gemm_cta_pairs(ops, oracle, m, n, k):
-    # tile code 512: 256 x 256 tiles computed by clusters of two CTAs (tcgen05 cta_group::2); odd row-tile counts,
-    # partial tiles in both directions and a K that is not a multiple of the stage depth are all in the list
+def test_nvfp4_gemm_cta_pairs(ops, oracle, m, n, k, block_n):
+    # tile code 512: 256 x 256 tiles computed by clusters of two CTAs (tcgen05 cta_group::2), 384: 256 x 192 tiles (two whole
+    # accumulators, every other tile starting in the middle of a 128-row scale tile); odd row-tile counts, partial tiles in
+    # both directions and a K that is not a multiple of the stage depth are all in the list
     rng = np.random.default_rng(m * 7 + n + k)
     x = rng.standard_normal((m, k)).astype(np.float32)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
-    _nvfp4_case(ops, oracle, x, w, block_n=512, rowscale=True, out_dtype="bf16")
+    _nvfp4_case(ops, oracle, x, w, block_n=block_n, rowscale=True, out_dtype="bf16")
 
 
 def test_nvfp4_gemm_cta_pairs_general_epilogue(ops, oracle):
@@ -119,8 +121,9 @@ def test_nvfp4_gemm_cta_pairs_general_epilogue(ops, oracle):
     rng = np.random.default_rng(11)
     x = rng.standard_normal((300, 512)).astype(np.float32)
     w = rng.standard_normal((328, 512)).astype(np.float32)
-    _nvfp4_case(ops, oracle, x, w, block_n=512, out_dtype="f32")
-    _nvfp4_case(ops, oracle, x, w, block_n=512, beta=0.5, out_dtype="bf16", alpha=0.01)
+    for code in (512, 384):
+        _nvfp4_case(ops, oracle, x, w, block_n=code, out_dtype="f32")
+        _nvfp4_case(ops, oracle, x, w, block_n=code, beta=0.5, out_dtype="bf16", alpha=0.01)
 
 
 def test_nvfp4_gemm_beta_accumulate(ops, oracle):
@@ -185,8 +188,9 @@ def test_fp8_gemm_scaled(ops, oracle, m, n, k):
     assert ok, stats
 
 
+@pytest.mark.parametrize("block_n", [512, 384])
 @pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (300, 328, 1040)])
-def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k):
+def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k, block_n):
     import torch
     rng = np.random.default_rng(m + n + 1)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -194,7 +198,7 @@ def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k):
     wq, ws = ops.quantize_fp8_weight(_dev(w))
     xq, xs = ops.quantize_fp8_dynamic(_dev(x, torch.bfloat16))
     plan = ops.Fp8TnMatmulPlan(m, n, k)
-    plan.set_block_n(512)
+    plan.set_block_n(block_n)
     y = plan.run(xq, wq, xs, ws, out_dtype=torch.bfloat16)
     assert plan.status() == 0
     ref = oracle.fp8_linear(xq.cpu().numpy(), xs.cpu().numpy(), wq.cpu().numpy(), ws.cpu().numpy())
@@ -203,7 +207,8 @@ def test_fp8_gemm_cta_pairs(ops, oracle, m, n, k):
 
 
 @pytest.mark.parametrize("m,n,k,block_n,splits", [(128, 320, 4096, 128, 3), (100, 264, 2080, 64, 2), (128, 512, 4096, 256, 2),
-                                                   (256, 512, 4096, 512, 4), (300, 328, 2336, 512, 2), (40, 5120, 13824, 128, 3)])
+                                                   (256, 512, 4096, 512, 4), (300, 328, 2336, 512, 2), (40, 5120, 13824, 128, 3),
+                                                   (300, 400, 2336, 384, 3)])
 @pytest.mark.parametrize("out_dtype,beta,rowscale", [("bf16", 0.0, True), ("f32", 0.5, False)])
 def test_nvfp4_gemm_split_k(ops, oracle, m, n, k, block_n, splits, out_dtype, beta, rowscale):
     # K divided over several work items per tile, fp32 partial sums summed by a second kernel: same criterion as unsplit
@@ -240,6 +245,12 @@ def test_split_k_choice_and_argument_checks(ops):
     assert ops.Fp4TnMatmulPlan(128, 27648, 5120).k_splits == 1
     assert ops.Fp4TnMatmulPlan(4096, 5120, 13824).k_splits == 1
     assert ops.Fp4TnMatmulPlan(256, 5120, 13824).k_splits == 1  # (more than one row tile: the partial sums cost more than they save)
+    # tile shape: pairs of CTAs from two row tiles on; 256 x 192 tiles where they save a turn of the 74 SM pairs
+    assert ops.Fp4TnMatmulPlan(512, 27648, 5120).block_n == 512
+    assert ops.Fp4TnMatmulPlan(4096, 27648, 5120).block_n == 512
+    assert ops.Fp4TnMatmulPlan(512, 5120, 13824).block_n == 384
+    assert ops.Fp4TnMatmulPlan(1024, 5120, 13824).block_n == 384
+    assert ops.Fp4TnMatmulPlan(8192, 5120, 13824).block_n == 512
     plan = ops.Fp4TnMatmulPlan(128, 256, 512)  # two 128-byte K stages
     for bad in (0, 17, 3):
         with pytest.raises(CudaError):

@@ -48,7 +48,7 @@ def test_quantizers_stay_inside_their_outputs():
 
 # (the last two: K split over three work items per tile, fp32 partial sums summed by the reduce kernel)
 @pytest.mark.parametrize("m,n,k,block_n,splits", [(130, 264, 1056, 0, 0), (300, 328, 512, 512, 0), (512, 1024, 1024, 512, 0), (1, 144, 64, 0, 0),
-                                                  (100, 330, 4096, 128, 3), (300, 328, 3072, 512, 3)])
+                                                  (100, 330, 4096, 128, 3), (300, 328, 3072, 512, 3), (300, 328, 512, 384, 0), (260, 1000, 1024, 384, 2)])
 def test_dense_gemm_writes_exactly_its_output(m, n, k, block_n, splits):
     torch = require_cuda()
     from eider_b200 import ops
