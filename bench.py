@@ -606,8 +606,8 @@ def run_prefill(args):
             for q in fused_plans:
                 if args.block_n:
                     q.set_block_n(args.block_n)
-                elif M > 128:
-                    q.set_block_n(512)  # the CTA-pair kernel stages whole tiles for the stores that leave the GPU
+                elif M > 128 and q.block_n not in (512, 384):
+                    q.set_block_n(512)  # the CTA-pair kernels stage whole tiles for the stores that leave the GPU
             # one multimem.st per tile pays from eight ranks on (measured: one TMA store per peer is faster on two and four)
             use_multicast = (not args.no_multicast) and (world >= 8 or args.multicast)
             sharded.fuse_into(fused_plans, M, multicast=use_multicast)

@@ -419,9 +419,9 @@ cudaError_t run_dense(DensePlan& plan, const uint8_t* x_values, const uint8_t* x
         p.out = plan.peers[0];
         p.ld_out = plan.peer_ld;
         // plain bf16 output on the CTA-pair kernel: whole tiles leave through shared memory and TMA stores
-        if (plan.peer_maps && out_is_bf16 && !channel_scale && plan.block_n == kPairBlockCode) p.out_maps = plan.peer_maps;
+        if (plan.peer_maps && out_is_bf16 && !channel_scale && is_pair_code(plan.block_n)) p.out_maps = plan.peer_maps;
         // one multicast store per tile instead of one store per peer
-        if (plan.multicast && out_is_bf16 && !channel_scale && plan.block_n == kPairBlockCode && plan.n % 8 == 0) {
+        if (plan.multicast && out_is_bf16 && !channel_scale && is_pair_code(plan.block_n) && plan.n % 8 == 0) {
             p.out_multicast = plan.multicast;
             p.out_maps = nullptr;
         }

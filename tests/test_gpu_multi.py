@@ -47,7 +47,8 @@ def _worker(rank, world, port, result):
         lin_fused.fuse_into(plan_fused, m)
         # plain peer stores (tile shape chosen by the plan), CTA pairs with one multicast store per tile (when the box
         # offers an NVLink multicast mapping), CTA pairs with one TMA store per peer
-        for code, use_multicast in ((0, False), (512, True), (512, False)):
+        # (384: the 256 x 192 form of the pair kernel, three 64-column steps per tile through the same staging buffers)
+        for code, use_multicast in ((0, False), (512, True), (512, False), (384, True), (384, False)):
             if code:
                 plan_fused.set_block_n(code)
             if not use_multicast:
