@@ -291,30 +291,33 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
     const uint32_t sms = static_cast<uint32_t>(sm_count());
     uint32_t best = 64;
     float best_cost = 1e30f;
-    for (uint32_t bn : {256u, 128u, 64u}) {
+    // (ties go to the narrower tile: the same number of waves with more SMs streaming; measured, 128 tokens, K 13824 -> N 5120:
+    // 18.6 us with 64-wide, 19.7 us with 128-wide tiles; 384 tokens, K 5120 -> N 27648: 29.8 us with 192-wide, 32.5 us with 256-wide)
+    for (uint32_t bn : {256u, 192u, 128u, 64u}) {
         const uint32_t tiles = row_tiles * ((n + bn - 1) / bn);
-        const float cost = static_cast<float>((tiles + sms - 1) / sms) * (bn == 256u ? 128.0f : 103.0f);
-        if (cost < best_cost) {
+        // (a 192-wide tile is bound by its loads, not by the 103-cycle floor of its MMA: 25.4 us against 22.2 us for the same
+        // outputs per SM on 256 x 192 pair tiles, whose cost below is 107)
+        const float cost = static_cast<float>((tiles + sms - 1) / sms) * (bn == 256u ? 128.0f : bn == 192u ? 123.0f : 103.0f);
+        if (cost <= best_cost) {
             best_cost = cost;
             best = bn;
         }
     }
-    // Two or more row tiles: 256 x 256 tiles on CTA pairs (each CTA fills only half of the weight tile, measured about 7 %
-    // faster than one-CTA 256-wide tiles).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
+    // Two or more row tiles: tiles on CTA pairs (each CTA fills only half of the weight tile, measured about 7 % faster than
+    // one-CTA 256-wide tiles).  An odd row-tile count wastes half a pair tile, which only large counts amortise.
+    // 256 x 192 pair tiles take 0.81 - 0.95 of a 256 x 256 one (0.9 here) and must promise 2 % to be preferred, so they are
+    // chosen where they save a turn of the SM pairs.  Measured with K 13824 -> N 5120 (20 against 27 column tiles for 74
+    // pairs): 512 tokens 24.6 -> 22.5 us, 1024 tokens 41.6 -> 36.2 us, 2048 tokens 60.0 -> 57.0 us; N 27648 stays with 256
+    // (512 tokens: 33.2 against 35.5 us).
     if (row_tiles >= 2 && (row_tiles % 2 == 0 || row_tiles >= 9)) {
-        const uint32_t pair_items = ((row_tiles + 1) / 2) * ((n + kPairN - 1) / kPairN);
-        const uint32_t waves = (pair_items + sms / 2 - 1) / (sms / 2);
+        const uint32_t pairs = sms / 2;
+        const uint32_t row_pairs = (row_tiles + 1) / 2;
+        const uint32_t waves = (row_pairs * ((n + kPairN - 1) / kPairN) + pairs - 1) / pairs;
+        const uint32_t narrow_waves = (row_pairs * ((n + kPairNarrowN - 1) / kPairNarrowN) + pairs - 1) / pairs;
         const float cost = static_cast<float>(waves) * 128.0f * 0.93f;
-        if (cost <= best_cost) {
-            // 256 x 192 pair tiles when they need fewer (or, being smaller, no more) turns of the SM pairs: a 192-wide tile
-            // takes 0.81 - 0.95 of a 256-wide one (0.9 here), so it has to save a wave in most cases.  Measured with
-            // K 13824 -> N 5120 (20 against 27 column tiles for 74 pairs): 512 tokens 24.6 -> 22.5 us, 1024 tokens
-            // 41.6 -> 36.2 us, 2048 tokens 60.0 -> 57.0 us; N 27648 stays with 256 (512 tokens: 33.2 against 35.5 us).
-            const uint32_t narrow_items = ((row_tiles + 1) / 2) * ((n + kPairNarrowN - 1) / kPairNarrowN);
-            const uint32_t narrow_waves = (narrow_items + sms / 2 - 1) / (sms / 2);
-            if (static_cast<float>(narrow_waves) * 0.9f < static_cast<float>(waves) * 0.98f) return kPairNarrowBlockCode;
-            return kPairBlockCode;
-        }
+        const float narrow_cost = static_cast<float>(narrow_waves) * 128.0f * 0.93f * 0.9f;
+        if (narrow_cost * 1.02f < cost && narrow_cost <= best_cost) return kPairNarrowBlockCode;
+        if (cost <= best_cost) return kPairBlockCode;
     }
     return best;
 }
@@ -346,7 +349,7 @@ uint32_t pick_k_splits(int kind, uint32_t m, uint32_t n, uint32_t k, uint32_t bl
     float best_cost = cost(1) * 0.85f;
     for (uint32_t s : {2u, 3u, 4u, 5u, 6u, 8u}) {
         const uint32_t per = (stages + s - 1) / s;
-        if (per < 8 || (s - 1) * per >= stages) continue;
+        if (per < 8 || (s - 1) * per >= stages || items * s > slots) continue;  // (and the split items still fit in one wave)
         const float c = cost(s);
         if (c < best_cost) {
             best_cost = c;

@@ -240,7 +240,10 @@ def test_fp8_gemm_split_k(ops, oracle, block_n, splits):
 def test_split_k_choice_and_argument_checks(ops):
     from eider_b200._lib import CudaError
     # few tiles and a long K: split; enough tiles, or a short K: not
-    assert ops.Fp4TnMatmulPlan(128, 5120, 13824).k_splits == 3
+    assert ops.Fp4TnMatmulPlan(128, 2560, 13824).k_splits == 3
+    narrow = ops.Fp4TnMatmulPlan(128, 5120, 13824)  # 80 tiles of 64 weight rows: no split would fit in one wave
+    assert narrow.block_n == 64 and narrow.k_splits == 1
+    assert ops.Fp4TnMatmulPlan(384, 27648, 5120).block_n == 192
     assert ops.Fp4TnMatmulPlan(512, 27648, 5120).k_splits == 1
     assert ops.Fp4TnMatmulPlan(128, 27648, 5120).k_splits == 1
     assert ops.Fp4TnMatmulPlan(4096, 5120, 13824).k_splits == 1
