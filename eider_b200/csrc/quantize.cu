@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
         if (threadIdx.x == 0) row_scales[row] = g;
     }
     const Divisor dg = make_divisor(g);
+    const bool unit = g == 1.0f;  // (x / 1 is x: the usual case of the routed-MoE rows and of calibrated scales folded elsewhere)
     uint8_t* prow = packed + static_cast<size_t>(row) * (k / 2);
     const uint32_t blocks = k / 16;
 #pragma unroll
@@ -140,10 +141,18 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
         const uint32_t h = threadIdx.x + j * blockDim.x;
         float v[8];
         float amax = 0.0f;
+        // one max per element: fmaxf drops NaNs as the quantizer's maximum does; an infinity (which it must drop too) shows
+        // in the result and sends the whole warp down the careful path for this pass
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            v[i] = div_rn(held[j][i], dg);
-            amax = fmaxf(amax, finite_abs(v[i]));
+            v[i] = unit ? held[j][i] : div_rn(held[j][i], dg);
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+        const bool careful = __any_sync(0xffffffffu, amax == __int_as_float(0x7f800000));
+        if (careful) {
+            amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, finite_abs(v[i]));
         }
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the other half of the block (all lanes take part)
         if (h >= halves) continue;
@@ -151,11 +160,16 @@ __global__ void __launch_bounds__(1024) quantize_nvfp4_fast_kernel(const T* __re
         const float sv = e4m3_value(sc);
         const Divisor ds = make_divisor(sv == 0.0f ? 1.0f : sv);
         uint32_t w = 0;
+        if (sv == 0.0f) {
+            // an all-zero (or all non-finite) block: zero codes
+        } else if (!careful) {
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float lo = sv == 0.0f ? 0.0f : div_rn(v[i], ds);
-            const float hi = sv == 0.0f ? 0.0f : div_rn(v[i + 1], ds);
-            w |= static_cast<uint32_t>(e2m1x2_code(lo, hi)) << (i * 4);
+            for (int i = 0; i < 8; i += 2)
+                w |= static_cast<uint32_t>(e2m1x2_code(div_rn_finite(v[i], ds), div_rn_finite(v[i + 1], ds))) << (i * 4);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i += 2)
+                w |= static_cast<uint32_t>(e2m1x2_code(div_rn(v[i], ds), div_rn(v[i + 1], ds))) << (i * 4);
         }
         *reinterpret_cast<uint32_t*>(prow + h * 4) = w;
         if ((h & 1) == 0) {
