@@ -124,6 +124,8 @@ SIGNATURES = {
     "eider_b200_gemm_plan_block_n": (_U32, [_P]),
     "eider_b200_gemm_plan_set_k_splits": (_I, [_P, _U32]),
     "eider_b200_gemm_plan_k_splits": (_U32, [_P]),
+    "eider_b200_gemm_pick_tile": (_U32, [_U32, _U32, _U32]),
+    "eider_b200_gemm_pick_k_splits": (_U32, [_I, _U32, _U32, _U32, _U32, _U32]),
     "eider_b200_gemm_plan_set_output_peers": (_I, [_P, _P, _U32, _U32]),
     "eider_b200_gemm_plan_status": (_I, [_P, _P]),
     "eider_b200_gemm_plan_set_output_multicast": (_I, [_P, _P]),

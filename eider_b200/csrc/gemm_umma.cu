@@ -284,11 +284,10 @@ bool dense_shape_ok(int kind, uint32_t m, uint32_t n, uint32_t k) {
     return k % 16 == 0;
 }
 
-uint32_t pick_block_n(uint32_t m, uint32_t n) {
+uint32_t pick_block_n(uint32_t m, uint32_t n, uint32_t sms) {
     // Cost model in MMA-cycles per K step: the slowest SM runs `waves` tiles, and an MMA retires in about 128 cycles at
     // N = 256 but never under about 103 however narrow it is, so narrower tiles only pay when they save a whole wave.
     const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
-    const uint32_t sms = static_cast<uint32_t>(sm_count());
     uint32_t best = 64;
     float best_cost = 1e30f;
     // (ties go to the narrower tile: the same number of waves with more SMs streaming; measured, 128 tokens, K 13824 -> N 5120:
@@ -329,12 +328,13 @@ uint32_t pick_block_n(uint32_t m, uint32_t n) {
 // 20.0 -> 29.8 us with two and 512 tokens 24.7 -> 40.7 us with three), so a plan only chooses a split for a single row tile;
 // the count comes from a coarse model (0.6 us per 128-byte K stage and wave, partials written at 10 TB/s and read at 6 TB/s,
 // 2 us per extra launch, at least eight stages per split, a predicted gain of 15 %).
-uint32_t pick_k_splits(int kind, uint32_t m, uint32_t n, uint32_t k, uint32_t block_n) {
+uint32_t pick_k_splits(int kind, uint32_t m, uint32_t n, uint32_t k, uint32_t block_n, uint32_t sms) {
     const uint32_t row_tiles = (m + kTileRows - 1) / kTileRows;
     if (row_tiles > 1) return 1;
     const uint32_t stages = ((kind == kNvf4 ? k / 2 : k) + kStageBytesK - 1) / kStageBytesK;
+    if (stages < 32) return 1;  // (a short K: the second launch costs what the split saves; the measured gains are at 54 stages)
     const bool pair = is_pair_code(block_n);
-    const uint32_t slots = pair ? static_cast<uint32_t>(sm_count()) / 2 : static_cast<uint32_t>(sm_count());
+    const uint32_t slots = pair ? sms / 2 : sms;
     const uint32_t pair_n = block_n == kPairNarrowBlockCode ? kPairNarrowN : kPairN;
     const uint32_t items = pair ? ((row_tiles + 1) / 2) * ((n + pair_n - 1) / pair_n) : row_tiles * ((n + block_n - 1) / block_n);
     if (slots == 0) return 1;
@@ -747,12 +747,12 @@ int eider_b200_nvfp4_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k) { ret
 
 void* eider_b200_nvfp4_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
     if (!dense_shape_ok(kNvf4, m, n, k)) return nullptr;
-    auto* plan = new DensePlan{kNvf4, m, n, k, pick_block_n(m, n), nullptr};
+    auto* plan = new DensePlan{kNvf4, m, n, k, pick_block_n(m, n, static_cast<uint32_t>(sm_count())), nullptr};
     if (alloc_status(&plan->status) != cudaSuccess) {
         delete plan;
         return nullptr;
     }
-    if (set_k_splits(*plan, pick_k_splits(kNvf4, m, n, k, plan->block_n)) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
+    if (set_k_splits(*plan, pick_k_splits(kNvf4, m, n, k, plan->block_n, static_cast<uint32_t>(sm_count()))) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
     return plan;
 }
 
@@ -780,7 +780,7 @@ int eider_b200_gemm_plan_set_block_n(void* raw, uint32_t block_n) {
     if (!plan || (block_n != 64 && block_n != 128 && block_n != 192 && block_n != 256 && !is_pair_code(block_n))) return 0;
     plan->block_n = block_n;
     // the split count goes with the tile shape
-    if (set_k_splits(*plan, pick_k_splits(plan->kind, plan->m, plan->n, plan->k, block_n)) != cudaSuccess) plan->splits = 1;
+    if (set_k_splits(*plan, pick_k_splits(plan->kind, plan->m, plan->n, plan->k, block_n, static_cast<uint32_t>(sm_count()))) != cudaSuccess) plan->splits = 1;
     return 1;
 }
 
@@ -788,6 +788,18 @@ cudaError_t eider_b200_gemm_plan_set_k_splits(void* raw, uint32_t splits) {
     auto* plan = static_cast<DensePlan*>(raw);
     if (!plan) return cudaErrorInvalidValue;
     return set_k_splits(*plan, splits);
+}
+
+// The plans' own choices as plain functions of the shape and the SM count (no device needed): what a plan created for
+// (m, n[, k]) on a device of `sms` SMs starts with.
+uint32_t eider_b200_gemm_pick_tile(uint32_t m, uint32_t n, uint32_t sms) {
+    if (m == 0 || n == 0 || sms < 2) return 0;
+    return pick_block_n(m, n, sms);
+}
+
+uint32_t eider_b200_gemm_pick_k_splits(int is_nvfp4, uint32_t m, uint32_t n, uint32_t k, uint32_t block_n, uint32_t sms) {
+    if (m == 0 || n == 0 || k == 0 || sms < 2 || block_n == 0) return 0;
+    return pick_k_splits(is_nvfp4 ? kNvf4 : kFp8, m, n, k, block_n, sms);
 }
 
 uint32_t eider_b200_gemm_plan_k_splits(void* raw) {
@@ -849,12 +861,12 @@ int eider_b200_fp8_gemm_tn_supported(uint32_t m, uint32_t n, uint32_t k) { retur
 
 void* eider_b200_fp8_gemm_tn_create(uint32_t m, uint32_t n, uint32_t k) {
     if (!dense_shape_ok(kFp8, m, n, k)) return nullptr;
-    auto* plan = new DensePlan{kFp8, m, n, k, pick_block_n(m, n), nullptr};
+    auto* plan = new DensePlan{kFp8, m, n, k, pick_block_n(m, n, static_cast<uint32_t>(sm_count())), nullptr};
     if (alloc_status(&plan->status) != cudaSuccess) {
         delete plan;
         return nullptr;
     }
-    if (set_k_splits(*plan, pick_k_splits(kFp8, m, n, k, plan->block_n)) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
+    if (set_k_splits(*plan, pick_k_splits(kFp8, m, n, k, plan->block_n, static_cast<uint32_t>(sm_count()))) != cudaSuccess) plan->splits = 1;  // (no workspace: no split)
     return plan;
 }
 

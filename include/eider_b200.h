@@ -542,6 +542,11 @@ EIDER_B200_API uint32_t eider_b200_gemm_plan_block_n(void* plan); /* the tile co
  * all-gather is on. */
 EIDER_B200_API cudaError_t eider_b200_gemm_plan_set_k_splits(void* plan, uint32_t splits);
 EIDER_B200_API uint32_t eider_b200_gemm_plan_k_splits(void* plan); /* the split count in use (0 for a null plan) */
+/* The choices a dense plan makes at creation, as plain functions of the shape and the device's SM count (no device is
+ * touched): the tile code for m tokens x n output features, and the K split count for that tile code (is_nvfp4: 1 for
+ * NVFP4 operands, 0 for FP8).  0 for a zero extent or fewer than two SMs. */
+EIDER_B200_API uint32_t eider_b200_gemm_pick_tile(uint32_t m, uint32_t n, uint32_t sms);
+EIDER_B200_API uint32_t eider_b200_gemm_pick_k_splits(int is_nvfp4, uint32_t m, uint32_t n, uint32_t k, uint32_t block_n, uint32_t sms);
 /* Fused all-gather for a column-sharded dense layer (no reference counterpart: the reference is single-GPU).  peers[q]
  * points at this rank's first output column inside rank q's full [tokens][ld_out] output (its own buffer included),
  * mapped into this process (CUDA IPC / symmetric memory), 32-byte aligned; count <= 8.  While set, the GEMM's epilogue
